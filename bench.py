@@ -1,0 +1,358 @@
+#!/usr/bin/env python3
+"""Benchmark of the SpMM hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Workload ("c2_dim_sweep"): three seeded synthetic 1,000,000 x 1,000,000 CSR matrices with
+16 entries per row on average (uniform-random columns, banded with half-bandwidth 32, R-MAT
+power-law a=.57 b=c=.19), values U[0,1), dense operand 2U-1, dims 16..256 step 16, fp32.
+One step = one pass over all 48 (matrix, dim) SpMMs.  Metric: GFLOP/s = 2*nnz*dim / t summed
+over the pass.  Every launch is timed on the device with its own pair of CUDA events and the
+L2 cache is flushed (a 256 MiB device memset) before each launch, outside the events; the
+step time is the sum of the launch times.  With N > 1 (torchrun, one rank per GPU) every rank
+runs the same pass on its own row block of an N-times taller matrix with the dense operand
+replicated (no data-path collective); the step time is the maximum over ranks.
+
+`--impl reference` times the reference's CPU path for the same product,
+torch.sparse.mm on a CSR tensor on the host (verification.py:44-77 of the reference), on a
+bounded sample of the workload with all host threads.
+"""
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+N_ROWS = 1_000_000
+NNZ_PER_ROW = 16
+DIMS = list(range(16, 257, 16))
+MATRICES = ("uniform", "banded", "rmat")
+FALLBACK_HBM_GBS = 6650.0
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="native", choices=["native", "reference"])
+    ap.add_argument("--rows", type=int, default=N_ROWS, help="rows per matrix (smaller for quick checks)")
+    ap.add_argument("--dims", type=int, nargs="*", default=DIMS)
+    ap.add_argument("--e2e-steps", type=int, default=2)
+    ap.add_argument("--cpu-seconds", type=float, default=15.0)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    return ap.parse_args()
+
+
+def measured_peak():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            return float(json.load(open(p))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+def spmm_bytes(n_rows, n_cols, nnz, dim, n_seg=None):
+    """Compulsory traffic of one SpMM: every array touched exactly once."""
+    b = 4 * (n_rows + 1) + 8 * nnz + 4 * dim * n_cols + 4 * dim * n_rows
+    if n_seg is not None:
+        b += 4 * (n_seg + 1) + 4 * n_seg - 4 * (n_rows + 1)
+    return b
+
+
+def build_matrices(n, device, seed_shift=0):
+    from paramspmm_ae_b200 import synth
+    scale = max(1, (n - 1).bit_length())
+    nnz = n * NNZ_PER_ROW
+    return {
+        "uniform": synth.uniform_rows(n, NNZ_PER_ROW, seed=21 + seed_shift, device=device),
+        "banded": synth.banded_rows(n, NNZ_PER_ROW, 32, seed=22 + seed_shift, device=device),
+        "rmat": synth.rmat(scale, nnz, n=n, seed=23 + seed_shift, device=device),
+    }
+
+
+# ----------------------------------------------------------------------------- clocks
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons of one GPU every 200 ms through NVML (read only)."""
+
+    def __init__(self, index):
+        super().__init__(daemon=True)
+        self.index, self.samples, self.reasons, self.max_mhz = index, [], set(), None
+        self._stop_evt = threading.Event()
+
+    def run(self):
+        try:
+            import pynvml as nv
+            nv.nvmlInit()
+            h = nv.nvmlDeviceGetHandleByIndex(self.index)
+            self.max_mhz = nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)
+            names = {
+                getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8): "hw_slowdown",
+                getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40): "hw_thermal_slowdown",
+                getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
+                getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4): "sw_power_cap",
+            }
+            get = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+                nv.nvmlDeviceGetCurrentClocksThrottleReasons
+            while not self._stop_evt.is_set():
+                self.samples.append(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM))
+                mask = get(h)
+                for bit, name in names.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+                self._stop_evt.wait(0.2)
+        except Exception as e:  # NVML missing: report that instead of inventing clocks
+            self.reasons.add("nvml_unavailable:%s" % type(e).__name__)
+
+    def stop(self):
+        self._stop_evt.set()
+        self.join(timeout=2)
+        return {"sm_mhz": statistics.median(self.samples) if self.samples else None,
+                "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons)}
+
+
+# ----------------------------------------------------------------------------- CPU arms
+def cpu_spmm_gflops(mats_cpu, dim, seconds, max_iters=50):
+    """torch.sparse.mm on CSR tensors on the host, all threads: GFLOP/s over one SpMM per matrix."""
+    import torch
+    from paramspmm_ae_b200 import synth
+    B = synth.dense_uniform(next(iter(mats_cpu.values())).n_cols, dim, 11)
+    sps = [torch.sparse_csr_tensor(m.rowPtr, m.colIdx, m.val, size=(m.n_rows, m.n_cols)) for m in mats_cpu.values()]
+    flops = sum(2.0 * m.nnz * dim for m in mats_cpu.values())
+    for s in sps:
+        torch.sparse.mm(s, B)  # warm-up
+    t_all, it = 0.0, 0
+    while t_all < seconds and it < max_iters:
+        t0 = time.perf_counter()
+        for s in sps:
+            torch.sparse.mm(s, B)
+        t_all += time.perf_counter() - t0
+        it += 1
+    return flops * it / t_all / 1e9, it
+
+
+def run_reference(args):
+    """The reference's CPU implementation of the product, same metric and unit."""
+    import torch
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    dim = 64
+    mats = build_matrices(args.rows, "cpu")
+    flops = sum(2.0 * m.nnz * dim for m in mats.values())
+    from paramspmm_ae_b200 import synth
+    B = synth.dense_uniform(args.rows, dim, 11)
+    sps = [torch.sparse_csr_tensor(m.rowPtr, m.colIdx, m.val, size=(m.n_rows, m.n_cols)) for m in mats.values()]
+    for _ in range(max(1, args.warmup)):
+        for s in sps:
+            torch.sparse.mm(s, B)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        for s in sps:
+            torch.sparse.mm(s, B)
+    dt = time.perf_counter() - t0
+    val = flops * args.steps / dt / 1e9
+    sample = "one SpMM per matrix (uniform, banded, rmat; %d rows, 16 nnz/row) at dim %d" % (args.rows, dim)
+    print(json.dumps({
+        "impl": "reference", "metric": "SpMM GFLOP/s (2*nnz*dim/t)", "value": val, "unit": "GFLOP/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "c2_dim_sweep", "rows": args.rows, "nnz_per_row": NNZ_PER_ROW},
+        "cpu_baseline": {"value": val, "unit": "GFLOP/s", "cores": torch.get_num_threads(), "kind": "reference",
+                         "sample": sample + "; torch.sparse.mm(CSR) on the host, the reference's CPU path"},
+        "e2e": {"value": val, "unit": "GFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+# ----------------------------------------------------------------------------- native arm
+def main():
+    args = parse()
+    if args.impl == "reference":
+        run_reference(args)
+        return
+    import torch
+    import torch.distributed as dist
+    from paramspmm_ae_b200 import _lib, decider, ops, synth
+
+    _lib.lib()  # no CUDA library, no benchmark
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group(backend="nccl", device_id=dev)
+    n = args.rows
+    dims = args.dims
+
+    # ---- inputs, resident in HBM before any timing starts
+    mats = build_matrices(n, dev, seed_shift=100 * rank)
+    plans, layouts = {}, {}
+    for name, m in mats.items():
+        st = decider.row_stats(m.rowPtr)
+        for dim in dims:
+            plans[name, dim] = decider.choose(st, dim)
+        grans = sorted({p["granularity"] for (nm, _), p in plans.items() if nm == name and p["if_split"]})
+        for g in grans:
+            rps, tr = ops.split_csr(m.rowPtr.cpu(), g)
+            layouts[name, g] = (rps.to(dev), tr.to(dev))
+    Bs = {dim: synth.dense_uniform(n, dim, 1000 + dim, dev) for dim in dims}
+    Cs = {dim: torch.empty(n, dim, device=dev) for dim in dims}
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    cases = [(name, dim) for dim in dims for name in MATRICES]
+
+    def launch(name, dim):
+        m, p = mats[name], plans[name, dim]
+        cfg = _lib.make_cfg(**p.kernel_cfg())
+        if p["if_split"]:
+            rps, tr = layouts[name, p["granularity"]]
+            ops.spmm_into(Cs[dim], Bs[dim], rps, m.colIdx, m.val, target_row=tr, n_out_rows=n, cfg=cfg)
+            return 2
+        ops.spmm_into(Cs[dim], Bs[dim], m.rowPtr, m.colIdx, m.val, cfg=cfg)
+        return 1
+
+    def one_pass(events=None):
+        launches = 0
+        for i, (name, dim) in enumerate(cases):
+            flush.zero_()  # evict L2 (outside the timed events)
+            if events is not None:
+                events[i][0].record()
+            launches += launch(name, dim)
+            if events is not None:
+                events[i][1].record()
+        return launches
+
+    for _ in range(max(3, args.warmup)):
+        one_pass()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    sampler = ClockSampler(local)
+    sampler.start()
+    evs = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in cases]
+           for _ in range(args.steps)]
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    launches = 0
+    for s in range(args.steps):
+        launches += one_pass(evs[s])
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - t0
+    clocks = sampler.stop()
+    per_case = [[evs[s][i][0].elapsed_time(evs[s][i][1]) for s in range(args.steps)] for i in range(len(cases))]
+    mean_ms = [sum(x) / len(x) for x in per_case]
+    step_ms = sum(mean_ms)
+    t = torch.tensor([step_ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.barrier()
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    step_ms_max = float(t.item())
+    flops_step = sum(2.0 * mats[name].nnz * dim for name, dim in cases)
+    value = world * flops_step / (step_ms_max * 1e-3) / 1e9
+
+    # ---- roofline of the launch that takes the largest share of the pass
+    peak, peak_kind = measured_peak()
+    sweep = []
+    for (name, dim), ms in zip(cases, mean_ms):
+        p = plans[name, dim]
+        n_seg = layouts[name, p["granularity"]][1].numel() if p["if_split"] else None
+        by = spmm_bytes(n, n, mats[name].nnz, dim, n_seg)
+        sweep.append({"matrix": name, "dim": dim, "ms": round(ms, 5),
+                      "gflops": round(2.0 * mats[name].nnz * dim / ms / 1e6, 1),
+                      "gbs": round(by / ms / 1e6, 1), "frac": round(by / ms / 1e6 / peak, 4),
+                      "split": int(p["if_split"])})
+    top = max(range(len(cases)), key=lambda i: mean_ms[i])
+    roofline = {"bound": "hbm", "achieved": sweep[top]["gbs"], "peak": peak, "unit": "GB/s",
+                "frac": sweep[top]["frac"], "traffic": None, "peak_source": peak_kind,
+                "kernel": "spmm_seg_kernel %s dim=%d" % (sweep[top]["matrix"], sweep[top]["dim"]),
+                "bytes_model": "4(n+1)+8nnz+4*dim*n_cols+4*dim*n_rows (+8S for a split layout)",
+                "best_frac": max(s["frac"] for s in sweep),
+                "rmat_dim_ge_64_frac": [s["frac"] for s in sweep if s["matrix"] == "rmat" and s["dim"] >= 64]}
+    tr_path = os.path.join(ROOT, "profiles", "spmm_dram_traffic.json")
+    if os.path.exists(tr_path):
+        try:
+            tj = json.load(open(tr_path))
+            key = "%s_dim%d" % (sweep[top]["matrix"], sweep[top]["dim"])
+            if key in tj:
+                roofline["traffic"] = tj[key]["bytes_per_launch"]
+                roofline["traffic_source"] = tj[key].get("source")
+        except Exception:
+            pass
+
+    # ---- end to end: host buffers in, host buffer out, copies inside the timed region
+    e2e = None
+    if not args.no_e2e and args.e2e_steps > 0:
+        hostA = {name: [t.cpu().pin_memory() for t in (m.rowPtr, m.colIdx, m.val)] for name, m in mats.items()}
+        maxd = max(dims)
+        hostB = torch.empty(n * maxd, dtype=torch.float32).pin_memory()
+        hostB.copy_(synth.dense_uniform(n, maxd, 7).reshape(-1))
+        hostC = torch.empty(n * maxd, dtype=torch.float32).pin_memory()
+        h2d = d2h = 0
+
+        def e2e_pass():
+            nonlocal h2d, d2h
+            h2d = d2h = 0
+            for name, dim in cases:
+                rp, ci, v = (t.to(dev, non_blocking=True) for t in hostA[name])
+                X = hostB[: n * dim].view(n, dim).to(dev, non_blocking=True)
+                out = ops.csr_spmm(X, rp, ci, v, 1, 8)
+                hostC[: n * dim].view(n, dim).copy_(out, non_blocking=True)
+                h2d += sum(t.numel() * t.element_size() for t in hostA[name]) + n * dim * 4
+                d2h += n * dim * 4
+            torch.cuda.synchronize()
+
+        e2e_pass()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(args.e2e_steps):
+            e2e_pass()
+        b.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([a.elapsed_time(b) / args.e2e_steps], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e = {"value": world * flops_step / (float(t.item()) * 1e-3) / 1e9, "unit": "GFLOP/s",
+               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": args.e2e_steps,
+               "call": "ParamSpMM.csr_spmm on device copies of pinned host CSR arrays and B, result copied "
+                       "back to pinned host memory, every launch of the pass"}
+
+    # ---- CPU baseline on the host cores (rank 0, N = 1 only)
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        mats_cpu = {k: m.to("cpu") for k, m in mats.items()}
+        g, it = cpu_spmm_gflops(mats_cpu, 64, args.cpu_seconds)
+        cpu = {"value": g, "unit": "GFLOP/s", "cores": torch.get_num_threads(), "kind": "reference",
+               "sample": "%d passes of one SpMM per matrix (3 matrices, %d rows, 16 nnz/row) at dim 64 with "
+                         "torch.sparse.mm(CSR) on the host, the reference's CPU path (verification.py:44-77)" % (it, n)}
+
+    if rank == 0:
+        print(json.dumps({
+            "metric": "SpMM GFLOP/s (2*nnz*dim/t)", "value": value, "unit": "GFLOP/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": step_ms_max,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic",
+            "config": {"workload": "c2_dim_sweep", "rows_per_gpu": n, "nnz_per_row": NNZ_PER_ROW,
+                       "matrices": list(MATRICES), "dims": dims, "launches_per_step": len(cases),
+                       "l2": "flushed before every launch (256 MiB memset outside the timed events)",
+                       "sharding": "row blocks, dense operand replicated, no collective"},
+            "e2e": e2e, "gpu_launches": launches, "clocks": clocks, "roofline": roofline,
+            "cpu_baseline": cpu, "wall_ms_per_step_incl_flush": wall / args.steps * 1e3, "sweep": sweep,
+        }))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

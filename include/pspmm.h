@@ -1,0 +1,175 @@
+/*
+ * libpspmm — C ABI of the B200 (sm_100a) sparse hot path: CSR/PCSR x dense SpMM, the
+ * pattern-masked SDDMM, and the PCSR index builders.
+ *
+ * This is the drop-in boundary.  Each entry point states which function of the
+ * ParamSpMM_AE project (path inside that project : lines) it stands in for.  All device
+ * pointers are plain CUDA device addresses on the current device; all "host" pointers are
+ * ordinary process memory.  Index arrays are int32, values and dense operands fp32,
+ * dense matrices row-major with an explicit leading dimension counted in floats.
+ *
+ * Conventions
+ *   - Every function returns 0 (PSPMM_OK) or a negative PSPMM_E_* code; nothing here ever
+ *     calls exit() or prints.  pspmm_strerror() names a code; pspmm_last_cuda_error()
+ *     returns the CUDA runtime error text behind the most recent PSPMM_E_CUDA on this thread.
+ *   - Device functions enqueue work on `stream` (a cudaStream_t passed as void*; NULL is the
+ *     legacy default stream) and return without synchronising, except the pspmm_profile_*
+ *     family, which synchronises on its own events.
+ *   - Device functions allocate nothing: outputs are caller-allocated.  Unless stated
+ *     otherwise an output is fully overwritten, so it does not have to be zeroed first.
+ *   - Inputs are never modified.
+ */
+#ifndef PSPMM_H
+#define PSPMM_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Marks the exported entry points (the library is built with hidden default visibility). */
+#if defined(__GNUC__)
+#define PSPMM_API __attribute__((visibility("default")))
+#else
+#define PSPMM_API
+#endif
+
+#define PSPMM_OK 0
+#define PSPMM_E_ARG (-1)      /* null pointer, negative size, misaligned leading dimension ... */
+#define PSPMM_E_CONFIG (-2)   /* a pspmm_cfg field or CF / blkWarpNum hint outside its domain */
+#define PSPMM_E_CUDA (-3)     /* a CUDA runtime call or kernel launch failed */
+#define PSPMM_E_UNSUPPORTED (-4)
+#define PSPMM_E_RANGE (-5)    /* a size exceeds what int32 indices can address */
+
+/*
+ * Kernel parameters.  Zero in any field means "let the library choose".  These replace the
+ * reference's template tuple <CF, blkWarpNum> (SpMM/SpMM.cpp:77-141): the legacy pair is
+ * still accepted as hint_CF / hint_blkWarpNum and validated against the reference's domain
+ * (CF 1..8, blkWarpNum 4 or 8; CF 1..4 for SDDMM), but it does not constrain the launch.
+ */
+typedef struct pspmm_cfg {
+    int32_t lanes_per_row;   /* lanes that share one (split-)row: 1,2,4,8,16,32; rows per warp = 32 / this */
+    int32_t vec_width;       /* floats per lane per load of a dense row: 1, 2 or 4 (128-bit) */
+    int32_t cta_threads;     /* 128, 256 or 512 */
+    int32_t rows_per_group;  /* consecutive (split-)rows a lane group walks before its CTA retires: 1..64 */
+    int32_t hint_CF;         /* legacy coarsening factor, validated only */
+    int32_t hint_blkWarpNum; /* legacy warps per block, validated only */
+} pspmm_cfg;
+
+PSPMM_API int pspmm_version(void);
+PSPMM_API const char *pspmm_strerror(int code);
+PSPMM_API const char *pspmm_last_cuda_error(void);
+
+/* Resolve a configuration exactly as the SpMM entry points would (fills the zero fields of
+ * *cfg for the given dim / leading dimensions / alignment) without launching anything. */
+PSPMM_API int pspmm_resolve_cfg(pspmm_cfg *cfg, int32_t dim, int64_t ldB, int64_t ldC, int32_t V,
+                      const void *B, const void *C);
+
+/*
+ * C[n_rows, dim] = A[n_rows, n_cols] * B[n_cols, dim], A in CSR or in PCSR (row-split CSR).
+ *
+ * Stands in for csr_spmm (SpMM/SpMM.cpp:77-141 -> SpMM_kernel.cu:129-197, 1157-1243) when
+ * rowPtr_split/target_row are NULL, and for csr_split_spmm (SpMM.cpp:143-207 ->
+ * SpMM_kernel.cu:199-272, 1245-1360) when they are given; in the split form `rowPtr` may be
+ * NULL.  target_row must be non-decreasing (what split_csr produces).  Unlike the reference
+ * the output may have a different row count from B (row shards) and C needs no prior zeroing:
+ * rows without entries are written as zeros.  Rows cut into several pieces are accumulated
+ * with vector atomics, so their summation order is not fixed.
+ */
+PSPMM_API int pspmm_spmm_csr(const int32_t *rowPtr, const int32_t *colIdx, const float *val,
+                   const float *B, float *C, int64_t n_rows, int64_t n_cols, int64_t nnz,
+                   int32_t dim, int64_t ldB, int64_t ldC, const pspmm_cfg *cfg,
+                   const int32_t *rowPtr_split, const int32_t *target_row, int64_t n_seg,
+                   void *stream);
+
+/*
+ * Same product with V x 1 blocks: block k of block-row r has column colIdx[k] and V values
+ * val[k*V .. k*V+V) that multiply B[colIdx[k]] into output rows V*r .. V*r+V-1.
+ * V = 2 stands in for bcsr_spmm / bcsr_split_spmm (SpMM/SpMM.cpp:209-337 ->
+ * SpMM_kernel.cu:274-417, 1362-1651), V = 3 for vec_spmm / vec_split_spmm
+ * (SpMM.cpp:339-480 -> SpMM_kernel.cu:419-562, 1653-1972).  C must have V * n_blk_rows rows.
+ * n_seg / target_row describe a split of the block-rows as above (NULL, 0 for none).
+ */
+PSPMM_API int pspmm_spmm_bcsr(const int32_t *rowPtr_b, const int32_t *colIdx, const float *val, int32_t V,
+                    const float *B, float *C, int64_t n_blk_rows, int64_t n_cols, int64_t nblk,
+                    int32_t dim, int64_t ldB, int64_t ldC, const pspmm_cfg *cfg,
+                    const int32_t *rowPtr_b_split, const int32_t *target_row, int64_t n_seg,
+                    void *stream);
+
+/*
+ * out[k] = <A[row(k), :], B[colIdx[k], :]> for every stored position k of a CSR pattern.
+ * Stands in for csr_sddmm / csr_split_sddmm (SDDMM/sddmm.cpp:15-117 ->
+ * sddmm_kernel.cu:143-246, 917-1057).  Stored values are not read.  Any dim is accepted
+ * (the reference stops at 128).
+ */
+PSPMM_API int pspmm_sddmm_csr(const int32_t *rowPtr, const int32_t *colIdx, const float *A, const float *B,
+                    float *out, int64_t n_rows, int64_t nnz, int32_t dim, int64_t ldA,
+                    int64_t ldB, const pspmm_cfg *cfg, const int32_t *rowPtr_split,
+                    const int32_t *target_row, int64_t n_seg, void *stream);
+
+/*
+ * Block form: out[k*V+u] = <A[V*row(k)+u, :], B[colIdx[k], :]> where val[k*V+u] != 0, and 0
+ * elsewhere (the stored values act as the mask).  Stands in for bcsr_sddmm /
+ * bcsr_split_sddmm (SDDMM/sddmm.cpp:119-219 -> sddmm_kernel.cu:248-351, 1059-1287) with
+ * V = 2 and vec_sddmm / vec_split_sddmm (sddmm.cpp:221-336) with V = 3.
+ */
+PSPMM_API int pspmm_sddmm_bcsr(const int32_t *rowPtr_b, const int32_t *colIdx, const float *val, int32_t V,
+                     const float *A, const float *B, float *out, int64_t n_blk_rows, int64_t nblk,
+                     int32_t dim, int64_t ldA, int64_t ldB, const pspmm_cfg *cfg,
+                     const int32_t *rowPtr_b_split, const int32_t *target_row, int64_t n_seg,
+                     void *stream);
+
+/*
+ * mask[nnz]: position of every CSR entry inside the flattened [nblk, 2] value array of the
+ * 2 x 1 block layout.  Stands in for genmask (SDDMM/sddmm.cpp:663-673 ->
+ * sddmm_kernel.cu:78-141); bit-exact, device arrays, prints nothing.
+ */
+PSPMM_API int pspmm_genmask(const int32_t *rowPtr_b, const int32_t *rowPtr, const float *val_b,
+                  int64_t n_blk_rows, int64_t n_rows, int64_t nnz, int32_t *mask, void *stream);
+
+/*
+ * Host-side PCSR partition.  Stands in for split_csr / split_csr_par (SpMM/SpMM.cpp:15-75;
+ * duplicated at SpCONV/SpCONV.cpp:14-74): every row is cut into ceil(len / granularity)
+ * pieces.  pspmm_split_count returns the piece count S through *n_seg (int64 prefix sums, so
+ * it stays exact where the reference's fp32 cumulative sum does not); pspmm_split_csr fills
+ * rowPtr_split[S+1] and target_row[S].  Host arrays; bit-exact with the reference.
+ */
+PSPMM_API int pspmm_split_count(const int32_t *rowPtr, int64_t n_rows, int32_t granularity, int64_t *n_seg);
+PSPMM_API int pspmm_split_csr(const int32_t *rowPtr, int64_t n_rows, int32_t granularity,
+                    int32_t *rowPtr_split, int32_t *target_row, int64_t n_seg);
+
+/*
+ * Host-side CSR -> V x 1 block CSR, laid out exactly as scipy's tobsr((V,1)) (which the
+ * reference calls at graph_input.py:245-266): blocks of a block-row appear in order of first
+ * encounter while walking its V rows top to bottom.  pspmm_bcsr_count fills rowPtr_b
+ * [ceil(n_rows/V)+1] and returns the block count through *nblk; pspmm_bcsr_fill writes
+ * colIdx_b[nblk] and val_b[nblk*V] (zeros where a lane has no entry).
+ */
+PSPMM_API int pspmm_bcsr_count(const int32_t *rowPtr, const int32_t *colIdx, int64_t n_rows, int64_t n_cols,
+                     int32_t V, int32_t *rowPtr_b, int64_t *nblk);
+PSPMM_API int pspmm_bcsr_fill(const int32_t *rowPtr, const int32_t *colIdx, const float *val, int64_t n_rows,
+                    int64_t n_cols, int32_t V, const int32_t *rowPtr_b, int32_t *colIdx_b,
+                    float *val_b);
+
+/*
+ * Timing loops.  Stand in for the *_spmm_profile / *_sddmm_profile functions
+ * (SpMM/SpMM.cpp:482-889 -> SpMM_kernel.cu:564-1155; SDDMM/sddmm.cpp:338-661): `warmup`
+ * untimed launches, then `iters` back-to-back launches between two CUDA events on `stream`;
+ * *ms_per_iter receives the mean.  V = 1 selects the CSR kernels, V = 2 / 3 the block ones.
+ */
+PSPMM_API int pspmm_profile_spmm(const int32_t *rowPtr, const int32_t *colIdx, const float *val, int32_t V,
+                       const float *B, float *C, int64_t n_rows, int64_t n_cols, int64_t nnz,
+                       int32_t dim, int64_t ldB, int64_t ldC, const pspmm_cfg *cfg,
+                       const int32_t *rowPtr_split, const int32_t *target_row, int64_t n_seg,
+                       int32_t warmup, int32_t iters, float *ms_per_iter, void *stream);
+PSPMM_API int pspmm_profile_sddmm(const int32_t *rowPtr, const int32_t *colIdx, const float *val, int32_t V,
+                        const float *A, const float *B, float *out, int64_t n_rows, int64_t nnz,
+                        int32_t dim, int64_t ldA, int64_t ldB, const pspmm_cfg *cfg,
+                        const int32_t *rowPtr_split, const int32_t *target_row, int64_t n_seg,
+                        int32_t warmup, int32_t iters, float *ms_per_iter, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PSPMM_H */

@@ -1,0 +1,118 @@
+#!/usr/bin/env python3
+"""Build recipe for the CPU oracle (test infrastructure, never part of the product).
+
+Two targets:
+
+* ``build_oracle()``  -> ``oracle/liboracle.so`` from ``oracle/pspmm_oracle.c``
+  (gcc, OpenMP).  Always possible.
+
+* ``build_ref()``     -> ``oracle/_ref/ParamSpMM_ref.so``: the HOST side of the
+  reference's own ``SpMM/SpMM.cpp`` (its ``split_csr`` / ``split_csr_par``
+  PCSR partition builders, SpMM.cpp:15-75), compiled with g++ from the source
+  where it lies in the mounted reference tree.  Nothing is copied: only the
+  shared object lands in ``oracle/_ref/`` (git-ignored).  The CUDA launchers
+  that file refers to (``*_cuda<CF,W>``, cuSPARSE and GE-SpMM wrappers) live
+  in the reference's ``.cu`` files, which are not compiled here; each such
+  undefined symbol is satisfied by a generated stub that aborts if ever
+  called, so the module loads and its two CPU functions can be used to pin
+  the oracle's restatement.  Skipped silently when the reference tree is not
+  mounted (e.g. on a GPU box).
+
+The reference's CUDA kernels themselves are not built here: as shipped they do
+not compile against the installed torch (removed ``Tensor::type()`` dispatch
+overload), so they are treated as unbuildable.
+"""
+from __future__ import annotations
+
+import os
+import re
+import subprocess
+import sys
+import sysconfig
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+REF_ROOT = os.environ.get("PSPMM_REFERENCE_ROOT", "/root/reference")
+REF_OUT = os.path.join(HERE, "_ref")
+
+
+def _run(cmd):
+    proc = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if proc.returncode != 0:
+        raise RuntimeError("command failed: %s\n%s" % (" ".join(cmd), proc.stdout))
+    return proc.stdout
+
+
+def _newer(target, sources):
+    if not os.path.exists(target):
+        return False
+    t = os.path.getmtime(target)
+    return all(os.path.getmtime(s) <= t for s in sources)
+
+
+def build_oracle(force=False):
+    src = os.path.join(HERE, "pspmm_oracle.c")
+    out = os.path.join(HERE, "liboracle.so")
+    if not force and _newer(out, [src]):
+        return out
+    _run(["gcc", "-O2", "-fopenmp", "-fvisibility=hidden", "-shared", "-fPIC", "-std=c11",
+          src, "-o", out])
+    return out
+
+
+def ref_available():
+    return os.path.isfile(os.path.join(REF_ROOT, "SpMM", "SpMM.cpp"))
+
+
+def build_ref(force=False):
+    """Compile the reference's SpMM.cpp host code into oracle/_ref (see module docstring)."""
+    if not ref_available():
+        return None
+    src = os.path.join(REF_ROOT, "SpMM", "SpMM.cpp")
+    out = os.path.join(REF_OUT, "ParamSpMM_ref.so")
+    if not force and os.path.exists(out):
+        return out
+    import torch  # noqa: F401  (only to locate headers / libs)
+    from torch.utils import cpp_extension as ce
+
+    os.makedirs(REF_OUT, exist_ok=True)
+    obj = os.path.join(REF_OUT, "SpMM_host.o")
+    incs = []
+    for p in ce.include_paths() + [sysconfig.get_paths()["include"], "/usr/local/cuda/include",
+                                   os.path.join(REF_ROOT, "SpMM")]:
+        incs += ["-I", p]
+    _run(["g++", "-O2", "-fopenmp", "-fPIC", "-std=c++17", "-c",
+          "-DTORCH_EXTENSION_NAME=ParamSpMM_ref", "-DTORCH_API_INCLUDE_EXTENSION_H"]
+         + incs + [src, "-o", obj])
+    # Symbols that only the reference's .cu files define.
+    undefined = [ln.split()[-1] for ln in _run(["nm", "-u", obj]).splitlines() if ln.strip()]
+    gpu_only = [s for s in undefined if re.search(r"_cuda|cusparse_|gespmm_", s)]
+    stub_s = os.path.join(REF_OUT, "gpu_stubs.s")
+    with open(stub_s, "w") as f:
+        f.write("\t.text\n")
+        for s in gpu_only:
+            f.write("\t.globl %s\n\t.type %s,@function\n%s:\n\tcall abort@PLT\n" % (s, s, s))
+        f.write('\t.section .note.GNU-stack,"",@progbits\n')
+    libdir = ce.library_paths()[0]
+    _run(["g++", "-shared", "-fopenmp", obj, stub_s, "-o", out, "-L", libdir,
+          "-Wl,-rpath," + libdir, "-ltorch", "-ltorch_cpu", "-lc10", "-ltorch_python"])
+    os.remove(obj)
+    return out
+
+
+def load_ref():
+    """Import the compiled reference host module, or return None when it is not there."""
+    path = os.path.join(REF_OUT, "ParamSpMM_ref.so")
+    if not os.path.exists(path):
+        return None
+    import importlib.util
+    import torch  # noqa: F401  (libtorch must be loaded first)
+
+    spec = importlib.util.spec_from_file_location("ParamSpMM_ref", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+if __name__ == "__main__":
+    print(build_oracle(force="--force" in sys.argv))
+    print(build_ref(force="--force" in sys.argv))

@@ -1,0 +1,100 @@
+"""ctypes binding of libpspmm.so (the C ABI declared in include/pspmm.h).
+
+There is no fallback: if the shared library is missing or a call fails, an exception is
+raised.  Build it with ``python -m paramspmm_ae_b200.build``.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "libpspmm.so")
+BASELINES_PATH = os.path.join(_PKG, "libpspmm_baselines.so")
+
+PSPMM_OK = 0
+PSPMM_E_ARG = -1
+PSPMM_E_CONFIG = -2
+PSPMM_E_CUDA = -3
+PSPMM_E_UNSUPPORTED = -4
+PSPMM_E_RANGE = -5
+
+_i32 = ctypes.c_int32
+_i64 = ctypes.c_int64
+_vp = ctypes.c_void_p
+
+
+class PspmmCfg(ctypes.Structure):
+    """Mirror of ``pspmm_cfg``; zero fields mean "library's choice"."""
+
+    _fields_ = [("lanes_per_row", _i32), ("vec_width", _i32), ("cta_threads", _i32),
+                ("rows_per_group", _i32), ("hint_CF", _i32), ("hint_blkWarpNum", _i32)]
+
+
+class PspmmError(RuntimeError):
+    def __init__(self, code, text):
+        super().__init__("libpspmm: %s (code %d)" % (text, code))
+        self.code = code
+
+
+_cfgp = ctypes.POINTER(PspmmCfg)
+
+# name -> argument types, exactly as declared in include/pspmm.h
+_SIGNATURES = {
+    "pspmm_resolve_cfg": [_cfgp, _i32, _i64, _i64, _i32, _vp, _vp],
+    "pspmm_spmm_csr": [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i32, _i64, _i64, _cfgp, _vp, _vp,
+                       _i64, _vp],
+    "pspmm_spmm_bcsr": [_vp, _vp, _vp, _i32, _vp, _vp, _i64, _i64, _i64, _i32, _i64, _i64, _cfgp,
+                        _vp, _vp, _i64, _vp],
+    "pspmm_sddmm_csr": [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i32, _i64, _i64, _cfgp, _vp, _vp, _i64,
+                        _vp],
+    "pspmm_sddmm_bcsr": [_vp, _vp, _vp, _i32, _vp, _vp, _vp, _i64, _i64, _i32, _i64, _i64, _cfgp,
+                         _vp, _vp, _i64, _vp],
+    "pspmm_genmask": [_vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp],
+    "pspmm_split_count": [_vp, _i64, _i32, ctypes.POINTER(_i64)],
+    "pspmm_split_csr": [_vp, _i64, _i32, _vp, _vp, _i64],
+    "pspmm_bcsr_count": [_vp, _vp, _i64, _i64, _i32, _vp, ctypes.POINTER(_i64)],
+    "pspmm_bcsr_fill": [_vp, _vp, _vp, _i64, _i64, _i32, _vp, _vp, _vp],
+    "pspmm_profile_spmm": [_vp, _vp, _vp, _i32, _vp, _vp, _i64, _i64, _i64, _i32, _i64, _i64, _cfgp,
+                           _vp, _vp, _i64, _i32, _i32, ctypes.POINTER(ctypes.c_float), _vp],
+    "pspmm_profile_sddmm": [_vp, _vp, _vp, _i32, _vp, _vp, _vp, _i64, _i64, _i32, _i64, _i64, _cfgp,
+                            _vp, _vp, _i64, _i32, _i32, ctypes.POINTER(ctypes.c_float), _vp],
+}
+EXPORTED = ["pspmm_version", "pspmm_strerror", "pspmm_last_cuda_error"] + list(_SIGNATURES)
+
+_lib = None
+
+
+def lib():
+    """The loaded library; raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError("%s not found: build it with `python -m paramspmm_ae_b200.build` "
+                              "(there is no CPU or PyTorch fallback)" % LIB_PATH)
+        handle = ctypes.CDLL(LIB_PATH)
+        handle.pspmm_version.restype = ctypes.c_int
+        handle.pspmm_strerror.restype = ctypes.c_char_p
+        handle.pspmm_strerror.argtypes = [ctypes.c_int]
+        handle.pspmm_last_cuda_error.restype = ctypes.c_char_p
+        for name, args in _SIGNATURES.items():
+            fn = getattr(handle, name)
+            fn.restype = ctypes.c_int
+            fn.argtypes = args
+        _lib = handle
+    return _lib
+
+
+def check(code):
+    """Raise PspmmError for a non-zero return code."""
+    if code == PSPMM_OK:
+        return
+    handle = lib()
+    text = handle.pspmm_strerror(code).decode()
+    if code == PSPMM_E_CUDA:
+        text += ": " + handle.pspmm_last_cuda_error().decode()
+    raise PspmmError(code, text)
+
+
+def make_cfg(CF=0, blkWarpNum=0, lanes_per_row=0, vec_width=0, cta_threads=0, rows_per_group=0):
+    return PspmmCfg(lanes_per_row, vec_width, cta_threads, rows_per_group, CF, blkWarpNum)

@@ -1,0 +1,168 @@
+"""cuSPARSE comparators behind the names the reference exposes from its extension modules
+(SpMM/SpMM.cpp:915-925, SDDMM/sddmm.cpp:696-697).  They call libpspmm_baselines.so, which is
+separate from the product library and links cuSPARSE; they are measurement baselines, not
+part of the SpMM/SDDMM path.
+
+``gespmm_*`` (a third-party kernel the reference vendors in SpMM/Baseline_kernel.cu:601-857)
+is not re-implemented; calling it raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+import torch
+
+from . import _lib
+from .ops import PROFILE_ITERS, PROFILE_WARMUP, _check_cuda, _gflops, _ptr, _stream
+
+_handle = None
+
+
+def _bl():
+    global _handle
+    if _handle is None:
+        if not os.path.exists(_lib.BASELINES_PATH):
+            raise ImportError("%s not found: build it with `python -m paramspmm_ae_b200.build`"
+                              % _lib.BASELINES_PATH)
+        h = ctypes.CDLL(_lib.BASELINES_PATH)
+        h.pspmm_baselines_last_error.restype = ctypes.c_char_p
+        _handle = h
+    return _handle
+
+
+def _ok(rc):
+    if rc != 0:
+        raise RuntimeError("baseline call failed: " + _bl().pspmm_baselines_last_error().decode())
+
+
+class _Plan:
+    def __init__(self, handle):
+        self.h = handle
+
+    def run(self):
+        _ok(_bl().pspmm_baselines_run(self.h, _stream()))
+
+    def close(self):
+        if self.h:
+            _bl().pspmm_baselines_plan_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        self.close()
+
+
+def spmm_plan(fmt, idx0, idx1, val, X, out, n_rows=None):
+    """fmt: 0 CSR default algorithm, 1 CSR ALG2, 2 COO, 3 CSC."""
+    for t, nm in ((idx0, "idx0"), (idx1, "idx1")):
+        _check_cuda(t, nm, torch.int32, 1)
+    _check_cuda(val, "values", torch.float32, 1)
+    _check_cuda(X, "input", torch.float32, 2)
+    n_cols, dim = X.shape
+    if n_rows is None:
+        n_rows = out.shape[0]
+    h = ctypes.c_void_p(0)
+    _ok(_bl().pspmm_baselines_spmm_plan(ctypes.byref(h), int(fmt), _ptr(idx0), _ptr(idx1), _ptr(val),
+                                        _ptr(X), _ptr(out), ctypes.c_int64(n_rows),
+                                        ctypes.c_int64(n_cols), ctypes.c_int64(val.shape[0]),
+                                        ctypes.c_int32(dim), ctypes.c_int64(X.stride(0)),
+                                        ctypes.c_int64(out.stride(0))))
+    return _Plan(h)
+
+
+def sddmm_plan(A, B, rowPtr, colIdx, val_out):
+    _check_cuda(A, "A", torch.float32, 2)
+    _check_cuda(B, "B", torch.float32, 2)
+    h = ctypes.c_void_p(0)
+    _ok(_bl().pspmm_baselines_sddmm_plan(ctypes.byref(h), _ptr(rowPtr), _ptr(colIdx), _ptr(val_out),
+                                         _ptr(A), _ptr(B), ctypes.c_int64(rowPtr.shape[0] - 1),
+                                         ctypes.c_int64(B.shape[0]), ctypes.c_int64(colIdx.shape[0]),
+                                         ctypes.c_int32(A.shape[1]), ctypes.c_int64(A.stride(0)),
+                                         ctypes.c_int64(B.stride(0))))
+    return _Plan(h)
+
+
+def time_plan_ms(plan, warmup=PROFILE_WARMUP, iters=PROFILE_ITERS):
+    for _ in range(warmup):
+        plan.run()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        plan.run()
+    e1.record()
+    e1.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
+def _compute(fmt, X, i0, i1, val):
+    out = torch.empty_like(X)
+    plan = spmm_plan(fmt, i0, i1, val, X, out)
+    plan.run()
+    torch.cuda.current_stream().synchronize()
+    plan.close()
+    return out
+
+
+def _profile(fmt, X, i0, i1, val):
+    out = torch.empty_like(X)
+    plan = spmm_plan(fmt, i0, i1, val, X, out)
+    ms = time_plan_ms(plan)
+    plan.close()
+    return _gflops(val.shape[0], X.shape[1], ms)
+
+
+def cusparse_compute(X, rowPtr, colIdx, val):
+    return _compute(0, X, rowPtr, colIdx, val)
+
+
+def cusparse_profile(X, rowPtr, colIdx, val):
+    return _profile(0, X, rowPtr, colIdx, val)
+
+
+def cusparse_compute_csr_alg2(X, rowPtr, colIdx, val):
+    return _compute(1, X, rowPtr, colIdx, val)
+
+
+def cusparse_profile_csr_alg2(X, rowPtr, colIdx, val):
+    return _profile(1, X, rowPtr, colIdx, val)
+
+
+def cusparse_compute_coo_alg4(X, row, col, val):
+    return _compute(2, X, row, col, val)
+
+
+def cusparse_profile_coo_alg4(X, row, col, val):
+    return _profile(2, X, row, col, val)
+
+
+def cusparse_compute_csc(X, colPtr, rowIdx, val):
+    return _compute(3, X, colPtr, rowIdx, val)
+
+
+def cusparse_profile_csc(X, colPtr, rowIdx, val):
+    return _profile(3, X, colPtr, rowIdx, val)
+
+
+def cusparse_sddmm_compute(A, B, rowPtr, colIdx, val):
+    """Overwrites `val` in place, as the reference's wrapper does
+    (SDDMM/sddmm_baseline_kernel.cu:24-80)."""
+    plan = sddmm_plan(A, B, rowPtr, colIdx, val)
+    plan.run()
+    torch.cuda.current_stream().synchronize()
+    plan.close()
+    return val
+
+
+def cusparse_sddmm_profile(A, B, rowPtr, colIdx, val):
+    plan = sddmm_plan(A, B, rowPtr, colIdx, val)
+    ms = time_plan_ms(plan)
+    plan.close()
+    return _gflops(colIdx.shape[0], A.shape[1], ms)
+
+
+def gespmm_compute(X, rowPtr, colIdx, val):
+    raise NotImplementedError("GE-SpMM is third-party code that is not part of this library")
+
+
+def gespmm_profile(X, rowPtr, colIdx, val):
+    raise NotImplementedError("GE-SpMM is third-party code that is not part of this library")

@@ -1,0 +1,148 @@
+// libpspmm_baselines: cuSPARSE comparators, kept out of libpspmm so the product library has no
+// cuSPARSE dependency.  These reproduce the call sequences the reference times its kernels
+// against (SpMM/Baseline_kernel.cu:24-599: cusparseSpMM on CSR with ALG_DEFAULT and CSR_ALG2,
+// COO, CSC; SDDMM/sddmm_baseline_kernel.cu:24-164: cusparseSDDMM), with the handle,
+// descriptors and workspace created once per plan instead of once per call.
+#include <cuda_runtime.h>
+#include <cusparse.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#define PB_API extern "C" __attribute__((visibility("default")))
+
+static thread_local char g_err[256] = "";
+PB_API const char *pspmm_baselines_last_error(void) { return g_err; }
+
+#define PB_CUSPARSE(expr)                                                                  \
+    do {                                                                                   \
+        cusparseStatus_t s__ = (expr);                                                     \
+        if (s__ != CUSPARSE_STATUS_SUCCESS) {                                              \
+            snprintf(g_err, sizeof(g_err), "cuSPARSE: %s (%s)", cusparseGetErrorString(s__), #expr); \
+            return -1;                                                                     \
+        }                                                                                  \
+    } while (0)
+#define PB_CUDA(expr)                                                                      \
+    do {                                                                                   \
+        cudaError_t e__ = (expr);                                                          \
+        if (e__ != cudaSuccess) {                                                          \
+            snprintf(g_err, sizeof(g_err), "CUDA: %s (%s)", cudaGetErrorString(e__), #expr); \
+            return -1;                                                                     \
+        }                                                                                  \
+    } while (0)
+
+struct Plan {
+    cusparseHandle_t handle = nullptr;
+    cusparseSpMatDescr_t A = nullptr;
+    cusparseDnMatDescr_t X = nullptr, Y = nullptr;
+    void *workspace = nullptr;
+    size_t workspace_bytes = 0;
+    int kind = 0;  // 0 SpMM, 1 SDDMM
+    cusparseSpMMAlg_t alg = CUSPARSE_SPMM_ALG_DEFAULT;
+    cusparseOperation_t opB = CUSPARSE_OPERATION_NON_TRANSPOSE;
+};
+
+static void plan_free(Plan *p)
+{
+    if (!p)
+        return;
+    if (p->X) cusparseDestroyDnMat(p->X);
+    if (p->Y) cusparseDestroyDnMat(p->Y);
+    if (p->A) cusparseDestroySpMat(p->A);
+    if (p->workspace) cudaFree(p->workspace);
+    if (p->handle) cusparseDestroy(p->handle);
+    delete p;
+}
+
+PB_API int pspmm_baselines_plan_destroy(void *plan)
+{
+    plan_free((Plan *)plan);
+    return 0;
+}
+
+// fmt: 0 CSR + ALG_DEFAULT, 1 CSR + CSR_ALG2, 2 COO + ALG_DEFAULT, 3 CSC + ALG_DEFAULT.
+// idx0/idx1: (rowPtr, colIdx) for CSR, (row, col) for COO, (colPtr, rowIdx) for CSC.
+PB_API int pspmm_baselines_spmm_plan(void **out, int fmt, const int32_t *idx0, const int32_t *idx1,
+                                     const float *val, const float *B, float *C, int64_t n_rows,
+                                     int64_t n_cols, int64_t nnz, int32_t dim, int64_t ldB,
+                                     int64_t ldC)
+{
+    if (!out || fmt < 0 || fmt > 3)
+        return -1;
+    Plan *p = new Plan();
+    struct Guard { Plan *&p; ~Guard() { if (p) plan_free(p); } } guard{p};
+    PB_CUSPARSE(cusparseCreate(&p->handle));
+    void *i0 = (void *)idx0, *i1 = (void *)idx1, *v = (void *)val;
+    if (fmt == 0 || fmt == 1)
+        PB_CUSPARSE(cusparseCreateCsr(&p->A, n_rows, n_cols, nnz, i0, i1, v, CUSPARSE_INDEX_32I,
+                                      CUSPARSE_INDEX_32I, CUSPARSE_INDEX_BASE_ZERO, CUDA_R_32F));
+    else if (fmt == 2)
+        PB_CUSPARSE(cusparseCreateCoo(&p->A, n_rows, n_cols, nnz, i0, i1, v, CUSPARSE_INDEX_32I,
+                                      CUSPARSE_INDEX_BASE_ZERO, CUDA_R_32F));
+    else
+        PB_CUSPARSE(cusparseCreateCsc(&p->A, n_rows, n_cols, nnz, i0, i1, v, CUSPARSE_INDEX_32I,
+                                      CUSPARSE_INDEX_32I, CUSPARSE_INDEX_BASE_ZERO, CUDA_R_32F));
+    PB_CUSPARSE(cusparseCreateDnMat(&p->X, n_cols, dim, ldB, (void *)B, CUDA_R_32F, CUSPARSE_ORDER_ROW));
+    PB_CUSPARSE(cusparseCreateDnMat(&p->Y, n_rows, dim, ldC, (void *)C, CUDA_R_32F, CUSPARSE_ORDER_ROW));
+    p->alg = fmt == 1 ? CUSPARSE_SPMM_CSR_ALG2 : CUSPARSE_SPMM_ALG_DEFAULT;
+    const float alpha = 1.f, beta = 0.f;
+    PB_CUSPARSE(cusparseSpMM_bufferSize(p->handle, CUSPARSE_OPERATION_NON_TRANSPOSE,
+                                        CUSPARSE_OPERATION_NON_TRANSPOSE, &alpha, p->A, p->X, &beta,
+                                        p->Y, CUDA_R_32F, p->alg, &p->workspace_bytes));
+    if (p->workspace_bytes)
+        PB_CUDA(cudaMalloc(&p->workspace, p->workspace_bytes));
+    *out = p;
+    p = nullptr;  // released to the caller
+    return 0;
+}
+
+// Sampled product on the CSR pattern: val[k] = <A[row(k)], B[colIdx[k]]> (B given row-major
+// [n_cols, dim] and used transposed, as the reference does).
+PB_API int pspmm_baselines_sddmm_plan(void **out, const int32_t *rowPtr, const int32_t *colIdx,
+                                      float *val, const float *A, const float *B, int64_t n_rows,
+                                      int64_t n_cols, int64_t nnz, int32_t dim, int64_t ldA,
+                                      int64_t ldB)
+{
+    if (!out)
+        return -1;
+    Plan *p = new Plan();
+    struct Guard { Plan *&p; ~Guard() { if (p) plan_free(p); } } guard{p};
+    p->kind = 1;
+    PB_CUSPARSE(cusparseCreate(&p->handle));
+    PB_CUSPARSE(cusparseCreateCsr(&p->A, n_rows, n_cols, nnz, (void *)rowPtr, (void *)colIdx, val,
+                                  CUSPARSE_INDEX_32I, CUSPARSE_INDEX_32I, CUSPARSE_INDEX_BASE_ZERO,
+                                  CUDA_R_32F));
+    PB_CUSPARSE(cusparseCreateDnMat(&p->X, n_rows, dim, ldA, (void *)A, CUDA_R_32F, CUSPARSE_ORDER_ROW));
+    // B^T as a column-major [dim, n_cols] matrix with leading dimension ldB is the row-major B.
+    PB_CUSPARSE(cusparseCreateDnMat(&p->Y, dim, n_cols, ldB, (void *)B, CUDA_R_32F, CUSPARSE_ORDER_COL));
+    const float alpha = 1.f, beta = 0.f;
+    PB_CUSPARSE(cusparseSDDMM_bufferSize(p->handle, CUSPARSE_OPERATION_NON_TRANSPOSE,
+                                         CUSPARSE_OPERATION_NON_TRANSPOSE, &alpha, p->X, p->Y, &beta,
+                                         p->A, CUDA_R_32F, CUSPARSE_SDDMM_ALG_DEFAULT,
+                                         &p->workspace_bytes));
+    if (p->workspace_bytes)
+        PB_CUDA(cudaMalloc(&p->workspace, p->workspace_bytes));
+    PB_CUSPARSE(cusparseSDDMM_preprocess(p->handle, CUSPARSE_OPERATION_NON_TRANSPOSE,
+                                         CUSPARSE_OPERATION_NON_TRANSPOSE, &alpha, p->X, p->Y, &beta,
+                                         p->A, CUDA_R_32F, CUSPARSE_SDDMM_ALG_DEFAULT, p->workspace));
+    *out = p;
+    p = nullptr;
+    return 0;
+}
+
+PB_API int pspmm_baselines_run(void *plan, void *stream)
+{
+    Plan *p = (Plan *)plan;
+    if (!p)
+        return -1;
+    const float alpha = 1.f, beta = 0.f;
+    PB_CUSPARSE(cusparseSetStream(p->handle, (cudaStream_t)stream));
+    if (p->kind == 0)
+        PB_CUSPARSE(cusparseSpMM(p->handle, CUSPARSE_OPERATION_NON_TRANSPOSE,
+                                 CUSPARSE_OPERATION_NON_TRANSPOSE, &alpha, p->A, p->X, &beta, p->Y,
+                                 CUDA_R_32F, p->alg, p->workspace));
+    else
+        PB_CUSPARSE(cusparseSDDMM(p->handle, CUSPARSE_OPERATION_NON_TRANSPOSE,
+                                  CUSPARSE_OPERATION_NON_TRANSPOSE, &alpha, p->X, p->Y, &beta, p->A,
+                                  CUDA_R_32F, CUSPARSE_SDDMM_ALG_DEFAULT, p->workspace));
+    return 0;
+}

@@ -1,0 +1,173 @@
+"""SpMM-decider: picks the PCSR representation and kernel parameters for a matrix and a dim.
+
+Stands in for the reference's ``SpMMDecider`` (decider.py:18-93), which feeds 15 matrix
+statistics to a pickled random forest per dim and decodes the predicted class into
+``<if_split, vec_size, CF, blkWarpNum>``.  Here the choice comes from a measured table
+(``config_table.json`` next to this file) keyed on a bucket of the nnz-per-row distribution
+and on dim; the table's values are the parameters of the sm_100a kernels: vector width,
+lanes per row (= 32 / rows per warp), rows per lane group and PCSR partition length.  The
+legacy 4-tuple is still returned to callers that expect it; its CF / blkWarpNum members are
+valid values of the reference's domain and act only as hints.
+"""
+from __future__ import annotations
+
+import json
+import math
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+TABLE_PATH = os.path.join(_HERE, "config_table.json")
+
+
+def gap_calculator(dim, CF, warp_size=32):
+    """Idle lanes in the last column tile (same rule as PCSR.py:19-26 of the reference)."""
+    t_res = dim % (warp_size * CF)
+    return 0 if t_res == 0 else min(dim, CF * warp_size) - t_res
+
+
+def dynamic_CF_prompter(dim, CF_set=None, warp_size=32):
+    """Coarsening factors the reference considers valid for a dim (PCSR.py:30-42)."""
+    if CF_set is None:
+        CF_set = [1, 2, 3, 4, 5, 6, 7, 8]
+    CF_set = CF_set[: math.ceil(dim / 32)]
+    return [cf for cf in CF_set if gap_calculator(dim, cf, warp_size) < 32]
+
+
+def row_stats(rowPtr):
+    """nnz-per-row summary of a CSR row pointer (torch tensor or numpy array, any device)."""
+    import torch
+
+    rp = torch.as_tensor(rowPtr).long()
+    ln = (rp[1:] - rp[:-1]).double()
+    n = ln.numel()
+    if n == 0:
+        return {"n_rows": 0, "nnz": 0, "avg": 0.0, "cov": 0.0, "max": 0, "real_avg": 0.0}
+    nnz = int(rp[-1] - rp[0])
+    avg = nnz / n
+    nonempty = int((ln > 0).sum())
+    std = float(ln.std(unbiased=True)) if n > 1 else 0.0
+    real_avg = nnz / nonempty if nonempty and nonempty / n < 0.98 else avg
+    return {"n_rows": n, "nnz": nnz, "avg": avg, "cov": std / avg if avg else 0.0,
+            "max": int(ln.max()), "real_avg": real_avg}
+
+
+def regime(stats):
+    """Bucket of the nnz-per-row distribution: mean length class x skew class."""
+    avg = stats["avg"]
+    size = "short" if avg < 24 else ("medium" if avg < 128 else "long")
+    skew = "skewed" if (stats["cov"] > 0.75 or stats["max"] > 16 * max(avg, 1.0)) else "even"
+    return size + "_" + skew
+
+
+def auto_granularity(real_avg_degree):
+    """The reference's partition length: ceil(avg / 32) * 32 (graph_input.py:101)."""
+    return max(32, int(math.ceil(real_avg_degree / 32) * 32))
+
+
+_DEFAULT_TABLE = {"version": 1, "source": "built-in defaults (no measurements)", "entries": {}}
+_table = None
+
+
+def load_table(path=None):
+    global _table
+    p = path or TABLE_PATH
+    if os.path.exists(p):
+        with open(p) as f:
+            _table = json.load(f)
+    else:
+        _table = dict(_DEFAULT_TABLE)
+    return _table
+
+
+def table():
+    return _table if _table is not None else load_table()
+
+
+def _dim_key(dim):
+    return str(int(math.ceil(dim / 16) * 16)) if dim <= 256 else "256"
+
+
+class Plan(dict):
+    """Chosen representation and kernel parameters.
+
+    Keys: if_split (0/1), vec_size (1/2), granularity (partition length or None = the
+    reference's rule), and kernel fields lanes_per_row / vec_width / cta_threads /
+    rows_per_group (0 = library default).
+    """
+
+    def kernel_cfg(self):
+        return {k: int(self.get(k, 0) or 0)
+                for k in ("lanes_per_row", "vec_width", "cta_threads", "rows_per_group")}
+
+
+def choose(stats, dim, op="spmm"):
+    """Table lookup (regime x dim); falls back to a rule when the table has no entry."""
+    reg = regime(stats)
+    ent = table().get("entries", {}).get(op, {}).get(reg, {})
+    e = ent.get(_dim_key(dim)) or ent.get("*")
+    if e is None:
+        e = {"if_split": 1 if reg.endswith("skewed") else 0, "vec_size": 1}
+    plan = Plan(if_split=0, vec_size=1, granularity=None, lanes_per_row=0, vec_width=0, cta_threads=0,
+                rows_per_group=0)
+    plan.update(e)
+    plan["regime"] = reg
+    if plan["if_split"] and not plan.get("granularity"):
+        plan["granularity"] = auto_granularity(stats["real_avg"])
+    return plan
+
+
+def legacy_tuple(plan, dim):
+    """<if_split, vec_size, CF, blkWarpNum> in the reference's domain (decider.py:63-80)."""
+    cfs = dynamic_CF_prompter(int(math.ceil(dim / 16) * 16))
+    return int(plan["if_split"]), int(plan["vec_size"]), cfs[-1], 8
+
+
+class SpMMDecider(object):
+    """Same surface as the reference's class (decider.py:18-93).  ``pickle_path`` is accepted
+    for compatibility; a path to a JSON table may be given instead and is loaded."""
+
+    def __init__(self, pickle_path=None):
+        self.pickle_path = pickle_path
+        self.model_dict = {}
+        if pickle_path and str(pickle_path).endswith(".json"):
+            load_table(pickle_path)
+
+    def gen_model_dict(self, dim_list):
+        if dim_list is None or len(dim_list) == 0:
+            raise ValueError("dim_list must be assigned and non-empty")
+        self.model_dict = {d: table() for d in dim_list}
+
+    def decode_tree(self, code, dim, vec_size_list=(1, 2), warpNum_list=(4, 8)):
+        if_split = code % 2
+        cf_list = dynamic_CF_prompter(dim)
+        nv = len(vec_size_list)
+        vec_size = vec_size_list[code // 2 % nv]
+        CF = cf_list[code // (nv * 2) % len(cf_list)]
+        W = warpNum_list[code // (len(cf_list) * nv * 2)]
+        return if_split, vec_size, CF, W
+
+    def plan(self, graph, dim):
+        stats = row_stats(graph.csr_data.rowPtr)
+        return choose(stats, dim)
+
+    def config_PCSR(self, graph, dim):
+        if dim not in self.model_dict:
+            raise ValueError("dim-" + str(dim) + " not found in model_dict")
+        return legacy_tuple(self.plan(graph, dim), dim)
+
+
+def install_tuner():
+    """Route the table's kernel parameters into the torch-level operators: every call made
+    through the legacy signatures then picks lanes per row / rows per group from the table,
+    keyed on dim and on the mean entries per (split-)row, which the call's tensor shapes give
+    without touching the device."""
+    from . import ops
+
+    def tuner(op, dim, mean_len, V, split):
+        size = "short" if mean_len < 24 else ("medium" if mean_len < 128 else "long")
+        ent = table().get("entries", {}).get(op, {})
+        e = (ent.get(size + "_even", {}) or {}).get(_dim_key(dim)) or {}
+        return {k: int(e.get(k, 0) or 0) for k in ("lanes_per_row", "vec_width", "cta_threads", "rows_per_group")}
+
+    ops.tuner = tuner
+    return tuner

@@ -1,0 +1,439 @@
+"""Torch-tensor level operators over libpspmm's C ABI.
+
+These functions keep the positional signatures, return types and error behaviour of the
+reference's three pybind extension modules (``ParamSpMM``: SpMM/SpMM.cpp:891-926,
+``ParamSDDMM``: SDDMM/sddmm.cpp:675-701, ``ParamSpCONV``: SpCONV/SpCONV.cpp:496-512); the
+modules under ``paramspmm_ae_b200/dropin`` re-export them under the reference's names.
+
+torch is plumbing here: it owns device memory and the current stream.  All arithmetic on
+the sparse path runs in libpspmm's CUDA kernels; a missing library or a non-CUDA tensor is
+an error, never a reason to fall back to a torch implementation.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _lib
+from ._lib import check, lib, make_cfg
+
+PROFILE_ITERS = 200   # SpMM/SpMM.h:12 (PROFILE)
+PROFILE_WARMUP = 20
+
+
+# ----------------------------------------------------------------------------- argument checks
+def _check_cuda(t, name, dtype=None, ndim=None):
+    if not isinstance(t, torch.Tensor):
+        raise RuntimeError("%s must be a tensor" % name)
+    if not t.is_cuda:
+        raise RuntimeError("%s must be a CUDA tensor" % name)
+    if not t.is_contiguous():
+        raise RuntimeError("%s must be contiguous" % name)
+    if dtype is not None and t.dtype != dtype:
+        raise RuntimeError("%s must have dtype %s, got %s" % (name, dtype, t.dtype))
+    if ndim is not None and t.dim() != ndim:
+        raise RuntimeError("%s must be %d-dimensional" % (name, ndim))
+
+
+def _check_cpu(t, name, dtype=torch.int32):
+    if not isinstance(t, torch.Tensor) or t.is_cuda:
+        raise RuntimeError("%s must be a CPU tensor" % name)
+    if not t.is_contiguous():
+        raise RuntimeError("%s must be contiguous" % name)
+    if t.dtype != dtype:
+        raise RuntimeError("%s must have dtype %s, got %s" % (name, dtype, t.dtype))
+
+
+def _check_legacy(CF, blkWarpNum, max_cf=8):
+    # Same domain the reference enforces with TORCH_CHECK (SpMM/SpMM.cpp:110,139).
+    if blkWarpNum not in (4, 8):
+        raise RuntimeError("blkWarpNum must be 4 or 8")
+    if not (isinstance(CF, int) and 1 <= CF <= max_cf):
+        raise RuntimeError("CF must be an integer in 1..%d" % max_cf)
+
+
+def _ptr(t):
+    return ctypes.c_void_p(t.data_ptr() if t is not None else 0)
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+# Kernel parameters chosen per call.  `tuner` (set by paramspmm_ae_b200.decider) maps
+# (op, dim, mean entries per segment, V, split) to the non-legacy fields of pspmm_cfg.
+tuner = None
+
+
+def _cfg(op, CF, W, dim, n_entries, n_seg, V, split):
+    kw = {}
+    if tuner is not None:
+        kw = tuner(op, dim, (n_entries / n_seg) if n_seg else 0.0, V, split) or {}
+    return make_cfg(CF=CF, blkWarpNum=W, **kw)
+
+
+# ----------------------------------------------------------------------------- host builders
+def split_csr(rowPtr, granularity):
+    """PCSR partition of a CPU int32 rowPtr -> [rowPtr_split, target_row] (SpMM/SpMM.cpp:15-40)."""
+    _check_cpu(rowPtr, "rowPtr")
+    n = rowPtr.shape[0] - 1
+    nseg = ctypes.c_int64(0)
+    check(lib().pspmm_split_count(_ptr(rowPtr), n, int(granularity), ctypes.byref(nseg)))
+    rps = torch.empty(nseg.value + 1, dtype=torch.int32)
+    tr = torch.empty(nseg.value, dtype=torch.int32)
+    check(lib().pspmm_split_csr(_ptr(rowPtr), n, int(granularity), _ptr(rps), _ptr(tr), nseg.value))
+    return [rps, tr]
+
+
+def split_csr_par(rowPtr, row_split_offset, granularity):
+    """Same result as :func:`split_csr` (SpMM/SpMM.cpp:42-75).
+
+    The reference takes per-row piece offsets computed by the caller through an fp32
+    cumulative sum; they are validated for type only and recomputed here with 64-bit integer
+    arithmetic, which agrees with them wherever the fp32 sum was exact.
+    """
+    _check_cpu(row_split_offset, "row_split_offset")
+    if row_split_offset.shape[0] != rowPtr.shape[0]:
+        raise RuntimeError("row_split_offset must have as many entries as rowPtr")
+    return split_csr(rowPtr, granularity)
+
+
+def bcsr_from_csr(rowPtr, colIdx, val, n_cols, V=2):
+    """CSR (CPU tensors) -> V x 1 block CSR laid out as scipy's tobsr((V,1)) does
+    (what graph_input.py:245-266 of the reference builds)."""
+    _check_cpu(rowPtr, "rowPtr")
+    _check_cpu(colIdx, "colIdx")
+    _check_cpu(val, "val", torch.float32)
+    n = rowPtr.shape[0] - 1
+    nbr = (n + V - 1) // V
+    rpb = torch.empty(nbr + 1, dtype=torch.int32)
+    nblk = ctypes.c_int64(0)
+    check(lib().pspmm_bcsr_count(_ptr(rowPtr), _ptr(colIdx), n, int(n_cols), V, _ptr(rpb),
+                                 ctypes.byref(nblk)))
+    cb = torch.empty(nblk.value, dtype=torch.int32)
+    vb = torch.empty((nblk.value, V), dtype=torch.float32)
+    check(lib().pspmm_bcsr_fill(_ptr(rowPtr), _ptr(colIdx), _ptr(val), n, int(n_cols), V, _ptr(rpb),
+                                _ptr(cb), _ptr(vb)))
+    return rpb, cb, vb
+
+
+# ----------------------------------------------------------------------------- SpMM
+def _spmm_inputs(X, rowPtr, colIdx, val, target_row, V):
+    _check_cuda(X, "input", torch.float32, 2)
+    _check_cuda(rowPtr, "rowPtr", torch.int32, 1)
+    _check_cuda(colIdx, "colIdx", torch.int32, 1)
+    _check_cuda(val, "values", torch.float32, 1 if V == 1 else 2)
+    if V > 1 and val.shape[1] != V:
+        raise RuntimeError("values must have %d columns" % V)
+    if target_row is not None:
+        _check_cuda(target_row, "target_row", torch.int32, 1)
+        if target_row.shape[0] != rowPtr.shape[0] - 1:
+            raise RuntimeError("target_row must have one entry per split row")
+
+
+def spmm_into(out, X, rowPtr, colIdx, val, target_row=None, V=1, n_out_rows=None, CF=0, W=0,
+              cfg=None):
+    """Launch the SpMM into a caller-provided output (also used by the multi-GPU row shards).
+
+    ``n_out_rows`` counts (block-)rows of the output; it defaults to the number of segments
+    when there is no split and must be given for split layouts.
+    """
+    dim = X.shape[1]
+    n_seg = rowPtr.shape[0] - 1
+    split = target_row is not None
+    if n_out_rows is None:
+        if split:
+            raise RuntimeError("n_out_rows is required for split layouts")
+        n_out_rows = n_seg
+    nent = colIdx.shape[0]
+    if cfg is None:
+        cfg = _cfg("spmm", CF, W, dim, nent, n_seg, V, split)
+    seg_ptr = _ptr(rowPtr)
+    null = ctypes.c_void_p(0)
+    if V == 1:
+        check(lib().pspmm_spmm_csr(null if split else seg_ptr, _ptr(colIdx), _ptr(val), _ptr(X),
+                                   _ptr(out), n_out_rows, X.shape[0], nent, dim, X.stride(0),
+                                   out.stride(0), ctypes.byref(cfg), seg_ptr if split else null,
+                                   _ptr(target_row) if split else null, n_seg if split else 0,
+                                   _stream()))
+    else:
+        check(lib().pspmm_spmm_bcsr(null if split else seg_ptr, _ptr(colIdx), _ptr(val), V, _ptr(X),
+                                    _ptr(out), n_out_rows, X.shape[0], nent, dim, X.stride(0),
+                                    out.stride(0), ctypes.byref(cfg), seg_ptr if split else null,
+                                    _ptr(target_row) if split else null, n_seg if split else 0,
+                                    _stream()))
+    return out
+
+
+def _spmm(X, rowPtr, colIdx, val, target_row, V, CF, W):
+    _check_legacy(CF, W)
+    _spmm_inputs(X, rowPtr, colIdx, val, target_row, V)
+    n, dim = X.shape
+    if V == 1:
+        # The reference returns zeros_like(input): one output row per input row.
+        n_out = n
+        out = torch.empty((n, dim), dtype=torch.float32, device=X.device)
+        if target_row is None and rowPtr.shape[0] - 1 != n:
+            raise RuntimeError("rowPtr must have input.size(0)+1 entries")
+    else:
+        padded = (n + V - 1) // V * V  # SpMM/SpMM_kernel.cu:281-282, 427-428
+        n_out = padded // V
+        if target_row is None and rowPtr.shape[0] - 1 != n_out:
+            raise RuntimeError("rowPtr must describe ceil(input.size(0)/%d) block rows" % V)
+        out = torch.empty((padded, dim), dtype=torch.float32, device=X.device)
+    return spmm_into(out, X, rowPtr, colIdx, val, target_row, V, n_out, CF, W)
+
+
+def csr_spmm(X, rowPtr, colIdx, val, CF, blkWarpNum):
+    return _spmm(X, rowPtr, colIdx, val, None, 1, CF, blkWarpNum)
+
+
+def csr_split_spmm(X, rowPtr_split, colIdx, val, target_row, CF, blkWarpNum):
+    return _spmm(X, rowPtr_split, colIdx, val, target_row, 1, CF, blkWarpNum)
+
+
+def bcsr_spmm(X, rowPtr_bcsr, colIdx, val, CF, blkWarpNum):
+    return _spmm(X, rowPtr_bcsr, colIdx, val, None, 2, CF, blkWarpNum)
+
+
+def bcsr_split_spmm(X, rowPtr_bcsr_split, colIdx, val, target_row, CF, blkWarpNum):
+    return _spmm(X, rowPtr_bcsr_split, colIdx, val, target_row, 2, CF, blkWarpNum)
+
+
+def _vec_size(val):
+    if val.dim() != 2 or val.shape[1] != 3:
+        raise RuntimeError("vec_size must be 3")  # SpMM/SpMM.cpp:352,406
+    return 3
+
+
+def vec_spmm(X, rowPtr_bcsr, colIdx, val, CF, blkWarpNum):
+    return _spmm(X, rowPtr_bcsr, colIdx, val, None, _vec_size(val), CF, blkWarpNum)
+
+
+def vec_split_spmm(X, rowPtr_bcsr_split, colIdx, val, target_row, CF, blkWarpNum):
+    return _spmm(X, rowPtr_bcsr_split, colIdx, val, target_row, _vec_size(val), CF, blkWarpNum)
+
+
+def spmm_time_ms(X, rowPtr, colIdx, val, target_row=None, V=1, CF=0, W=0, cfg=None,
+                 warmup=PROFILE_WARMUP, iters=PROFILE_ITERS, out=None):
+    """Mean milliseconds per launch over `iters` back-to-back launches (CUDA events)."""
+    _spmm_inputs(X, rowPtr, colIdx, val, target_row, V)
+    n, dim = X.shape
+    n_seg = rowPtr.shape[0] - 1
+    split = target_row is not None
+    n_out = (n + V - 1) // V
+    if out is None:
+        out = torch.empty((n_out * V, dim), dtype=torch.float32, device=X.device)
+    nent = colIdx.shape[0]
+    if cfg is None:
+        cfg = _cfg("spmm", CF, W, dim, nent, n_seg, V, split)
+    ms = ctypes.c_float(0.0)
+    null = ctypes.c_void_p(0)
+    check(lib().pspmm_profile_spmm(null if split else _ptr(rowPtr), _ptr(colIdx), _ptr(val), V,
+                                   _ptr(X), _ptr(out), n_out, n, nent, dim, X.stride(0),
+                                   out.stride(0), ctypes.byref(cfg),
+                                   _ptr(rowPtr) if split else null,
+                                   _ptr(target_row) if split else null, n_seg if split else 0,
+                                   warmup, iters, ctypes.byref(ms), _stream()))
+    return ms.value
+
+
+def _gflops(nnz, dim, ms):
+    # int(2*nnz*dim / 1e6 / ms), the figure the reference's *_profile functions return
+    # (SpMM/SpMM_kernel.cu:645-656).
+    return int(nnz / 1e6 * dim * 2 / ms)
+
+
+def csr_spmm_profile(X, rowPtr, colIdx, val, CF, blkWarpNum):
+    _check_legacy(CF, blkWarpNum)
+    return _gflops(colIdx.shape[0], X.shape[1], spmm_time_ms(X, rowPtr, colIdx, val, None, 1, CF, blkWarpNum))
+
+
+def csr_split_spmm_profile(X, rowPtr_split, colIdx, val, target_row, CF, blkWarpNum):
+    _check_legacy(CF, blkWarpNum)
+    return _gflops(colIdx.shape[0], X.shape[1],
+                   spmm_time_ms(X, rowPtr_split, colIdx, val, target_row, 1, CF, blkWarpNum))
+
+
+def bcsr_spmm_profile(X, rowPtr, colIdx, val, nnz, CF, blkWarpNum):
+    _check_legacy(CF, blkWarpNum)
+    return _gflops(nnz, X.shape[1], spmm_time_ms(X, rowPtr, colIdx, val, None, 2, CF, blkWarpNum))
+
+
+def bcsr_split_spmm_profile(X, rowPtr, colIdx, val, target_row, nnz, CF, blkWarpNum):
+    _check_legacy(CF, blkWarpNum)
+    return _gflops(nnz, X.shape[1], spmm_time_ms(X, rowPtr, colIdx, val, target_row, 2, CF, blkWarpNum))
+
+
+def vec_spmm_profile(X, rowPtr, colIdx, val, nnz, CF, blkWarpNum):
+    _check_legacy(CF, blkWarpNum)
+    return _gflops(nnz, X.shape[1],
+                   spmm_time_ms(X, rowPtr, colIdx, val, None, _vec_size(val), CF, blkWarpNum))
+
+
+def vec_split_spmm_profile(X, rowPtr, colIdx, val, target_row, nnz, CF, blkWarpNum):
+    _check_legacy(CF, blkWarpNum)
+    return _gflops(nnz, X.shape[1],
+                   spmm_time_ms(X, rowPtr, colIdx, val, target_row, _vec_size(val), CF, blkWarpNum))
+
+
+# ----------------------------------------------------------------------------- SDDMM
+def _sddmm(A, B, rowPtr, colIdx, val, target_row, V, CF, W, time_only=False):
+    _check_legacy(CF, W, max_cf=4)  # SDDMM/sddmm.cpp:31-43
+    _check_cuda(A, "A", torch.float32, 2)
+    _check_cuda(B, "B", torch.float32, 2)
+    _check_cuda(rowPtr, "rowPtr", torch.int32, 1)
+    _check_cuda(colIdx, "colIdx", torch.int32, 1)
+    _check_cuda(val, "values", torch.float32, 1 if V == 1 else 2)
+    if A.shape[1] != B.shape[1]:
+        raise RuntimeError("A and B must have the same number of columns")
+    split = target_row is not None
+    if split:
+        _check_cuda(target_row, "target_row", torch.int32, 1)
+    dim = A.shape[1]
+    n_seg = rowPtr.shape[0] - 1
+    nent = colIdx.shape[0]
+    out = torch.empty_like(val)
+    cfg = _cfg("sddmm", CF, W, dim, nent, n_seg, V, split)
+    null = ctypes.c_void_p(0)
+    n_rows = n_seg if not split else (A.shape[0] // V)
+    args_tail = (ctypes.byref(cfg), _ptr(rowPtr) if split else null,
+                 _ptr(target_row) if split else null, n_seg if split else 0)
+    if time_only:
+        ms = ctypes.c_float(0.0)
+        check(lib().pspmm_profile_sddmm(null if split else _ptr(rowPtr), _ptr(colIdx), _ptr(val), V,
+                                        _ptr(A), _ptr(B), _ptr(out), n_rows, nent, dim, A.stride(0),
+                                        B.stride(0), *args_tail, PROFILE_WARMUP, PROFILE_ITERS,
+                                        ctypes.byref(ms), _stream()))
+        return ms.value
+    if V == 1:
+        check(lib().pspmm_sddmm_csr(null if split else _ptr(rowPtr), _ptr(colIdx), _ptr(A), _ptr(B),
+                                    _ptr(out), n_rows, nent, dim, A.stride(0), B.stride(0),
+                                    *args_tail, _stream()))
+    else:
+        check(lib().pspmm_sddmm_bcsr(null if split else _ptr(rowPtr), _ptr(colIdx), _ptr(val), V,
+                                     _ptr(A), _ptr(B), _ptr(out), n_rows, nent, dim, A.stride(0),
+                                     B.stride(0), *args_tail, _stream()))
+    return out
+
+
+def csr_sddmm(A, B, rowPtr, colIdx, val, CF, blkWarpNum):
+    return _sddmm(A, B, rowPtr, colIdx, val, None, 1, CF, blkWarpNum)
+
+
+def csr_split_sddmm(A, B, rowPtr_split, colIdx, val, target_row, CF, blkWarpNum):
+    return _sddmm(A, B, rowPtr_split, colIdx, val, target_row, 1, CF, blkWarpNum)
+
+
+def bcsr_sddmm(A, B, rowPtr, colIdx, val, CF, blkWarpNum):
+    return _sddmm(A, B, rowPtr, colIdx, val, None, 2, CF, blkWarpNum)
+
+
+def bcsr_split_sddmm(A, B, rowPtr_split, colIdx, val, target_row, CF, blkWarpNum):
+    return _sddmm(A, B, rowPtr_split, colIdx, val, target_row, 2, CF, blkWarpNum)
+
+
+def vec_sddmm(A, B, rowPtr, colIdx, val, CF, blkWarpNum):
+    return _sddmm(A, B, rowPtr, colIdx, val, None, _vec_size(val), CF, blkWarpNum)
+
+
+def vec_split_sddmm(A, B, rowPtr_split, colIdx, val, target_row, CF, blkWarpNum):
+    return _sddmm(A, B, rowPtr_split, colIdx, val, target_row, _vec_size(val), CF, blkWarpNum)
+
+
+def csr_sddmm_profile(A, B, rowPtr, colIdx, val, CF, blkWarpNum):
+    return _gflops(colIdx.shape[0], A.shape[1], _sddmm(A, B, rowPtr, colIdx, val, None, 1, CF, blkWarpNum, True))
+
+
+def csr_split_sddmm_profile(A, B, rowPtr_split, colIdx, val, target_row, CF, blkWarpNum):
+    return _gflops(colIdx.shape[0], A.shape[1],
+                   _sddmm(A, B, rowPtr_split, colIdx, val, target_row, 1, CF, blkWarpNum, True))
+
+
+def bcsr_sddmm_profile(A, B, rowPtr, colIdx, val, nnz, CF, blkWarpNum):
+    return _gflops(nnz, A.shape[1], _sddmm(A, B, rowPtr, colIdx, val, None, 2, CF, blkWarpNum, True))
+
+
+def bcsr_split_sddmm_profile(A, B, rowPtr_split, colIdx, val, target_row, nnz, CF, blkWarpNum):
+    return _gflops(nnz, A.shape[1],
+                   _sddmm(A, B, rowPtr_split, colIdx, val, target_row, 2, CF, blkWarpNum, True))
+
+
+def vec_sddmm_profile(A, B, rowPtr, colIdx, val, nnz, CF, blkWarpNum):
+    return _gflops(nnz, A.shape[1],
+                   _sddmm(A, B, rowPtr, colIdx, val, None, _vec_size(val), CF, blkWarpNum, True))
+
+
+def vec_split_sddmm_profile(A, B, rowPtr_split, colIdx, val, target_row, nnz, CF, blkWarpNum):
+    return _gflops(nnz, A.shape[1],
+                   _sddmm(A, B, rowPtr_split, colIdx, val, target_row, _vec_size(val), CF, blkWarpNum, True))
+
+
+def genmask(rowPtr_bcsr, rowPtr, blkval, nnz):
+    """int32[nnz] map from CSR entry order to the flattened [nblk,2] block values
+    (SDDMM/sddmm.cpp:663-673)."""
+    _check_cuda(rowPtr_bcsr, "rowPtr_bcsr", torch.int32, 1)
+    _check_cuda(rowPtr, "rowPtr", torch.int32, 1)
+    _check_cuda(blkval, "blkval", torch.float32, 2)
+    if blkval.shape[1] != 2:
+        raise RuntimeError("blkval must be [nblk, 2]")
+    mask = torch.empty(int(nnz), dtype=torch.int32, device=rowPtr.device)
+    check(lib().pspmm_genmask(_ptr(rowPtr_bcsr), _ptr(rowPtr), _ptr(blkval),
+                              rowPtr_bcsr.shape[0] - 1, rowPtr.shape[0] - 1, int(nnz), _ptr(mask),
+                              _stream()))
+    return mask
+
+
+# ----------------------------------------------------------------------------- GCN layer (SpCONV)
+def _conv_forward(V, H, weight, rowPtr, colIdx, val, target_row, CF, W):
+    """A @ (H @ W): dense GEMM (cuBLAS through torch.mm) then SpMM (SpCONV/SpCONV.h:43-193)."""
+    _check_legacy(CF, W, max_cf=4)  # SpCONV/SpCONV.cpp:93-104
+    HW = torch.mm(H, weight)
+    n = HW.shape[0]
+    out = _spmm(HW, rowPtr, colIdx, val, target_row, V, CF, W)
+    return out[:n] if out.shape[0] != n else out  # block variants slice back (SpCONV.h:115-118)
+
+
+def _conv_backward(V, g_out, H, weight, rowPtr, colIdx, val, target_row, CF, W):
+    """AG = A @ g_out (A itself, the normalised adjacency is symmetric); dH = AG @ W^T;
+    dW = H^T @ AG (SpCONV/SpCONV.h:57-72)."""
+    _check_legacy(CF, W, max_cf=4)
+    g_out = g_out.contiguous()
+    n = g_out.shape[0]
+    AG = _spmm(g_out, rowPtr, colIdx, val, target_row, V, CF, W)
+    if AG.shape[0] != n:
+        AG = AG[:n]
+    return [torch.mm(AG, weight.t()), torch.mm(H.t(), AG)]
+
+
+def csr_spmm_forward(H, weight, rowPtr, colIdx, val, CF, blkWarpNum):
+    return _conv_forward(1, H, weight, rowPtr, colIdx, val, None, CF, blkWarpNum)
+
+
+def csr_spmm_backward(g_out, H, weight, rowPtr, colIdx, val, CF, blkWarpNum):
+    return _conv_backward(1, g_out, H, weight, rowPtr, colIdx, val, None, CF, blkWarpNum)
+
+
+def csr_split_spmm_forward(H, weight, rowPtr_split, colIdx, val, target_row, CF, blkWarpNum):
+    return _conv_forward(1, H, weight, rowPtr_split, colIdx, val, target_row, CF, blkWarpNum)
+
+
+def csr_split_spmm_backward(g_out, H, weight, rowPtr_split, colIdx, val, target_row, CF, blkWarpNum):
+    return _conv_backward(1, g_out, H, weight, rowPtr_split, colIdx, val, target_row, CF, blkWarpNum)
+
+
+def bcsr_spmm_forward(H, weight, rowPtr, colIdx, val, CF, blkWarpNum):
+    return _conv_forward(2, H, weight, rowPtr, colIdx, val, None, CF, blkWarpNum)
+
+
+def bcsr_spmm_backward(g_out, H, weight, rowPtr, colIdx, val, CF, blkWarpNum):
+    return _conv_backward(2, g_out, H, weight, rowPtr, colIdx, val, None, CF, blkWarpNum)
+
+
+def bcsr_split_spmm_forward(H, weight, rowPtr_split, colIdx, val, target_row, CF, blkWarpNum):
+    return _conv_forward(2, H, weight, rowPtr_split, colIdx, val, target_row, CF, blkWarpNum)
+
+
+def bcsr_split_spmm_backward(g_out, H, weight, rowPtr_split, colIdx, val, target_row, CF, blkWarpNum):
+    return _conv_backward(2, g_out, H, weight, rowPtr_split, colIdx, val, target_row, CF, blkWarpNum)

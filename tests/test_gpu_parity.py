@@ -1,0 +1,332 @@
+"""GPU parity tests: the CUDA kernels, called through the C ABI (ctypes), against the CPU oracle.
+
+Tolerance for floating-point results: |got - want| <= 1e-4 + 1e-5 * |want| (max relative error
+1e-5 with an absolute floor of 1e-4), the bound the project states for fp32 outputs.  Index
+arrays must match bit for bit.
+"""
+import ctypes
+import os
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+RTOL, ATOL = 1e-5, 1e-4
+
+
+def close(got, want):
+    got = got.detach().cpu().numpy() if isinstance(got, torch.Tensor) else np.asarray(got)
+    np.testing.assert_allclose(got, np.asarray(want), rtol=RTOL, atol=ATOL)
+
+
+@pytest.fixture(scope="module")
+def dev():
+    assert torch.cuda.is_available(), "these tests need a CUDA device"
+    from paramspmm_ae_b200 import _lib
+    _lib.lib()  # fails loudly when the CUDA library has not been built
+    return torch.device("cuda:0")
+
+
+@pytest.fixture(scope="module")
+def mats():
+    """Small seeded matrices covering the row-length regimes, each with some empty rows."""
+    from paramspmm_ae_b200 import synth
+    out = {
+        "powerlaw": synth.powerlaw_graph(3001, 24000, seed=1),          # odd n, hub rows, self loops
+        "uniform16": synth.uniform_rows(2000, 16, seed=21),              # every row exactly 16
+        "banded": synth.banded_rows(1500, 16, 32, seed=22),
+        "rmat": synth.with_empty_rows(synth.rmat(12, 60000, seed=23), every=5),
+        "tiny": synth.uniform_rows(7, 3, seed=2),
+    }
+    # one matrix whose row 0 is far longer than any partition length
+    hub = synth.uniform_rows(1200, 4, seed=3)
+    rp = hub.rowPtr.clone().long()
+    g = torch.Generator().manual_seed(4)
+    extra_cols = torch.sort(torch.randperm(1200, generator=g)[:900]).values.int()
+    ci = torch.cat([extra_cols, hub.colIdx[4:]])
+    v = torch.cat([torch.rand(900, generator=g), hub.val[4:]])
+    rp[1:] += 900 - 4
+    out["hub"] = synth.CSR(rp.int(), ci, v, 1200, 1200)
+    return out
+
+
+def dense(n, dim, seed):
+    from paramspmm_ae_b200 import synth
+    return synth.dense_uniform(n, dim, seed)
+
+
+DIMS = [1, 3, 4, 8, 16, 20, 32, 47, 48, 64, 80, 100, 128, 160, 256, 260]
+
+
+@pytest.mark.parametrize("name", ["powerlaw", "uniform16", "banded", "rmat", "tiny", "hub"])
+def test_csr_spmm_matches_oracle(dev, oracle, mats, name):
+    from paramspmm_ae_b200 import ops
+    m = mats[name]
+    rp, ci, v = m.numpy()
+    d = m.to(dev)
+    for dim in DIMS:
+        B = dense(m.n_cols, dim, 100 + dim)
+        want = oracle.spmm_csr(rp, ci, v, B.numpy())
+        got = ops.csr_spmm(B.to(dev), d.rowPtr, d.colIdx, d.val, 1, 4)
+        assert got.shape == (m.n_rows, dim)
+        close(got, want)
+
+
+def test_csr_spmm_meets_the_reference_acceptance_rule(dev, oracle, mats):
+    """verification.py:79-102: no element may differ by more than 1e-4 relative from
+    torch.sparse.mm (computed here on the CPU)."""
+    from paramspmm_ae_b200 import ops
+    m = mats["uniform16"]
+    rp, ci, v = m.numpy()
+    d = m.to(dev)
+    B = torch.ones(m.n_cols, 32)  # the operand the reference itself verifies with
+    ref = oracle.spmm_torch_cpu(rp, ci, v, B.numpy())
+    got = ops.csr_spmm(B.to(dev), d.rowPtr, d.colIdx, d.val, 1, 8).cpu().numpy()
+    assert oracle.verification_compare(ref, got, rel=1e-4)
+
+
+def test_golden_spmm_fixture(dev, golden_dir):
+    from paramspmm_ae_b200 import ops
+    z = np.load(os.path.join(golden_dir, "spmm_torch.npz"))
+    t = lambda k: torch.from_numpy(z[k]).to(dev)
+    got = ops.csr_spmm(t("B"), t("rowPtr"), t("colIdx"), t("val"), 1, 4)
+    close(got, z["C_torch"])
+    close(got, z["C_scipy"])
+
+
+@pytest.mark.parametrize("name", ["powerlaw", "rmat", "hub", "uniform16"])
+@pytest.mark.parametrize("gran", [1, 7, 32, 512])
+def test_csr_split_spmm_matches_oracle(dev, oracle, mats, name, gran):
+    from paramspmm_ae_b200 import ops
+    m = mats[name]
+    rp, ci, v = m.numpy()
+    rps, tr = ops.split_csr(m.rowPtr, gran)
+    o_rps, o_tr = oracle.split_csr(rp, gran)
+    assert np.array_equal(rps.numpy(), o_rps) and np.array_equal(tr.numpy(), o_tr)
+    d = m.to(dev)
+    for dim in (4, 16, 47, 64, 100, 128, 256):
+        B = dense(m.n_cols, dim, 200 + dim)
+        want = oracle.spmm_csr_split(o_rps, o_tr, ci, v, B.numpy(), m.n_rows)
+        got = ops.csr_split_spmm(B.to(dev), rps.to(dev), d.colIdx, d.val, tr.to(dev), 1, 4)
+        close(got, want)
+        close(got, oracle.spmm_csr(rp, ci, v, B.numpy()))
+
+
+@pytest.mark.parametrize("V", [2, 3])
+@pytest.mark.parametrize("name", ["powerlaw", "rmat", "tiny", "hub"])
+def test_block_spmm_matches_oracle(dev, oracle, mats, name, V):
+    from paramspmm_ae_b200 import ops
+    m = mats[name]
+    rp, ci, v = m.numpy()
+    rpb, cb, vb = ops.bcsr_from_csr(m.rowPtr, m.colIdx, m.val, m.n_cols, V)
+    o = oracle.bcsr_build(rp, ci, v, m.n_cols, V)
+    assert np.array_equal(rpb.numpy(), o[0]) and np.array_equal(cb.numpy(), o[1])
+    assert np.array_equal(vb.numpy(), o[2])
+    nbr = rpb.shape[0] - 1
+    fn = ops.bcsr_spmm if V == 2 else ops.vec_spmm
+    fn_split = ops.bcsr_split_spmm if V == 2 else ops.vec_split_spmm
+    s_rpb, s_tr = ops.split_csr(rpb, 8)
+    for dim in (4, 16, 47, 64, 96, 128, 256):
+        B = dense(m.n_cols, dim, 300 + dim)
+        want = oracle.spmm_bcsr(o[0], o[1], o[2], B.numpy(), nbr)
+        got = fn(B.to(dev), rpb.to(dev), cb.to(dev), vb.to(dev), 1, 4)
+        assert got.shape == (nbr * V, dim)  # rows padded to a multiple of V
+        close(got, want)
+        close(got[: m.n_rows], oracle.spmm_csr(rp, ci, v, B.numpy()))
+        got = fn_split(B.to(dev), s_rpb.to(dev), cb.to(dev), vb.to(dev), s_tr.to(dev), 2, 8)
+        close(got, want)
+
+
+def test_spmm_explicit_configs(dev, oracle, mats):
+    """Every kernel parameter the configuration table can choose gives the same product."""
+    from paramspmm_ae_b200 import _lib, ops
+    m = mats["rmat"]
+    rp, ci, v = m.numpy()
+    d = m.to(dev)
+    rps, tr = ops.split_csr(m.rowPtr, 32)
+    rps, tr = rps.to(dev), tr.to(dev)
+    for dim in (16, 64, 96, 128, 256):
+        B = dense(m.n_cols, dim, 400 + dim)
+        want = oracle.spmm_csr(rp, ci, v, B.numpy())
+        Bd = B.to(dev)
+        for lpr in (2, 4, 8, 16, 32):
+            for vw in (1, 2, 4):
+                for thr, rpg in ((128, 1), (256, 4), (512, 8)):
+                    cfg = _lib.make_cfg(lanes_per_row=lpr, vec_width=vw, cta_threads=thr, rows_per_group=rpg)
+                    out = torch.full((m.n_rows, dim), float("nan"), device=dev)
+                    ops.spmm_into(out, Bd, d.rowPtr, d.colIdx, d.val, cfg=cfg)
+                    close(out, want)
+                    out = torch.full((m.n_rows, dim), float("nan"), device=dev)
+                    ops.spmm_into(out, Bd, rps, d.colIdx, d.val, target_row=tr, n_out_rows=m.n_rows, cfg=cfg)
+                    close(out, want)
+
+
+def test_spmm_strided_operands_and_row_shards(dev, oracle, mats):
+    """Leading dimensions larger than dim, and an output with fewer rows than B (a row shard)."""
+    from paramspmm_ae_b200 import ops
+    m = mats["powerlaw"]
+    rp, ci, v = m.numpy()
+    d = m.to(dev)
+    for dim, ld in ((64, 96), (47, 50), (20, 22)):
+        wide = dense(m.n_cols, ld, 500 + dim)
+        B = wide[:, :dim]
+        want = oracle.spmm_csr(rp, ci, v, np.ascontiguousarray(B.numpy()))
+        Bd = wide.to(dev)[:, :dim]
+        out_wide = torch.zeros(m.n_rows, ld, device=dev)
+        ops.spmm_into(out_wide[:, :dim], Bd, d.rowPtr, d.colIdx, d.val)
+        close(out_wide[:, :dim], want)
+        assert not out_wide[:, dim:].any()  # nothing written past dim
+    # rows [lo, hi) of A as a shard with re-based row pointers and global column ids
+    lo, hi = 700, 1900
+    rp_s = (m.rowPtr[lo: hi + 1] - m.rowPtr[lo]).contiguous()
+    a, b = int(m.rowPtr[lo]), int(m.rowPtr[hi])
+    B = dense(m.n_cols, 64, 77)
+    want = oracle.spmm_csr(rp, ci, v, B.numpy())[lo:hi]
+    out = torch.empty(hi - lo, 64, device=dev)
+    ops.spmm_into(out, B.to(dev), rp_s.to(dev), d.colIdx[a:b].contiguous(), d.val[a:b].contiguous())
+    close(out, want)
+
+
+def test_spmm_empty_inputs(dev):
+    from paramspmm_ae_b200 import ops
+    X = torch.randn(5, 16, device=dev)
+    rp = torch.zeros(6, dtype=torch.int32, device=dev)
+    e_i = torch.zeros(0, dtype=torch.int32, device=dev)
+    e_f = torch.zeros(0, device=dev)
+    out = ops.csr_spmm(X, rp, e_i, e_f, 1, 4)
+    assert out.shape == (5, 16) and not out.any()
+    out = ops.csr_split_spmm(X, torch.zeros(1, dtype=torch.int32, device=dev), e_i, e_f, e_i, 1, 4)
+    assert out.shape == (5, 16) and not out.any()
+
+
+@pytest.mark.parametrize("name", ["powerlaw", "rmat", "uniform16", "hub"])
+def test_csr_sddmm_matches_oracle(dev, oracle, mats, name):
+    from paramspmm_ae_b200 import ops
+    m = mats[name]
+    rp, ci, v = m.numpy()
+    d = m.to(dev)
+    rps, tr = ops.split_csr(m.rowPtr, 32)
+    for dim in (4, 16, 47, 64, 100, 128, 200, 1100):
+        A = dense(m.n_rows + 1, dim, 600 + dim)
+        B = dense(m.n_cols, dim, 700 + dim)
+        want = oracle.sddmm_csr(rp, ci, A.numpy(), B.numpy())
+        got = ops.csr_sddmm(A.to(dev), B.to(dev), d.rowPtr, d.colIdx, d.val, min(4, (dim + 31) // 32), 4)
+        assert got.shape == (m.nnz,)
+        close(got, want)
+        got = ops.csr_split_sddmm(A.to(dev), B.to(dev), rps.to(dev), d.colIdx, d.val, tr.to(dev),
+                                  min(4, (dim + 31) // 32), 8)
+        close(got, want)
+
+
+@pytest.mark.parametrize("V", [2, 3])
+def test_block_sddmm_matches_oracle(dev, oracle, mats, V):
+    from paramspmm_ae_b200 import ops
+    m = mats["powerlaw"]
+    rp, ci, v = m.numpy()
+    rpb, cb, vb = ops.bcsr_from_csr(m.rowPtr, m.colIdx, m.val, m.n_cols, V)
+    nbr = rpb.shape[0] - 1
+    s_rpb, s_tr = ops.split_csr(rpb, 16)
+    fn = ops.bcsr_sddmm if V == 2 else ops.vec_sddmm
+    fn_split = ops.bcsr_split_sddmm if V == 2 else ops.vec_split_sddmm
+    for dim in (16, 47, 64, 128):
+        A = dense(nbr * V, dim, 800 + dim)
+        B = dense(m.n_cols, dim, 900 + dim)
+        want = oracle.sddmm_bcsr(rpb.numpy(), cb.numpy(), vb.numpy(), A.numpy(), B.numpy())
+        got = fn(A.to(dev), B.to(dev), rpb.to(dev), cb.to(dev), vb.to(dev), min(4, (dim + 31) // 32), 4)
+        assert got.shape == (cb.shape[0], V)
+        close(got, want)
+        got = fn_split(A.to(dev), B.to(dev), s_rpb.to(dev), cb.to(dev), vb.to(dev), s_tr.to(dev),
+                       min(4, (dim + 31) // 32), 4)
+        close(got, want)
+
+
+@pytest.mark.parametrize("name", ["powerlaw", "rmat", "tiny", "hub"])
+def test_genmask_bit_exact(dev, oracle, mats, name):
+    from paramspmm_ae_b200 import ops
+    m = mats[name]
+    rp, ci, v = m.numpy()
+    rpb, cb, vb = ops.bcsr_from_csr(m.rowPtr, m.colIdx, m.val, m.n_cols, 2)
+    want = oracle.genmask(rpb.numpy(), rp, vb.numpy(), m.nnz)
+    got = ops.genmask(rpb.to(dev), m.rowPtr.to(dev), vb.to(dev), m.nnz)
+    assert got.dtype == torch.int32 and got.shape == (m.nnz,)
+    assert np.array_equal(got.cpu().numpy(), want)
+
+
+def test_profile_entry_points_return_gflops(dev, mats):
+    from paramspmm_ae_b200 import ops
+    m = mats["uniform16"].to(dev)
+    X = torch.ones(m.n_rows, 64, device=dev)
+    g = ops.csr_spmm_profile(X, m.rowPtr, m.colIdx, m.val, 2, 8)
+    assert isinstance(g, int) and g > 0
+    g = ops.csr_sddmm_profile(X, X, m.rowPtr, m.colIdx, m.val, 2, 8)
+    assert isinstance(g, int) and g > 0
+
+
+def test_spconv_forward_backward(dev, oracle, mats):
+    """GCN layer A(HW) and its gradients (SpCONV/SpCONV.h:43-72) against dense fp64 algebra."""
+    from paramspmm_ae_b200 import ops
+    m = mats["powerlaw"]  # symmetric: the backward pass multiplies by A, not A^T
+    rp, ci, v = m.numpy()
+    d = m.to(dev)
+    n = m.n_rows
+    H = dense(n, 40, 1)
+    W = dense(40, 24, 2)
+    G = dense(n, 24, 3)
+    HW = (H.double() @ W.double()).float().numpy()
+    want = oracle.spmm_csr(rp, ci, v, HW)
+    got = ops.csr_spmm_forward(H.to(dev), W.to(dev), d.rowPtr, d.colIdx, d.val, 1, 4)
+    np.testing.assert_allclose(got.cpu().numpy(), want, rtol=1e-4, atol=1e-4)
+    AG = oracle.spmm_csr(rp, ci, v, G.numpy()).astype(np.float64)
+    dH, dW = ops.csr_spmm_backward(G.to(dev), H.to(dev), W.to(dev), d.rowPtr, d.colIdx, d.val, 1, 4)
+    np.testing.assert_allclose(dH.cpu().numpy(), AG @ W.double().numpy().T, rtol=1e-4, atol=1e-4)
+    np.testing.assert_allclose(dW.cpu().numpy(), H.double().numpy().T @ AG, rtol=1e-4, atol=2e-3)
+    rpb, cb, vb = ops.bcsr_from_csr(m.rowPtr, m.colIdx, m.val, n, 2)
+    got = ops.bcsr_spmm_forward(H.to(dev), W.to(dev), rpb.to(dev), cb.to(dev), vb.to(dev), 1, 4)
+    assert got.shape == (n, 24)  # sliced back from the padded row count
+    np.testing.assert_allclose(got.cpu().numpy(), want, rtol=1e-4, atol=1e-4)
+
+
+def test_cusparse_comparators_agree(dev, oracle, mats):
+    from paramspmm_ae_b200 import baselines
+    m = mats["rmat"]
+    rp, ci, v = m.numpy()
+    d = m.to(dev)
+    B = dense(m.n_cols, 64, 5)
+    want = oracle.spmm_csr(rp, ci, v, B.numpy())
+    close(baselines.cusparse_compute(B.to(dev), d.rowPtr, d.colIdx, d.val), want)
+    close(baselines.cusparse_compute_csr_alg2(B.to(dev), d.rowPtr, d.colIdx, d.val), want)
+    A = dense(m.n_rows, 64, 6)
+    vals = d.val.clone()
+    baselines.cusparse_sddmm_compute(A.to(dev), B.to(dev), d.rowPtr, d.colIdx, vals)
+    close(vals, oracle.sddmm_csr(rp, ci, A.numpy(), B.numpy()))
+
+
+def test_full_size_properties(dev):
+    """At benchmark size (10^6 rows, 1.6*10^7 entries) the oracle is too slow; check properties:
+    A*ones equals the row sums of the values, the product is linear in B, split and plain
+    layouts agree, and the result matches cuSPARSE through torch.sparse.mm on the device."""
+    from paramspmm_ae_b200 import ops, synth
+    n, dim = 1_000_000, 64
+    m = synth.rmat(20, 16_000_000, n=n, seed=23, device=dev)
+    assert m.nnz == 16_000_000
+    ones = torch.ones(n, dim, device=dev)
+    got = ops.csr_spmm(ones, m.rowPtr, m.colIdx, m.val, 2, 8)
+    rows = torch.repeat_interleave(torch.arange(n, device=dev), (m.rowPtr[1:] - m.rowPtr[:-1]).long())
+    rowsum = torch.zeros(n, device=dev, dtype=torch.float64).index_add_(0, rows, m.val.double())
+    torch.testing.assert_close(got[:, 0].double(), rowsum, rtol=1e-5, atol=1e-4)
+    torch.testing.assert_close(got[:, dim - 1], got[:, 0], rtol=0, atol=0)
+    B1 = synth.dense_uniform(n, dim, 1, dev)
+    B2 = synth.dense_uniform(n, dim, 2, dev)
+    c1 = ops.csr_spmm(B1, m.rowPtr, m.colIdx, m.val, 2, 8)
+    c2 = ops.csr_spmm(B2, m.rowPtr, m.colIdx, m.val, 2, 8)
+    c12 = ops.csr_spmm(B1 + B2, m.rowPtr, m.colIdx, m.val, 2, 8)
+    # hub rows sum tens of thousands of terms: scale the absolute floor by the row's magnitude
+    scale = 1 + rowsum.max().item()
+    torch.testing.assert_close(c12, c1 + c2, rtol=1e-5, atol=1e-6 * scale * 50)
+    rps, tr = ops.split_csr(m.rowPtr.cpu(), 32)
+    cs = ops.csr_split_spmm(B1, rps.to(dev), m.colIdx, m.val, tr.to(dev), 2, 8)
+    torch.testing.assert_close(cs, c1, rtol=1e-5, atol=1e-6 * scale * 50)
+    s = torch.sparse_csr_tensor(m.rowPtr, m.colIdx, m.val, size=(n, n))
+    torch.testing.assert_close(torch.sparse.mm(s, B1), c1, rtol=1e-5, atol=1e-6 * scale * 50)
