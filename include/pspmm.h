@@ -51,8 +51,9 @@ extern "C" {
 typedef struct pspmm_cfg {
     int32_t lanes_per_row;   /* lanes that share one (split-)row: 1,2,4,8,16,32; rows per warp = 32 / this */
     int32_t vec_width;       /* floats per lane per load of a dense row: 1, 2 or 4 (128-bit) */
-    int32_t cta_threads;     /* 128, 256 or 512 */
-    int32_t rows_per_group;  /* consecutive (split-)rows a lane group walks before its CTA retires: 1..64 */
+    int32_t cta_threads;     /* 128 or 256 */
+    int32_t rows_per_group;  /* consecutive (split-)rows one lane group owns: 1..16 */
+    int32_t gather_batch;    /* 16-byte gathers a lane keeps in flight: 2, 4, 8 or 16 (registers vs occupancy) */
     int32_t hint_CF;         /* legacy coarsening factor, validated only */
     int32_t hint_blkWarpNum; /* legacy warps per block, validated only */
 } pspmm_cfg;

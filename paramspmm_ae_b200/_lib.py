@@ -28,7 +28,8 @@ class PspmmCfg(ctypes.Structure):
     """Mirror of ``pspmm_cfg``; zero fields mean "library's choice"."""
 
     _fields_ = [("lanes_per_row", _i32), ("vec_width", _i32), ("cta_threads", _i32),
-                ("rows_per_group", _i32), ("hint_CF", _i32), ("hint_blkWarpNum", _i32)]
+                ("rows_per_group", _i32), ("gather_batch", _i32), ("hint_CF", _i32),
+                ("hint_blkWarpNum", _i32)]
 
 
 class PspmmError(RuntimeError):
@@ -96,5 +97,6 @@ def check(code):
     raise PspmmError(code, text)
 
 
-def make_cfg(CF=0, blkWarpNum=0, lanes_per_row=0, vec_width=0, cta_threads=0, rows_per_group=0):
-    return PspmmCfg(lanes_per_row, vec_width, cta_threads, rows_per_group, CF, blkWarpNum)
+def make_cfg(CF=0, blkWarpNum=0, lanes_per_row=0, vec_width=0, cta_threads=0, rows_per_group=0,
+             gather_batch=0):
+    return PspmmCfg(lanes_per_row, vec_width, cta_threads, rows_per_group, gather_batch, CF, blkWarpNum)

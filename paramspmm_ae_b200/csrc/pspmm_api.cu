@@ -25,7 +25,7 @@ extern "C" const char *pspmm_strerror(int code)
     switch (code) {
     case PSPMM_OK: return "ok";
     case PSPMM_E_ARG: return "invalid argument (null pointer, negative size or leading dimension smaller than dim)";
-    case PSPMM_E_CONFIG: return "invalid configuration (CF must be 1..8 (1..4 for SDDMM), blkWarpNum 4 or 8, lanes_per_row a power of two <= 32, vec_width 1/2/4, cta_threads 128/256/512)";
+    case PSPMM_E_CONFIG: return "invalid configuration (CF must be 1..8 (1..4 for SDDMM), blkWarpNum 4 or 8, lanes_per_row a power of two <= 32, vec_width 1/2/4, cta_threads 128/256, rows_per_group 1..16)";
     case PSPMM_E_CUDA: return "CUDA error (see pspmm_last_cuda_error)";
     case PSPMM_E_UNSUPPORTED: return "unsupported combination";
     case PSPMM_E_RANGE: return "size exceeds the int32 index range";
@@ -49,9 +49,12 @@ int pspmm_validate_cfg(const pspmm_cfg *cfg, bool sddmm)
         return PSPMM_E_CONFIG;
     if (cfg->vec_width != 0 && cfg->vec_width != 1 && cfg->vec_width != 2 && cfg->vec_width != 4)
         return PSPMM_E_CONFIG;
-    if (cfg->cta_threads != 0 && cfg->cta_threads != 128 && cfg->cta_threads != 256 && cfg->cta_threads != 512)
+    if (cfg->cta_threads != 0 && cfg->cta_threads != 128 && cfg->cta_threads != 256)
         return PSPMM_E_CONFIG;
-    if (cfg->rows_per_group < 0 || cfg->rows_per_group > 64)
+    if (cfg->rows_per_group < 0 || cfg->rows_per_group > PSPMM_RPG_MAX)
+        return PSPMM_E_CONFIG;
+    if (cfg->gather_batch != 0 && cfg->gather_batch != 2 && cfg->gather_batch != 4 &&
+        cfg->gather_batch != 8 && cfg->gather_batch != 16)
         return PSPMM_E_CONFIG;
     return PSPMM_OK;
 }
@@ -118,6 +121,7 @@ int pspmm_resolve_shape(const pspmm_cfg *cfg, int32_t dim, int vw_max, int V, La
     }
     s.threads = (cfg && cfg->cta_threads) ? cfg->cta_threads : 256;
     s.rpg = (cfg && cfg->rows_per_group) ? cfg->rows_per_group : 4;
+    s.mlp = (cfg && cfg->gather_batch) ? cfg->gather_batch : 8;
     *out = s;
     return PSPMM_OK;
 }
@@ -136,46 +140,73 @@ extern "C" int pspmm_resolve_cfg(pspmm_cfg *cfg, int32_t dim, int64_t ldB, int64
     cfg->vec_width = s.vw;
     cfg->cta_threads = s.threads;
     cfg->rows_per_group = s.rpg;
+    cfg->gather_batch = s.mlp;
     return PSPMM_OK;
 }
 
 // ----------------------------------------------------------------------------- zero pre-pass
-// For a split layout: zero every output (block-)row that either receives REDs (first piece of
-// a row that has several) or is covered by no piece at all.  Thread s looks at piece s; the
-// extra thread s == n_seg closes the tail.  target_row must be non-decreasing.
-__global__ void zero_uncovered_rows_kernel(const int32_t *__restrict__ target_row, int64_t n_seg,
-                                           int64_t n_out, int V, float *C, int64_t ldC, int dim,
-                                           int vecok)
+// For a split layout, before the SpMM kernel runs.  Lane groups of the SpMM kernel own `rpg`
+// consecutive segments each, so group boundaries sit at segment indices that are multiples of
+// rpg; a row whose segments straddle such a boundary is accumulated with REDs and must start
+// from zero.  This kernel zeroes those rows (once, from the first boundary they straddle) and
+// every run of more than PSPMM_GAP_MAX rows that no segment covers (the SpMM kernel zeroes
+// shorter runs itself).  Thread s looks at segment s.  Straddled rows are zeroed by the
+// finding warp; long runs are queued in shared memory and zeroed by the whole CTA, one row per
+// warp per step.  target_row must be non-decreasing.
+__global__ void __launch_bounds__(256)
+zero_shared_rows_kernel(const int32_t *__restrict__ target_row, int64_t n_seg, int64_t n_out, int rpg,
+                        int V, float *C, int64_t ldC, int dim, int vecok)
 {
+    __shared__ long long q_lo[512], q_hi[512];
+    __shared__ int q_n;
+    if (threadIdx.x == 0)
+        q_n = 0;
+    __syncthreads();
     const int64_t s = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     const int lane = threadIdx.x & 31;
-    int64_t r0 = 0, r1 = 0;
-    if (s <= n_seg) {
-        const int64_t me = s < n_seg ? (int64_t)target_row[s] : n_out;
-        const int64_t prev = s > 0 ? (int64_t)target_row[s - 1] : -1;
-        if (prev != me) {
-            const bool first_of_many = (s + 1 < n_seg) && ((int64_t)target_row[s + 1] == me);
-            r0 = prev + 1;
-            r1 = me + (first_of_many ? 1 : 0);
+    int64_t one = -1;  // a straddled row to zero, or -1
+    if (s < n_seg) {
+        const int64_t me = target_row[s];
+        const int64_t next = s + 1 < n_seg ? (int64_t)target_row[s + 1] : n_out;
+        if (s > 0 && s % rpg == 0 && (int64_t)target_row[s - 1] == me) {
+            const int64_t before = s - rpg - 1;  // last segment ahead of the previous boundary
+            if (before < 0 || (int64_t)target_row[before] != me)
+                one = me;
+        }
+        if (next - me - 1 > PSPMM_GAP_MAX) {
+            const int i = atomicAdd(&q_n, 1);
+            q_lo[i] = me + 1;
+            q_hi[i] = next;
+        }
+        if (s == 0 && me > PSPMM_GAP_MAX) {
+            const int i = atomicAdd(&q_n, 1);
+            q_lo[i] = 0;
+            q_hi[i] = me;
         }
     }
-    unsigned todo = __ballot_sync(PSPMM_FULL_MASK, r1 > r0);
+    auto zero_row = [&](int64_t r) {
+        float *row = C + r * ldC;
+        if (vecok) {
+            for (int j = lane * 4; j < dim; j += 128)
+                *reinterpret_cast<float4 *>(row + j) = make_float4(0.f, 0.f, 0.f, 0.f);
+        } else {
+            for (int j = lane; j < dim; j += 32)
+                row[j] = 0.f;
+        }
+    };
+    unsigned todo = __ballot_sync(PSPMM_FULL_MASK, one >= 0);
     while (todo) {
         const int src = __ffs(todo) - 1;
         todo &= todo - 1;
-        const int64_t a0 = __shfl_sync(PSPMM_FULL_MASK, r0, src) * V;
-        const int64_t a1 = __shfl_sync(PSPMM_FULL_MASK, r1, src) * V;
-        for (int64_t r = a0; r < a1; ++r) {
-            float *row = C + r * ldC;
-            if (vecok) {
-                for (int j = lane * 4; j < dim; j += 128)
-                    *reinterpret_cast<float4 *>(row + j) = make_float4(0.f, 0.f, 0.f, 0.f);
-            } else {
-                for (int j = lane; j < dim; j += 32)
-                    row[j] = 0.f;
-            }
-        }
+        const int64_t r = __shfl_sync(PSPMM_FULL_MASK, one, src);
+        for (int w = 0; w < V; ++w)
+            zero_row(r * V + w);
     }
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+    for (int i = 0; i < q_n; ++i)
+        for (int64_t r = q_lo[i] * V + warp; r < q_hi[i] * V; r += nwarp)
+            zero_row(r);
 }
 
 // ----------------------------------------------------------------------------- SpMM
@@ -207,10 +238,9 @@ static int spmm_launch(const int32_t *segPtr, const int32_t *target_row, int64_t
     pspmm_resolve_shape(cfg, dim, pspmm_vw_max(dim, ldB, ldC, B, C), V, &s);
 
     if (target_row) {
-        const int64_t threads = n_seg + 1;
         const int vecok = (dim % 4 == 0 && ldC % 4 == 0 && ((uintptr_t)C) % 16 == 0) ? 1 : 0;
-        zero_uncovered_rows_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, st>>>(
-            target_row, n_seg, n_out_blk_rows, V, C, ldC, dim, vecok);
+        zero_shared_rows_kernel<<<(unsigned)((n_seg + 255) / 256), 256, 0, st>>>(
+            target_row, n_seg, n_out_blk_rows, s.rpg, V, C, ldC, dim, vecok);
     }
 
     SpmmArgs a;
@@ -221,6 +251,7 @@ static int spmm_launch(const int32_t *segPtr, const int32_t *target_row, int64_t
     a.B = B;
     a.C = C;
     a.n_seg = n_seg;
+    a.n_out = n_out_blk_rows;
     a.ldB = ldB;
     a.ldC = ldC;
     a.nvec = dim / s.vw;
@@ -253,7 +284,7 @@ extern "C" int pspmm_spmm_csr(const int32_t *rowPtr, const int32_t *colIdx, cons
     if (rc)
         return rc;
     const bool split = target_row != nullptr || rowPtr_split != nullptr;
-    if (split && (!target_row || !rowPtr_split || n_seg < 0))
+    if (split && (!rowPtr_split || n_seg < 0 || (n_seg > 0 && !target_row)))
         return PSPMM_E_ARG;
     if (!split && !rowPtr)
         return PSPMM_E_ARG;
@@ -279,7 +310,7 @@ extern "C" int pspmm_spmm_bcsr(const int32_t *rowPtr_b, const int32_t *colIdx, c
     if (rc)
         return rc;
     const bool split = target_row != nullptr || rowPtr_b_split != nullptr;
-    if (split && (!target_row || !rowPtr_b_split || n_seg < 0))
+    if (split && (!rowPtr_b_split || n_seg < 0 || (n_seg > 0 && !target_row)))
         return PSPMM_E_ARG;
     if (!split && !rowPtr_b)
         return PSPMM_E_ARG;
@@ -345,7 +376,7 @@ extern "C" int pspmm_sddmm_csr(const int32_t *rowPtr, const int32_t *colIdx, con
     if (rc)
         return rc;
     const bool split = target_row != nullptr || rowPtr_split != nullptr;
-    if (split && (!target_row || !rowPtr_split || n_seg < 0))
+    if (split && (!rowPtr_split || n_seg < 0 || (n_seg > 0 && !target_row)))
         return PSPMM_E_ARG;
     if (!split && !rowPtr)
         return PSPMM_E_ARG;
@@ -371,7 +402,7 @@ extern "C" int pspmm_sddmm_bcsr(const int32_t *rowPtr_b, const int32_t *colIdx, 
     if (rc)
         return rc;
     const bool split = target_row != nullptr || rowPtr_b_split != nullptr;
-    if (split && (!target_row || !rowPtr_b_split || n_seg < 0))
+    if (split && (!rowPtr_b_split || n_seg < 0 || (n_seg > 0 && !target_row)))
         return PSPMM_E_ARG;
     if (!split && !rowPtr_b)
         return PSPMM_E_ARG;

@@ -8,6 +8,8 @@
 
 #define PSPMM_FULL_MASK 0xffffffffu
 #define PSPMM_MAX_CF 8
+#define PSPMM_RPG_MAX 16  // most consecutive segments one lane group owns
+#define PSPMM_GAP_MAX 16  // longest run of uncovered rows the SpMM kernel zeroes by itself
 
 // Records the CUDA error text for pspmm_last_cuda_error() and returns PSPMM_E_CUDA.
 int pspmm_note_cuda_error(cudaError_t e);
@@ -29,6 +31,7 @@ struct SpmmArgs {
     const float *B;
     float *C;
     int64_t n_seg;
+    int64_t n_out;              // output (block-)rows
     int64_t ldB, ldC;
     int32_t nvec;               // dim / VW: vectors per dense row
     int32_t rows_per_group;
@@ -50,7 +53,7 @@ struct SddmmArgs {
 
 // Resolved launch shape.
 struct LaunchShape {
-    int lpr, vw, cf, threads, rpg, tiles;
+    int lpr, vw, cf, threads, rpg, tiles, mlp;
 };
 
 // Per-translation-unit dispatchers (one per vector width so the files compile in parallel).

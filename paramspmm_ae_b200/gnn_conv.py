@@ -1,0 +1,112 @@
+"""GCN / GIN / AGNN layers over the PCSR operators: mirror of the reference's ``gnn_conv.py``.
+
+Same module and autograd-function names, constructor arguments and forward signatures
+(gnn_conv.py:13-238 of the reference).  The layer semantics are the reference's:
+
+* GCN   forward  A (H W); backward AG = A G (A itself: the normalised adjacency is symmetric),
+        dH = AG W^T, dW = H^T AG.
+* GIN   forward  (A X) W; backward dW = (A X)^T G, dX = A (G W^T).
+* AGNN  forward  X' = X W, e = SDDMM(X', X') * beta, out = SpMM(e, X'); no edge softmax and no
+        row normalisation (the reference has none); the gradient w.r.t. beta follows the
+        reference's expression (gnn_conv.py:164-172).
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+n_heads = 1
+
+
+class GCNFunction(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, H, weight, ParamSpMM):
+        ctx.save_for_backward(H, weight)
+        ctx.ParamSpMM = ParamSpMM
+        return ParamSpMM.forward(H, weight)
+
+    @staticmethod
+    def backward(ctx, d_output):
+        H, weight = ctx.saved_tensors
+        d_input, d_weight = ctx.ParamSpMM.backward(d_output.contiguous(), H, weight)
+        return d_input, d_weight, None
+
+
+class GINFunction(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, X, weight, ParamSpMM):
+        X_agg = ParamSpMM.GIN_spmm(X)
+        ctx.save_for_backward(X_agg, weight)
+        ctx.ParamSpMM = ParamSpMM
+        return torch.mm(X_agg, weight)
+
+    @staticmethod
+    def backward(ctx, d_output):
+        X_agg, weight = ctx.saved_tensors
+        d_weight = torch.mm(X_agg.t(), d_output)
+        d_input = ctx.ParamSpMM.GIN_spmm(torch.mm(d_output, weight.t()).contiguous())
+        return d_input, d_weight, None
+
+
+class AGNNFunction(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, X, weights, attention_w, ParamSpMM, colIdx):
+        X_prime = torch.mm(X, weights)
+        edge = ParamSpMM.AGNN_sddmm(X_prime)
+        # [n_edges] for CSR, [n_blocks, V] for block layouts; one attention head
+        edge_attentions = (edge * attention_w.reshape(())).contiguous()
+        out = ParamSpMM.AGNN_spmm(edge_attentions, X_prime)
+        ctx.save_for_backward(X, weights, edge_attentions)
+        ctx.colIdx, ctx.ParamSpMM = colIdx, ParamSpMM
+        return out
+
+    @staticmethod
+    def backward(ctx, d_output):
+        P = ctx.ParamSpMM
+        X, weights, edge_attentions = ctx.saved_tensors
+        d_output = d_output.contiguous()
+        d_prime = P.AGNN_spmm(edge_attentions, d_output)
+        d_input = torch.mm(d_prime, weights.t())
+        d_weights = torch.mm(X.t(), d_prime)
+        d_att = P.AGNN_sddmm(d_output)
+        if d_att.dim() != 1:
+            d_att = d_att.reshape(-1)[P.mask]  # back to CSR entry order
+        d_attention_w = torch.mm(d_att[None, :].expand(n_heads, -1), ctx.colIdx.float()).transpose(0, 1)
+        return d_input, d_weights, d_attention_w, None, None
+
+
+class _Conv(torch.nn.Module):
+    def __init__(self, input_dim, output_dim):
+        super().__init__()
+        self.weights = torch.nn.Parameter(torch.randn(input_dim, output_dim))
+        self.reset_parameters()
+
+    def reset_parameters(self):
+        stdv = 1.0 / math.sqrt(self.weights.size(1))
+        self.weights.data.uniform_(-stdv, stdv)
+
+    def _operator(self, spmm_dict):
+        dim = self.weights.size(1)
+        if dim not in spmm_dict:
+            raise ValueError("SpMMDecider not support dim: " + str(dim))
+        return spmm_dict[dim]
+
+
+class GCNConv(_Conv):
+    def forward(self, H, spmm_dict):
+        return GCNFunction.apply(H, self.weights, self._operator(spmm_dict))
+
+
+class GINConv(_Conv):
+    def forward(self, X, spmm_dict):
+        return GINFunction.apply(X, self.weights, self._operator(spmm_dict))
+
+
+class AGNNConv(_Conv):
+    def __init__(self, input_dim, output_dim):
+        super().__init__(input_dim, output_dim)
+        self.attention_w = torch.nn.Parameter(torch.randn(1, n_heads))
+
+    def forward(self, X, spmm_dict, colIdx):
+        return AGNNFunction.apply(X, self.weights, self.attention_w, self._operator(spmm_dict), colIdx)

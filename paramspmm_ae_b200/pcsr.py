@@ -1,0 +1,189 @@
+"""Operator objects: host-side mirror of the reference's ``pcsr_spmm`` (PCSR.py:127-657) and
+``pcsr_sddmm`` (SDDMM.py:46-254).
+
+A ``pcsr_spmm`` holds the device copies of one representation of a matrix (CSR or V x 1
+block CSR, plain or row-split) together with the legacy ``(vec_size, if_split, CF,
+blkWarpNum)`` tuple and routes every method to the matching operator.  Method names,
+arguments and return values follow the reference; the routing is a table instead of the
+reference's nested conditionals.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import baselines, ops
+
+# (vec_size class, if_split) -> operator.  vec_size class: 1 -> "csr", 2 -> "bcsr", else "vec".
+_SPMM = {("csr", False): ops.csr_spmm, ("csr", True): ops.csr_split_spmm,
+         ("bcsr", False): ops.bcsr_spmm, ("bcsr", True): ops.bcsr_split_spmm,
+         ("vec", False): ops.vec_spmm, ("vec", True): ops.vec_split_spmm}
+_SDDMM = {("csr", False): ops.csr_sddmm, ("csr", True): ops.csr_split_sddmm,
+          ("bcsr", False): ops.bcsr_sddmm, ("bcsr", True): ops.bcsr_split_sddmm,
+          ("vec", False): ops.vec_sddmm, ("vec", True): ops.vec_split_sddmm}
+_SPMM_PROFILE = {("csr", False): ops.csr_spmm_profile, ("csr", True): ops.csr_split_spmm_profile,
+                 ("bcsr", False): ops.bcsr_spmm_profile, ("bcsr", True): ops.bcsr_split_spmm_profile,
+                 ("vec", False): ops.vec_spmm_profile, ("vec", True): ops.vec_split_spmm_profile}
+_SDDMM_PROFILE = {("csr", False): ops.csr_sddmm_profile, ("csr", True): ops.csr_split_sddmm_profile,
+                  ("bcsr", False): ops.bcsr_sddmm_profile, ("bcsr", True): ops.bcsr_split_sddmm_profile,
+                  ("vec", False): ops.vec_sddmm_profile, ("vec", True): ops.vec_split_sddmm_profile}
+_CONV_FWD = {("csr", False): ops.csr_spmm_forward, ("csr", True): ops.csr_split_spmm_forward,
+             ("bcsr", False): ops.bcsr_spmm_forward, ("bcsr", True): ops.bcsr_split_spmm_forward}
+_CONV_BWD = {("csr", False): ops.csr_spmm_backward, ("csr", True): ops.csr_split_spmm_backward,
+             ("bcsr", False): ops.bcsr_spmm_backward, ("bcsr", True): ops.bcsr_split_spmm_backward}
+
+
+def _kind(vec_size):
+    return "csr" if vec_size == 1 else ("bcsr" if vec_size == 2 else "vec")
+
+
+class pcsr_spmm(object):
+    def __init__(self, graph, vec_size, if_split, mtx_nodes=None, mtx_edges=None, rowPtr=None,
+                 colIdx=None, val=None, target_row=None, CF=1, blkWarpNum=4, device="cuda"):
+        """From a ``graph_input`` (graph is not None) or from raw tensors (PCSR.py:128-204)."""
+        if_split = bool(if_split)
+        self.mask = None
+        if graph is None:
+            if any(x is None for x in (mtx_edges, mtx_nodes, rowPtr, colIdx, val)):
+                raise ValueError("when graph is None, mtx_nodes, mtx_edges, rowPtr, colIdx, val should be given")
+            if if_split and target_row is None:
+                raise ValueError("target_row should be given when if_split is True")
+            if not if_split and target_row is not None:
+                raise ValueError("target_row should not be given when if_split is False")
+            if (vec_size == 1) != (val.dim() == 1):
+                raise ValueError("val must be 1-D for vec_size 1 and [nblk, vec_size] otherwise")
+            self.mtx_nodes, self.mtx_edges = mtx_nodes, mtx_edges
+            self.rowPtr, self.colIdx, self.val = rowPtr.to(device), colIdx.to(device), val.to(device)
+            self.target_row = target_row.to(device) if target_row is not None else None
+        else:
+            self.mtx_nodes, self.mtx_edges = graph.mtx_nodes, graph.mtx_edges
+            src = graph.csr_data if vec_size == 1 else graph.bcsr_data
+            self.rowPtr = (src.rowPtr_split if if_split else src.rowPtr).to(device)
+            self.colIdx, self.val = src.colIdx.to(device), src.val.to(device)
+            self.target_row = src.target_row.to(device) if if_split else None
+            if vec_size != 1 and graph.mask is not None:
+                self.mask = graph.mask.to(device)
+        self.vec_size, self.if_split, self.CF, self.blkWarpNum = vec_size, if_split, CF, blkWarpNum
+        self.result = None
+
+    # -- helpers ------------------------------------------------------------------------
+    def _key(self):
+        return _kind(self.vec_size), self.if_split
+
+    def _layout(self, val=None):
+        v = self.val if val is None else val
+        if self.if_split:
+            return (self.rowPtr, self.colIdx, v, self.target_row)
+        return (self.rowPtr, self.colIdx, v)
+
+    def _dense_input(self, dim, x):
+        if x is None and dim is None:
+            raise ValueError("at least one of x and dim should be given")
+        if dim is not None:
+            return torch.ones(self.mtx_nodes, dim, device="cuda")
+        return x.to("cuda")
+
+    # -- SpMM ---------------------------------------------------------------------------
+    def get_spmm_result(self, dim=None, x=None, CF=None, blkWarpNum=None):
+        X = self._dense_input(dim, x)
+        CF = self.CF if CF is None else CF
+        W = self.blkWarpNum if blkWarpNum is None else blkWarpNum
+        out = _SPMM[self._key()](X, *self._layout(), CF, W)
+        self.result = out[: self.mtx_nodes].to("cpu")  # block layouts pad the row count
+
+    def AGNN_spmm(self, spVal, X):
+        """SpMM with caller-supplied edge values in place of the stored ones (PCSR.py:244-265)."""
+        return _SPMM[self._key()](X, *self._layout(spVal), self.CF, self.blkWarpNum)
+
+    def GIN_spmm(self, X):
+        return _SPMM[self._key()](X, *self._layout(), self.CF, self.blkWarpNum)
+
+    # -- SDDMM --------------------------------------------------------------------------
+    def AGNN_sddmm(self, A):
+        """Edge scores <A[i], A[j]> on the pattern (PCSR.py:290-320); CF = ceil(dim/32)."""
+        if self.vec_size == 2 and self.mask is None:
+            raise ValueError("mask should be given when vec_size=2")
+        CF = (A.size(1) + 31) // 32
+        return _SDDMM[self._key()](A, A, *self._layout(), CF, self.blkWarpNum)
+
+    def get_sddmm_result(self, dim, blkWarpNum):
+        A = torch.ones((self.mtx_nodes + 1) // 2 * 2, dim, device="cuda")
+        B = torch.ones(self.mtx_nodes, dim, device="cuda")
+        self.result = _SDDMM[self._key()](A, B, *self._layout(), (dim + 31) // 32, blkWarpNum).to("cpu")
+        return self.result
+
+    # -- GCN layer ----------------------------------------------------------------------
+    def _conv_key(self):
+        return ("csr" if self.vec_size == 1 else "bcsr"), self.if_split
+
+    def forward(self, H, w):
+        if H is None or w is None:
+            raise ValueError("H and w should be given")
+        return _CONV_FWD[self._conv_key()](H, w, *self._layout(), self.CF, self.blkWarpNum)
+
+    def backward(self, d_output, H, w):
+        if d_output is None or H is None:
+            raise ValueError("d_output and H should be given")
+        return tuple(_CONV_BWD[self._conv_key()](d_output, H, w, *self._layout(), self.CF, self.blkWarpNum))
+
+    # -- timing -------------------------------------------------------------------------
+    def cf_warpnum_profiling(self, CF, blkWarpNum, dim=None, x=None):
+        X = self._dense_input(dim, x)
+        extra = () if self.vec_size == 1 else (self.mtx_edges,)
+        tp = _SPMM_PROFILE[self._key()](X, *self._layout(), *extra, CF, blkWarpNum)
+        print("dim: {} gflops: {:.0f}".format(X.shape[1], tp))
+        return tp
+
+    def profiling(self, dim=None, x=None):
+        return self.cf_warpnum_profiling(self.CF, self.blkWarpNum, dim, x)
+
+    def _baseline(self, compute, profile, label, dim, x, is_profiling):
+        if self.if_split or self.vec_size != 1:
+            raise ValueError("cusparse only support vec_size=1 and if_split=False")
+        X = self._dense_input(dim, x)
+        if is_profiling:
+            tp = profile(X, self.rowPtr, self.colIdx, self.val)
+            print("{}-> dim: {} gflops: {:.0f}".format(label, dim, tp))
+            return tp
+        return compute(X, self.rowPtr, self.colIdx, self.val).to("cpu")
+
+    def cusparse_ref(self, dim=None, x=None, is_profiling=False):
+        return self._baseline(baselines.cusparse_compute, baselines.cusparse_profile, "cusparse", dim, x, is_profiling)
+
+    def cusparse_csr_alg2_ref(self, dim=None, x=None, is_profiling=False):
+        return self._baseline(baselines.cusparse_compute_csr_alg2, baselines.cusparse_profile_csr_alg2,
+                              "cusparse_csr_alg2", dim, x, is_profiling)
+
+    def gespmm_ref(self, dim=None, x=None, is_profiling=False):
+        return self._baseline(baselines.gespmm_compute, baselines.gespmm_profile, "gespmm", dim, x, is_profiling)
+
+
+class pcsr_sddmm(pcsr_spmm):
+    """SDDMM-side operator object (SDDMM.py:46-254): same storage, SDDMM timing and reference."""
+
+    def profiling(self, blkWarpNum, dim):
+        A = torch.ones((self.mtx_nodes + 1) // 2 * 2, dim, device="cuda")
+        B = torch.ones(self.mtx_nodes, dim, device="cuda")
+        extra = () if self.vec_size == 1 else (self.mtx_edges,)
+        tp = _SDDMM_PROFILE[self._key()](A, B, *self._layout(), *extra, (dim + 31) // 32, blkWarpNum)
+        print("dim: {} gflops: {:.0f}".format(dim, tp))
+        return tp
+
+    def cusparse_ref(self, dim=None, is_profiling=False):
+        if self.if_split or self.vec_size != 1:
+            raise ValueError("cusparse only support vec_size=1 and if_split=False")
+        A = torch.ones(self.mtx_nodes, dim, device="cuda")
+        vals = self.val.clone()
+        if is_profiling:
+            return baselines.cusparse_sddmm_profile(A, A, self.rowPtr, self.colIdx, vals)
+        return baselines.cusparse_sddmm_compute(A, A, self.rowPtr, self.colIdx, vals).to("cpu")
+
+
+def compare(result, result_ref, rel=1e-4):
+    """The reference's SDDMM acceptance rule (SDDMM.py:19-36): relative error at most 1e-4."""
+    err = (result_ref - result).abs()
+    return not bool((err > rel * result_ref.abs()).any())
+
+
+def compare_2d(result, result_ref, mask, rel=1e-4):
+    """Block results are compared in CSR order through the mask (SDDMM.py:39-43)."""
+    return compare(result.reshape(-1)[mask], result_ref, rel)
