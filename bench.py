@@ -47,6 +47,7 @@ def parse():
     ap.add_argument("--cpu-seconds", type=float, default=15.0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-comparators", action="store_true", help="skip the cuSPARSE timing rows")
     return ap.parse_args()
 
 
@@ -328,6 +329,32 @@ def main():
                "call": "ParamSpMM.csr_spmm on device copies of pinned host CSR arrays and B, result copied "
                        "back to pinned host memory, every launch of the pass"}
 
+    # ---- cuSPARSE on the same GPU, same inputs (reported next to the kernels; rank 0, N = 1 only)
+    comparators = None
+    if rank == 0 and world == 1 and not args.no_comparators:
+        try:
+            from paramspmm_ae_b200 import baselines
+            rows = []
+            for dim in [d for d in (16, 64, 128, 256) if d in dims]:
+                for name in MATRICES:
+                    m = mats[name]
+                    ours = mean_ms[cases.index((name, dim))]
+                    rec = {"matrix": name, "dim": dim, "ours_ms": round(ours, 5)}
+                    for label, fmt in (("cusparse_csr_default", 0), ("cusparse_csr_alg2", 1)):
+                        plan = baselines.spmm_plan(fmt, m.rowPtr, m.colIdx, m.val, Bs[dim], Cs[dim])
+                        ms = baselines.time_plan_ms(plan, warmup=3, iters=20)
+                        plan.close()
+                        rec[label + "_ms"] = round(ms, 5)
+                    rec["speedup_vs_best_cusparse"] = round(min(rec["cusparse_csr_default_ms"], rec["cusparse_csr_alg2_ms"]) / ours, 3)
+                    rows.append(rec)
+            sp = [r["speedup_vs_best_cusparse"] for r in rows]
+            comparators = {"note": "cusparseSpMM fp32 CSR, row-major B/C, plan and workspace created outside the loop, "
+                                   "20 back-to-back launches without L2 flush (our column is flushed): favours cuSPARSE",
+                           "geomean_speedup_vs_best_cusparse": round(float(torch.tensor(sp).log().mean().exp()), 3),
+                           "rows": rows}
+        except Exception as e:
+            comparators = {"unavailable": "%s: %s" % (type(e).__name__, e)}
+
     # ---- CPU baseline on the host cores (rank 0, N = 1 only)
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
@@ -348,7 +375,7 @@ def main():
                        "l2": "flushed before every launch (256 MiB memset outside the timed events)",
                        "sharding": "row blocks, dense operand replicated, no collective"},
             "e2e": e2e, "gpu_launches": launches, "clocks": clocks, "roofline": roofline,
-            "cpu_baseline": cpu, "wall_ms_per_step_incl_flush": wall / args.steps * 1e3, "sweep": sweep,
+            "cpu_baseline": cpu, "comparators": comparators, "wall_ms_per_step_incl_flush": wall / args.steps * 1e3, "sweep": sweep,
         }))
     if world > 1:
         dist.destroy_process_group()

@@ -219,9 +219,32 @@ static int check_sizes(int64_t n_rows, int64_t n_cols, int64_t nnz, int32_t dim)
     return PSPMM_OK;
 }
 
+// Fraction of the gathered operand to pin in L2: all of it when it fits in about three quarters
+// of the cache, otherwise the share that does.
+static float l2_keep_fraction(double operand_bytes)
+{
+    static thread_local int cached_dev = -1;
+    static thread_local double l2_bytes = 0.0;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess)
+        return 1.0f;
+    if (dev != cached_dev) {
+        int v = 0;
+        if (cudaDeviceGetAttribute(&v, cudaDevAttrL2CacheSize, dev) != cudaSuccess || v <= 0)
+            v = 64 << 20;
+        l2_bytes = (double)v;
+        cached_dev = dev;
+    }
+    const double budget = 0.75 * l2_bytes;
+    if (operand_bytes <= budget)
+        return 1.0f;
+    const double f = budget / operand_bytes;
+    return (float)(f < 0.02 ? 0.02 : f);
+}
+
 static int spmm_launch(const int32_t *segPtr, const int32_t *target_row, int64_t n_seg,
                        const int32_t *colIdx, const float *val, int V, const float *B, float *C,
-                       int64_t n_out_blk_rows, int32_t dim, int64_t ldB, int64_t ldC,
+                       int64_t n_out_blk_rows, int64_t n_cols, int32_t dim, int64_t ldB, int64_t ldC,
                        const pspmm_cfg *cfg, cudaStream_t st)
 {
     int rc = pspmm_validate_cfg(cfg, false);
@@ -256,6 +279,7 @@ static int spmm_launch(const int32_t *segPtr, const int32_t *target_row, int64_t
     a.ldC = ldC;
     a.nvec = dim / s.vw;
     a.rows_per_group = s.rpg;
+    a.keep_fraction = l2_keep_fraction((double)n_cols * (double)ldB * 4.0);
     const int64_t per_cta = (int64_t)(s.threads / s.lpr) * s.rpg;
     const int64_t gx = (n_seg + per_cta - 1) / per_cta;
     if (gx > INT32_MAX || s.tiles > 65535)
@@ -295,7 +319,7 @@ extern "C" int pspmm_spmm_csr(const int32_t *rowPtr, const int32_t *colIdx, cons
     if (split && n_seg >= INT32_MAX)
         return PSPMM_E_RANGE;
     return spmm_launch(split ? rowPtr_split : rowPtr, target_row, split ? n_seg : n_rows, colIdx,
-                       val, 1, B, C, n_rows, dim, ldB, ldC, cfg, (cudaStream_t)stream);
+                       val, 1, B, C, n_rows, n_cols, dim, ldB, ldC, cfg, (cudaStream_t)stream);
 }
 
 extern "C" int pspmm_spmm_bcsr(const int32_t *rowPtr_b, const int32_t *colIdx, const float *val,
@@ -319,7 +343,7 @@ extern "C" int pspmm_spmm_bcsr(const int32_t *rowPtr_b, const int32_t *colIdx, c
     if (nblk > 0 && (!colIdx || !val))
         return PSPMM_E_ARG;
     return spmm_launch(split ? rowPtr_b_split : rowPtr_b, target_row, split ? n_seg : n_blk_rows,
-                       colIdx, val, V, B, C, n_blk_rows, dim, ldB, ldC, cfg, (cudaStream_t)stream);
+                       colIdx, val, V, B, C, n_blk_rows, n_cols, dim, ldB, ldC, cfg, (cudaStream_t)stream);
 }
 
 // ----------------------------------------------------------------------------- SDDMM

@@ -35,6 +35,7 @@ struct SpmmArgs {
     int64_t ldB, ldC;
     int32_t nvec;               // dim / VW: vectors per dense row
     int32_t rows_per_group;
+    float keep_fraction;        // share of B's lines marked evict-last in L2 (0..1]
 };
 
 struct SddmmArgs {

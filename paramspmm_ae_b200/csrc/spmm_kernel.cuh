@@ -55,7 +55,8 @@ __device__ __forceinline__ const float *row_slice(const char *base, int c, unsig
 // One batch of UU entries starting at shared-memory index e: gathers first, FMAs after.
 template <int UU, int LPR, int VW, int CF, int V>
 __device__ __forceinline__ void spmm_batch(const int *ent, int e, const char *const (&bcol)[CF],
-                                           unsigned ldB_bytes, float (&acc)[V][CF][VW])
+                                           unsigned ldB_bytes, unsigned long long keep,
+                                           float (&acc)[V][CF][VW])
 {
     int c[UU];
     float v[UU][V];
@@ -77,7 +78,7 @@ __device__ __forceinline__ void spmm_batch(const int *ent, int e, const char *co
     for (int u = 0; u < UU; ++u)
 #pragma unroll
         for (int cf = 0; cf < CF; ++cf)
-            x[u][cf] = ldg_vec<VW>(row_slice(bcol[cf], c[u], ldB_bytes));
+            x[u][cf] = ldg_vec_hint<VW>(row_slice(bcol[cf], c[u], ldB_bytes), keep);
 #pragma unroll
     for (int u = 0; u < UU; ++u)
 #pragma unroll
@@ -108,8 +109,8 @@ __global__ void __launch_bounds__(256, SpmmOcc<MLP>::MIN_CTAS) spmm_seg_kernel(c
     using Tile = SpmmTile<LPR, V>;
     constexpr int CAP = Tile::CAP;
     constexpr int U0 = MLP / (CF * (V > 1 ? 2 : 1));
-    constexpr int U1 = U0 < 1 ? 1 : U0;
-    constexpr int U = U1 > 16 ? 16 : U1;  // entries per full gather batch
+    // entries per full gather batch: a power of two (the row tail falls through U/2, U/4, ...)
+    constexpr int U = U0 >= 16 ? 16 : (U0 >= 8 ? 8 : (U0 >= 4 ? 4 : (U0 >= 2 ? 2 : 1)));
 
     extern __shared__ __align__(16) int smem_words[];
     const int gpc = blockDim.x / LPR;
@@ -150,6 +151,10 @@ __global__ void __launch_bounds__(256, SpmmOcc<MLP>::MIN_CTAS) spmm_seg_kernel(c
         bcol[cf] = reinterpret_cast<const char *>(a.B + voff[cf]);
     }
     const unsigned ldB_bytes = (unsigned)(a.ldB * 4);
+    // B is gathered many times: keep a stable fraction of it in L2.  A is read once and C is
+    // written once: both are marked evict-first so they do not push B out.
+    const unsigned long long keep = l2_policy_keep(a.keep_fraction);
+    const unsigned long long stream = l2_policy_stream();
 
     float acc[V][CF][VW];
 #pragma unroll
@@ -172,12 +177,12 @@ __global__ void __launch_bounds__(256, SpmmOcc<MLP>::MIN_CTAS) spmm_seg_kernel(c
             const int k = cur + i;
             if constexpr (V == 1) {
                 *reinterpret_cast<int2 *>(ent + 2 * i) =
-                    make_int2(__ldg(a.colIdx + k), __float_as_int(__ldg(a.val + k)));
+                    make_int2(ldg_stream_b32(a.colIdx + k, stream), ldg_stream_b32(a.val + k, stream));
             } else {
-                ent[(1 + V) * i] = __ldg(a.colIdx + k);
+                ent[(1 + V) * i] = ldg_stream_b32(a.colIdx + k, stream);
 #pragma unroll
                 for (int w = 0; w < V; ++w)
-                    ent[(1 + V) * i + 1 + w] = __float_as_int(__ldg(a.val + (int64_t)k * V + w));
+                    ent[(1 + V) * i + 1 + w] = ldg_stream_b32(a.val + (int64_t)k * V + w, stream);
             }
         }
         __syncwarp(gmask);
@@ -187,28 +192,28 @@ __global__ void __launch_bounds__(256, SpmmOcc<MLP>::MIN_CTAS) spmm_seg_kernel(c
             int e = (rb > cur ? rb : cur) - cur;
             const int eh = (re < lim ? re : lim) - cur;
             for (; e + U <= eh; e += U)
-                spmm_batch<U, LPR, VW, CF, V>(ent, e, bcol, ldB_bytes, acc);
+                spmm_batch<U, LPR, VW, CF, V>(ent, e, bcol, ldB_bytes, keep, acc);
             if constexpr (U >= 16) {
                 if (e + 8 <= eh) {
-                    spmm_batch<8, LPR, VW, CF, V>(ent, e, bcol, ldB_bytes, acc);
+                    spmm_batch<8, LPR, VW, CF, V>(ent, e, bcol, ldB_bytes, keep, acc);
                     e += 8;
                 }
             }
             if constexpr (U >= 8) {
                 if (e + 4 <= eh) {
-                    spmm_batch<4, LPR, VW, CF, V>(ent, e, bcol, ldB_bytes, acc);
+                    spmm_batch<4, LPR, VW, CF, V>(ent, e, bcol, ldB_bytes, keep, acc);
                     e += 4;
                 }
             }
             if constexpr (U >= 4) {
                 if (e + 2 <= eh) {
-                    spmm_batch<2, LPR, VW, CF, V>(ent, e, bcol, ldB_bytes, acc);
+                    spmm_batch<2, LPR, VW, CF, V>(ent, e, bcol, ldB_bytes, keep, acc);
                     e += 2;
                 }
             }
             if constexpr (U >= 2) {
                 if (e < eh)
-                    spmm_batch<1, LPR, VW, CF, V>(ent, e, bcol, ldB_bytes, acc);
+                    spmm_batch<1, LPR, VW, CF, V>(ent, e, bcol, ldB_bytes, keep, acc);
             }
             if (re > lim)
                 break;  // the row continues in the next window
@@ -238,7 +243,7 @@ __global__ void __launch_bounds__(256, SpmmOcc<MLP>::MIN_CTAS) spmm_seg_kernel(c
                         if (shared)
                             red_add_vec<VW>(crow + voff[cf], acc[w][cf]);
                         else
-                            st_stream_vec<VW>(crow + voff[cf], acc[w][cf]);
+                            st_vec_hint<VW>(crow + voff[cf], acc[w][cf], stream);
                     }
 #pragma unroll
                     for (int i = 0; i < VW; ++i)
@@ -256,7 +261,7 @@ __global__ void __launch_bounds__(256, SpmmOcc<MLP>::MIN_CTAS) spmm_seg_kernel(c
 #pragma unroll
                         for (int cf = 0; cf < CF; ++cf)
                             if (act[cf])
-                                st_stream_vec<VW>(crow + voff[cf], zero);
+                                st_vec_hint<VW>(crow + voff[cf], zero, stream);
                     }
                 };
                 const int64_t after = (int64_t)next - orow - 1;

@@ -25,6 +25,62 @@ __device__ __forceinline__ FVec<VW> ldg_vec(const float *p)
     return r;
 }
 
+// L2 eviction policies (createpolicy).  `keep` marks a fraction of the touched lines
+// evict_last so that a stable subset of a randomly gathered operand stays resident when the
+// whole operand does not fit; `stream` marks lines evict_first (data read or written once).
+__device__ __forceinline__ unsigned long long l2_policy_keep(float fraction)
+{
+    unsigned long long pol;
+    asm volatile("createpolicy.fractional.L2::evict_last.L2::evict_unchanged.b64 %0, %1;" : "=l"(pol) : "f"(fraction));
+    return pol;
+}
+__device__ __forceinline__ unsigned long long l2_policy_stream()
+{
+    unsigned long long pol;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+
+// Read-only load of VW floats with an L2 cache-policy hint.
+template <int VW>
+__device__ __forceinline__ FVec<VW> ldg_vec_hint(const float *p, unsigned long long pol)
+{
+    FVec<VW> r;
+    if constexpr (VW == 4) {
+        asm("ld.global.nc.L2::cache_hint.v4.f32 {%0, %1, %2, %3}, [%4], %5;"
+            : "=f"(r.v[0]), "=f"(r.v[1]), "=f"(r.v[2]), "=f"(r.v[3]) : "l"(p), "l"(pol));
+    } else if constexpr (VW == 2) {
+        asm("ld.global.nc.L2::cache_hint.v2.f32 {%0, %1}, [%2], %3;"
+            : "=f"(r.v[0]), "=f"(r.v[1]) : "l"(p), "l"(pol));
+    } else {
+        asm("ld.global.nc.L2::cache_hint.f32 %0, [%1], %2;" : "=f"(r.v[0]) : "l"(p), "l"(pol));
+    }
+    return r;
+}
+
+// Streaming 32-bit read (index / value arrays): no L1 allocation, evict-first in L2.
+__device__ __forceinline__ int ldg_stream_b32(const void *p, unsigned long long pol)
+{
+    int r;
+    asm("ld.global.nc.L1::no_allocate.L2::cache_hint.b32 %0, [%1], %2;" : "=r"(r) : "l"(p), "l"(pol));
+    return r;
+}
+
+// Store of VW floats with an L2 cache-policy hint.
+template <int VW>
+__device__ __forceinline__ void st_vec_hint(float *p, const float *v, unsigned long long pol)
+{
+    if constexpr (VW == 4) {
+        asm volatile("st.global.L2::cache_hint.v4.f32 [%0], {%1, %2, %3, %4}, %5;"
+                     :: "l"(p), "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3]), "l"(pol) : "memory");
+    } else if constexpr (VW == 2) {
+        asm volatile("st.global.L2::cache_hint.v2.f32 [%0], {%1, %2}, %3;"
+                     :: "l"(p), "f"(v[0]), "f"(v[1]), "l"(pol) : "memory");
+    } else {
+        asm volatile("st.global.L2::cache_hint.f32 [%0], %1, %2;" :: "l"(p), "f"(v[0]), "l"(pol) : "memory");
+    }
+}
+
 // Predicated read-only load: returns zeros and touches no memory when `on` is false.  Written
 // as one predicated PTX instruction so that a batch of these stays straight-line code and the
 // loads of the whole batch can be in flight together (a C++ conditional around a load may

@@ -1,0 +1,153 @@
+"""Row-sharded SpMM across the GPUs of one node (one process per GPU, torch.distributed).
+
+The reference is single-GPU.  The product C = A B shards naturally by rows of A: rank p owns
+a contiguous block of rows of A (chosen on the prefix sum of rowPtr so every rank holds about
+nnz / world entries), the same block of rows of C, and, between GNN layers, the matching block
+of rows of the dense operand.  The one exchange step is an all-gather of the dense row blocks
+(NCCL over NVLink on GPUs); the SpMM itself is local and needs no collective.
+
+Unequal row blocks are gathered without any repacking: every rank pads its block to the
+largest block's row count, ``all_gather_into_tensor`` lays the padded blocks one after the
+other, and the column indices of the local shard of A are remapped ONCE, at set-up, to
+positions in that padded layout (column c owned by rank q at local row i becomes
+q * max_rows + i).  The gathered buffer is then the dense operand as it stands.
+
+``dim_chunks > 1`` splits the dense columns into slices and gathers slice s+1 on a side
+stream while the SpMM of slice s runs (the kernels take explicit leading dimensions, so a
+slice of C is written in place).
+"""
+from __future__ import annotations
+
+import torch
+
+
+def partition_rows_by_nnz(rowPtr, world):
+    """Row boundaries [world + 1]: block p = rows [b[p], b[p+1]) holds about nnz / world entries."""
+    rp = torch.as_tensor(rowPtr).long().cpu()
+    n = rp.numel() - 1
+    nnz = int(rp[-1])
+    targets = torch.tensor([(nnz * p) // world for p in range(1, world)], dtype=torch.long)
+    cuts = torch.searchsorted(rp, targets, right=False).clamp_(0, n)
+    b = torch.cat([torch.zeros(1, dtype=torch.long), cuts, torch.tensor([n])])
+    return torch.cummax(b, 0).values  # non-decreasing even for degenerate inputs
+
+
+def partition_rows_even(n, world):
+    return torch.tensor([(n * p) // world for p in range(world + 1)], dtype=torch.long)
+
+
+def extract_rows(rowPtr, colIdx, val, lo, hi):
+    """Rows [lo, hi) of a CSR matrix with re-based row pointers and global column ids."""
+    rp = torch.as_tensor(rowPtr)
+    a, b = int(rp[lo]), int(rp[hi])
+    return ((rp[lo: hi + 1] - rp[lo]).to(torch.int32).contiguous(), colIdx[a:b].contiguous(),
+            val[a:b].contiguous())
+
+
+def remap_columns(colIdx, col_bounds, max_rows):
+    """Global column ids -> positions in the padded all-gather layout."""
+    cb = torch.as_tensor(col_bounds).long().to(colIdx.device)
+    c = colIdx.long()
+    owner = torch.searchsorted(cb, c, right=True) - 1
+    return (owner * max_rows + (c - cb[owner])).to(torch.int32)
+
+
+class ShardedSpMM:
+    """One rank's share of a row-sharded SpMM.
+
+    ``row_bounds``: rows of A / C per rank.  ``col_bounds``: rows of the dense operand per rank
+    (for a square matrix between GNN layers this is ``row_bounds`` again).  ``local_spmm`` is the
+    kernel launcher ``f(out, B, rowPtr, colIdx, val)``; it defaults to the CUDA operator.
+    """
+
+    def __init__(self, rowPtr, colIdx, val, n_cols, rank, world, row_bounds=None, col_bounds=None,
+                 device="cuda", group=None, local_spmm=None, dim_chunks=1):
+        self.rank, self.world, self.group, self.dim_chunks = rank, world, group, dim_chunks
+        self.row_bounds = partition_rows_by_nnz(rowPtr, world) if row_bounds is None else torch.as_tensor(row_bounds).long()
+        self.col_bounds = partition_rows_even(n_cols, world) if col_bounds is None else torch.as_tensor(col_bounds).long()
+        if int(self.col_bounds[-1]) != n_cols or int(self.row_bounds[-1]) != len(rowPtr) - 1:
+            raise ValueError("bounds do not cover the matrix")
+        self.max_rows = int((self.col_bounds[1:] - self.col_bounds[:-1]).max())
+        lo, hi = int(self.row_bounds[rank]), int(self.row_bounds[rank + 1])
+        self.lo, self.hi = lo, hi
+        rp, ci, v = extract_rows(rowPtr, colIdx, val, lo, hi)
+        self.rowPtr = rp.to(device)
+        self.colIdx = remap_columns(ci.to(device), self.col_bounds, self.max_rows)
+        self.val = v.to(device)
+        self.device = torch.device(device)
+        self.my_cols = (int(self.col_bounds[rank]), int(self.col_bounds[rank + 1]))
+        if local_spmm is None:
+            from . import ops
+
+            def local_spmm(out, B, rowPtr, colIdx, val):
+                return ops.spmm_into(out, B, rowPtr, colIdx, val)
+        self.local_spmm = local_spmm
+        self._side = torch.cuda.Stream() if (self.device.type == "cuda" and dim_chunks > 1) else None
+
+    @property
+    def local_rows(self):
+        return self.hi - self.lo
+
+    def _gather(self, shard_slice):
+        """Padded all-gather of one [rows, d] block of the dense operand -> [world*max_rows, d]."""
+        import torch.distributed as dist
+
+        rows, d = shard_slice.shape
+        padded = shard_slice
+        if rows != self.max_rows or not shard_slice.is_contiguous():
+            padded = torch.zeros(self.max_rows, d, dtype=shard_slice.dtype, device=shard_slice.device)
+            padded[:rows] = shard_slice
+        full = torch.empty(self.world * self.max_rows, d, dtype=shard_slice.dtype, device=shard_slice.device)
+        if self.world == 1:
+            full.copy_(padded)
+        else:
+            dist.all_gather_into_tensor(full, padded, group=self.group)
+        return full
+
+    def forward(self, B_shard, out=None):
+        """B_shard: this rank's rows [col_bounds[rank], col_bounds[rank+1]) of the dense operand.
+        Returns this rank's rows of C = A B."""
+        if B_shard.shape[0] != self.my_cols[1] - self.my_cols[0]:
+            raise ValueError("dense shard has %d rows, expected %d" % (B_shard.shape[0], self.my_cols[1] - self.my_cols[0]))
+        dim = B_shard.shape[1]
+        if out is None:
+            out = torch.empty(self.local_rows, dim, dtype=B_shard.dtype, device=B_shard.device)
+        k = max(1, min(self.dim_chunks, dim // 4)) if self.dim_chunks > 1 else 1
+        if k == 1:
+            self.local_spmm(out, self._gather(B_shard), self.rowPtr, self.colIdx, self.val)
+            return out
+        # dim slices, multiples of 4 columns so that 128-bit loads stay possible
+        step = ((dim + k - 1) // k + 3) // 4 * 4
+        slices = [(c0, min(dim, c0 + step)) for c0 in range(0, dim, step)]
+        main = torch.cuda.current_stream()
+        gathered, events = [None] * len(slices), [None] * len(slices)
+
+        def issue(i):
+            c0, c1 = slices[i]
+            self._side.wait_stream(main)
+            with torch.cuda.stream(self._side):
+                gathered[i] = self._gather(B_shard[:, c0:c1])
+                events[i] = torch.cuda.Event()
+                events[i].record(self._side)
+
+        issue(0)
+        for i, (c0, c1) in enumerate(slices):
+            if i + 1 < len(slices):
+                issue(i + 1)
+            main.wait_event(events[i])
+            self.local_spmm(out[:, c0:c1], gathered[i], self.rowPtr, self.colIdx, self.val)
+            gathered[i].record_stream(main)
+        return out
+
+    def forward_replicated(self, B_full, out=None):
+        """SpMM against a dense operand every rank already holds in full (no exchange)."""
+        if out is None:
+            out = torch.empty(self.local_rows, B_full.shape[1], dtype=B_full.dtype, device=B_full.device)
+        if not hasattr(self, "_colIdx_global"):
+            raise RuntimeError("call keep_global_columns() at set-up to use a replicated operand")
+        self.local_spmm(out, B_full, self.rowPtr, self._colIdx_global, self.val)
+        return out
+
+    def keep_global_columns(self, colIdx_global_shard):
+        self._colIdx_global = colIdx_global_shard.to(self.device)
+        return self

@@ -147,14 +147,15 @@ def test_spmm_explicit_configs(dev, oracle, mats):
     d = m.to(dev)
     rps, tr = ops.split_csr(m.rowPtr, 32)
     rps, tr = rps.to(dev), tr.to(dev)
-    for dim in (16, 64, 96, 128, 256):
+    for dim in (16, 48, 64, 96, 128, 256):
         B = dense(m.n_cols, dim, 400 + dim)
         want = oracle.spmm_csr(rp, ci, v, B.numpy())
         Bd = B.to(dev)
         for lpr in (2, 4, 8, 16, 32):
             for vw in (1, 2, 4):
-                for thr, rpg in ((128, 1), (256, 4), (256, 16)):
-                    cfg = _lib.make_cfg(lanes_per_row=lpr, vec_width=vw, cta_threads=thr, rows_per_group=rpg)
+                for thr, rpg, mlp in ((128, 1, 4), (256, 4, 8), (256, 16, 16), (256, 2, 2)):
+                    cfg = _lib.make_cfg(lanes_per_row=lpr, vec_width=vw, cta_threads=thr, rows_per_group=rpg,
+                                        gather_batch=mlp)
                     out = torch.full((m.n_rows, dim), float("nan"), device=dev)
                     ops.spmm_into(out, Bd, d.rowPtr, d.colIdx, d.val, cfg=cfg)
                     close(out, want)

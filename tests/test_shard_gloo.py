@@ -1,0 +1,89 @@
+"""CPU tests of the multi-GPU row sharding with a 2-rank gloo group: partitioning, the padded
+all-gather layout and the column remap.  The local product is computed with the CPU oracle
+here (the CUDA kernel takes its place on GPUs; the exchange logic is identical)."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from paramspmm_ae_b200 import shard, synth
+
+
+def test_partition_balances_nnz():
+    m = synth.powerlaw_graph(5000, 40000, seed=3)
+    for world in (1, 2, 4, 8):
+        b = shard.partition_rows_by_nnz(m.rowPtr, world)
+        assert b[0] == 0 and b[-1] == m.n_rows and bool((b[1:] >= b[:-1]).all())
+        per = [int(m.rowPtr[b[p + 1]] - m.rowPtr[b[p]]) for p in range(world)]
+        assert sum(per) == m.nnz
+        max_row = int((m.rowPtr[1:] - m.rowPtr[:-1]).max())
+        assert max(per) <= m.nnz / world + max_row
+    # degenerate inputs
+    assert shard.partition_rows_by_nnz(torch.zeros(5, dtype=torch.int32), 3).tolist() == [0, 0, 0, 4]
+
+
+def test_extract_and_remap():
+    m = synth.uniform_rows(50, 4, seed=1)
+    rp, ci, v = shard.extract_rows(m.rowPtr, m.colIdx, m.val, 10, 30)
+    assert rp[0] == 0 and rp[-1] == 80 and ci.shape[0] == 80
+    cb = torch.tensor([0, 13, 50])
+    r = shard.remap_columns(torch.tensor([0, 12, 13, 49], dtype=torch.int32), cb, 37)
+    assert r.tolist() == [0, 12, 37, 37 + 36]
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port, dim_chunks, q):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from oracle import oracle as orc
+        m = synth.powerlaw_graph(1201, 9000, seed=7)          # same seed on every rank
+        B = synth.dense_uniform(m.n_cols, 24, 5)
+
+        def local_spmm(out, Bfull, rowPtr, colIdx, val):
+            out.copy_(torch.from_numpy(orc.spmm_csr(rowPtr.numpy(), colIdx.numpy(), val.numpy(),
+                                                    np.ascontiguousarray(Bfull.numpy()))))
+            return out
+
+        row_b = shard.partition_rows_by_nnz(m.rowPtr, world)
+        op = shard.ShardedSpMM(m.rowPtr, m.colIdx, m.val, m.n_cols, rank, world, row_bounds=row_b,
+                               col_bounds=row_b, device="cpu", local_spmm=local_spmm, dim_chunks=1)
+        lo, hi = op.my_cols
+        C_local = op.forward(B[lo:hi].contiguous())
+        want = orc.spmm_csr(*m.numpy(), B.numpy())[op.lo: op.hi]
+        ok = np.allclose(C_local.numpy(), want, rtol=1e-5, atol=1e-5)
+        # a second layer: the output shard is the next dense shard (row_bounds == col_bounds)
+        C2 = op.forward(C_local)
+        want2 = orc.spmm_csr(*m.numpy(), orc.spmm_csr(*m.numpy(), B.numpy()))[op.lo: op.hi]
+        ok2 = np.allclose(C2.numpy(), want2, rtol=1e-4, atol=1e-4)
+        q.put((rank, bool(ok), bool(ok2), op.local_rows))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_sharded_spmm_two_layers_gloo(world):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, 1, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=120) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert all(r[1] and r[2] for r in res), res
+    assert sum(r[3] for r in res) == 1201
