@@ -41,6 +41,8 @@ def parse():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
+    ap.add_argument("--workload", default="c2_dim_sweep", choices=["c2_dim_sweep", "c4_agnn_layer", "c3_gcn"],
+                    help="c2_dim_sweep is the benchmark proper; the others are one-GPU side measurements")
     ap.add_argument("--rows", type=int, default=N_ROWS, help="rows per matrix (smaller for quick checks)")
     ap.add_argument("--dims", type=int, nargs="*", default=DIMS)
     ap.add_argument("--e2e-steps", type=int, default=2)
@@ -185,6 +187,19 @@ def main():
     from paramspmm_ae_b200 import _lib, decider, ops, synth
 
     _lib.lib()  # no CUDA library, no benchmark
+    if args.workload != "c2_dim_sweep":
+        from paramspmm_ae_b200 import workloads
+        if args.workload == "c4_agnn_layer":
+            r = workloads.agnn_layer(iters=max(3, args.steps))
+            line = {"metric": "AGNN layer (SDDMM, scale, SpMM) GFLOP/s (2*nnz*dim/t per kernel)",
+                    "value": 2 * 2.0 * r["nnz"] * r["dim"] / r["layer_sddmm_scale_spmm_ms"] / 1e6, "unit": "GFLOP/s"}
+        else:
+            r = workloads.gcn_forward_backward(iters=max(2, min(args.steps, 5)))
+            line = {"metric": "GCN 3-layer forward+backward ms/step", "value": r["ms_per_step"], "unit": "ms",
+                    "higher_is_better": False}
+        line.update({"n_gpus": 1, "dtype": "f32", "data": "synthetic", "config": {"workload": args.workload}, "detail": r})
+        print(json.dumps(line))
+        return
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))

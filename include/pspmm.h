@@ -22,6 +22,7 @@
 #ifndef PSPMM_H
 #define PSPMM_H
 
+#include <stddef.h>
 #include <stdint.h>
 
 #ifdef __cplusplus
@@ -139,6 +140,21 @@ PSPMM_API int pspmm_genmask(const int32_t *rowPtr_b, const int32_t *rowPtr, cons
 PSPMM_API int pspmm_split_count(const int32_t *rowPtr, int64_t n_rows, int32_t granularity, int64_t *n_seg);
 PSPMM_API int pspmm_split_csr(const int32_t *rowPtr, int64_t n_rows, int32_t granularity,
                     int32_t *rowPtr_split, int32_t *target_row, int64_t n_seg);
+
+/*
+ * The same partition built on the GPU from a device-resident rowPtr (device arrays in, device
+ * arrays out; bit-exact with pspmm_split_csr, hence with SpMM/SpMM.cpp:15-75).  The kernels
+ * need scratch memory for per-tile offsets: pspmm_split_device_scratch_bytes() tells how much
+ * for a row count, the caller provides it (8-byte aligned device memory).
+ * pspmm_split_count_device copies the piece count back and therefore synchronises `stream`;
+ * pspmm_split_csr_device only enqueues work.
+ */
+PSPMM_API int pspmm_split_device_scratch_bytes(int64_t n_rows, size_t *bytes);
+PSPMM_API int pspmm_split_count_device(const int32_t *rowPtr, int64_t n_rows, int32_t granularity,
+                                       void *scratch, size_t scratch_bytes, int64_t *n_seg, void *stream);
+PSPMM_API int pspmm_split_csr_device(const int32_t *rowPtr, int64_t n_rows, int32_t granularity,
+                                     int32_t *rowPtr_split, int32_t *target_row, int64_t n_seg,
+                                     void *scratch, size_t scratch_bytes, void *stream);
 
 /*
  * Host-side CSR -> V x 1 block CSR, laid out exactly as scipy's tobsr((V,1)) (which the

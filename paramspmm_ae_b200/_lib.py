@@ -54,6 +54,9 @@ _SIGNATURES = {
     "pspmm_genmask": [_vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp],
     "pspmm_split_count": [_vp, _i64, _i32, ctypes.POINTER(_i64)],
     "pspmm_split_csr": [_vp, _i64, _i32, _vp, _vp, _i64],
+    "pspmm_split_device_scratch_bytes": [_i64, ctypes.POINTER(ctypes.c_size_t)],
+    "pspmm_split_count_device": [_vp, _i64, _i32, _vp, ctypes.c_size_t, ctypes.POINTER(_i64), _vp],
+    "pspmm_split_csr_device": [_vp, _i64, _i32, _vp, _vp, _i64, _vp, ctypes.c_size_t, _vp],
     "pspmm_bcsr_count": [_vp, _vp, _i64, _i64, _i32, _vp, ctypes.POINTER(_i64)],
     "pspmm_bcsr_fill": [_vp, _vp, _vp, _i64, _i64, _i32, _vp, _vp, _vp],
     "pspmm_profile_spmm": [_vp, _vp, _vp, _i32, _vp, _vp, _i64, _i64, _i64, _i32, _i64, _i64, _cfgp,

@@ -372,6 +372,7 @@ static int sddmm_launch(const int32_t *segPtr, const int32_t *target_row, int64_
     a.ldB = ldB;
     a.nvec = dim / s.vw;
     a.rows_per_group = s.rpg;
+    a.keep_fraction = 1.0f;  // the row count of B is not part of the call: no partial pinning
     const int64_t per_cta = (int64_t)(s.threads / s.lpr) * s.rpg;
     const int64_t gx = (n_seg + per_cta - 1) / per_cta;
     if (gx > INT32_MAX)

@@ -50,6 +50,7 @@ struct SddmmArgs {
     int64_t ldA, ldB;
     int32_t nvec;
     int32_t rows_per_group;
+    float keep_fraction;
 };
 
 // Resolved launch shape.

@@ -44,14 +44,6 @@ struct SpmmTile {
     static constexpr int GROUP_WORDS = HEAD_WORDS + CAP * (1 + V);
 };
 
-// Address of a lane's slice of dense row c: base + c * ld_bytes as one 32x32+64 multiply-add.
-__device__ __forceinline__ const float *row_slice(const char *base, int c, unsigned ld_bytes)
-{
-    unsigned long long r;
-    asm("mad.wide.u32 %0, %1, %2, %3;" : "=l"(r) : "r"((unsigned)c), "r"(ld_bytes), "l"(base));
-    return reinterpret_cast<const float *>(r);
-}
-
 // One batch of UU entries starting at shared-memory index e: gathers first, FMAs after.
 template <int UU, int LPR, int VW, int CF, int V>
 __device__ __forceinline__ void spmm_batch(const int *ent, int e, const char *const (&bcol)[CF],

@@ -81,6 +81,14 @@ __device__ __forceinline__ void st_vec_hint(float *p, const float *v, unsigned l
     }
 }
 
+// Address of a lane's slice of dense row c: base + c * ld_bytes as one 32x32+64 multiply-add.
+__device__ __forceinline__ const float *row_slice(const char *base, int c, unsigned ld_bytes)
+{
+    unsigned long long r;
+    asm("mad.wide.u32 %0, %1, %2, %3;" : "=l"(r) : "r"((unsigned)c), "r"(ld_bytes), "l"(base));
+    return reinterpret_cast<const float *>(r);
+}
+
 // Predicated read-only load: returns zeros and touches no memory when `on` is false.  Written
 // as one predicated PTX instruction so that a batch of these stays straight-line code and the
 // loads of the whole batch can be in flight together (a C++ conditional around a load may

@@ -99,6 +99,25 @@ def split_csr_par(rowPtr, row_split_offset, granularity):
     return split_csr(rowPtr, granularity)
 
 
+def split_csr_device(rowPtr, granularity):
+    """PCSR partition of a CUDA int32 rowPtr, built on the device -> [rowPtr_split, target_row]
+    (CUDA tensors; bit-exact with :func:`split_csr`).  Reads the piece count back, so it
+    synchronises the current stream once."""
+    _check_cuda(rowPtr, "rowPtr", torch.int32, 1)
+    n = rowPtr.shape[0] - 1
+    need = ctypes.c_size_t(0)
+    check(lib().pspmm_split_device_scratch_bytes(n, ctypes.byref(need)))
+    scratch = torch.empty((need.value + 7) // 8, dtype=torch.int64, device=rowPtr.device)
+    nseg = ctypes.c_int64(0)
+    check(lib().pspmm_split_count_device(_ptr(rowPtr), n, int(granularity), _ptr(scratch), need.value,
+                                         ctypes.byref(nseg), _stream()))
+    rps = torch.empty(nseg.value + 1, dtype=torch.int32, device=rowPtr.device)
+    tr = torch.empty(nseg.value, dtype=torch.int32, device=rowPtr.device)
+    check(lib().pspmm_split_csr_device(_ptr(rowPtr), n, int(granularity), _ptr(rps), _ptr(tr), nseg.value,
+                                       _ptr(scratch), need.value, _stream()))
+    return [rps, tr]
+
+
 def bcsr_from_csr(rowPtr, colIdx, val, n_cols, V=2):
     """CSR (CPU tensors) -> V x 1 block CSR laid out as scipy's tobsr((V,1)) does
     (what graph_input.py:245-266 of the reference builds)."""

