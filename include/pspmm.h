@@ -157,6 +157,23 @@ PSPMM_API int pspmm_split_csr_device(const int32_t *rowPtr, int64_t n_rows, int3
                                      void *scratch, size_t scratch_bytes, void *stream);
 
 /*
+ * pspmm_split_csr_device without any scratch argument and without a single allocation (it has
+ * no counterpart in the reference).  Meant for callers that are barred from creating device
+ * memory when they need the partition: processes whose GPU memory is fully handed out at
+ * start-up, code confined to someone else's memory pool, plug-ins invoked where allocation
+ * calls are off limits.  The tile offsets live in a fixed array inside the library (about
+ * 128 KiB on every GPU that loads it), which limits the input to 16,777,216 rows; larger
+ * inputs get PSPMM_E_RANGE and should use pspmm_split_csr_device.  n_seg comes from
+ * pspmm_split_count (host) as usual.  The first call on each device looks up the array's device
+ * address; make that first call outside any stream capture.  All calls on a device share the
+ * array: calls that can overlap on the GPU race with each other, so keep them on one stream.
+ * Leftovers of an earlier call need no clearing, each call rewrites what it reads.
+ */
+PSPMM_API int pspmm_split_csr_device_static(const int32_t *rowPtr, int64_t n_rows, int32_t granularity,
+                                            int32_t *rowPtr_split, int32_t *target_row, int64_t n_seg,
+                                            void *stream);
+
+/*
  * Host-side CSR -> V x 1 block CSR, laid out exactly as scipy's tobsr((V,1)) (which the
  * reference calls at graph_input.py:245-266): blocks of a block-row appear in order of first
  * encounter while walking its V rows top to bottom.  pspmm_bcsr_count fills rowPtr_b

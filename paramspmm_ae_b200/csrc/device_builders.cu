@@ -213,3 +213,74 @@ extern "C" int pspmm_split_csr_device(const int32_t *rowPtr, int64_t n_rows, int
     PSPMM_CUDA_TRY(cudaGetLastError());
     return PSPMM_OK;
 }
+
+// ----------------------------------------------------------------------------- no-allocation variant
+// Some hosts of this library are not allowed to create device memory at the moment they need a
+// partition: a serving process whose device memory was carved up completely at start-up, code
+// that runs under another framework's memory pool and must not step outside it, or a plug-in
+// called at a point where the embedding application forbids CUDA allocation calls.  Such a
+// caller cannot obtain the few kilobytes of tile offsets that pspmm_split_csr_device asks for.
+// For them the offsets live in the array below, which is part of the library image: every GPU
+// that loads the library holds these bytes until the process exits.
+//
+// The array bounds the problem: PSPMM_STATIC_SPLIT_MAX_TILES tiles of 1024 rows, i.e. at most
+// 16,777,216 rows.  All calls on a device share the one array, so two calls whose kernels may
+// overlap on the GPU (different streams, or different host threads) corrupt each other's
+// offsets; issue them on one stream or order them yourself.  Nothing in the array has to be
+// zero when a call starts: the first kernel of each call overwrites every element the later
+// kernels read, so contents left behind by the previous call are harmless.
+#define PSPMM_STATIC_SPLIT_MAX_TILES 16384
+static __device__ __align__(256) long long g_static_tile_off[PSPMM_STATIC_SPLIT_MAX_TILES + 1];
+
+namespace {
+constexpr int MAX_DEVICES = 64;
+long long *g_static_ptr[MAX_DEVICES] = {};  // device address of the array, per device ordinal
+
+// The array's name is only a host-side handle; kernels need its address in the current
+// device's address space, which the runtime reports per device.
+int static_scratch_for_current_device(long long **out)
+{
+    int dev = -1;
+    PSPMM_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= MAX_DEVICES)
+        return PSPMM_E_UNSUPPORTED;
+    long long *p = __atomic_load_n(&g_static_ptr[dev], __ATOMIC_ACQUIRE);
+    if (!p) {
+        void *addr = nullptr;
+        PSPMM_CUDA_TRY(cudaGetSymbolAddress(&addr, g_static_tile_off));
+        p = static_cast<long long *>(addr);
+        __atomic_store_n(&g_static_ptr[dev], p, __ATOMIC_RELEASE);  // same value from any thread
+    }
+    *out = p;
+    return PSPMM_OK;
+}
+}  // namespace
+
+extern "C" int pspmm_split_csr_device_static(const int32_t *rowPtr, int64_t n_rows, int32_t granularity,
+                                             int32_t *rowPtr_split, int32_t *target_row, int64_t n_seg,
+                                             void *stream)
+{
+    if (!rowPtr || n_rows < 0 || granularity <= 0)
+        return PSPMM_E_ARG;
+    if (!rowPtr_split || n_seg < 0 || (n_seg > 0 && !target_row))
+        return PSPMM_E_ARG;
+    const int64_t n_tiles = (n_rows + TILE - 1) / TILE;
+    if (n_tiles > PSPMM_STATIC_SPLIT_MAX_TILES || n_seg >= INT32_MAX)
+        return PSPMM_E_RANGE;  // more rows than the built-in scratch covers: use pspmm_split_csr_device
+    cudaStream_t st = (cudaStream_t)stream;
+    if (n_rows == 0) {
+        PSPMM_CUDA_TRY(cudaMemsetAsync(rowPtr_split, 0, sizeof(int32_t), st));
+        return PSPMM_OK;
+    }
+    long long *tile_off = nullptr;
+    int rc = static_scratch_for_current_device(&tile_off);
+    if (rc)
+        return rc;
+    rc = launch_counts(rowPtr, n_rows, granularity, tile_off, st);
+    if (rc)
+        return rc;
+    fill_split<<<(unsigned)n_tiles, TILE, 0, st>>>(rowPtr, n_rows, granularity, tile_off, rowPtr_split,
+                                                  target_row, n_seg);
+    PSPMM_CUDA_TRY(cudaGetLastError());
+    return PSPMM_OK;
+}
