@@ -33,6 +33,13 @@ NNZ_PER_ROW = 16
 DIMS = list(range(16, 257, 16))
 MATRICES = ("uniform", "banded", "rmat")
 FALLBACK_HBM_GBS = 6650.0
+# dram__bytes_read.sum + dram__bytes_write.sum per launch from `ncu --set full` captures of these
+# launches at 1,000,000 rows (summaries with the commands: profiles/spmm_seg_kernel_c2_*.md).
+NCU_DRAM_BYTES = {
+    ("uniform", 64): 3.172e9, ("banded", 64): 0.602e9, ("rmat", 64): 0.715e9,
+    ("uniform", 128): 7.447e9, ("banded", 128): 1.116e9, ("rmat", 128): 2.014e9,
+    ("uniform", 256): 16.086e9, ("banded", 256): 2.149e9, ("rmat", 256): 5.775e9,
+}
 
 
 def parse():
@@ -293,16 +300,10 @@ def main():
                 "bytes_model": "4(n+1)+8nnz+4*dim*n_cols+4*dim*n_rows (+8S for a split layout)",
                 "best_frac": max(s["frac"] for s in sweep),
                 "rmat_dim_ge_64_frac": [s["frac"] for s in sweep if s["matrix"] == "rmat" and s["dim"] >= 64]}
-    tr_path = os.path.join(ROOT, "profiles", "spmm_dram_traffic.json")
-    if os.path.exists(tr_path):
-        try:
-            tj = json.load(open(tr_path))
-            key = "%s_dim%d" % (sweep[top]["matrix"], sweep[top]["dim"])
-            if key in tj:
-                roofline["traffic"] = tj[key]["bytes_per_launch"]
-                roofline["traffic_source"] = tj[key].get("source")
-        except Exception:
-            pass
+    key = (sweep[top]["matrix"], sweep[top]["dim"])
+    if n == N_ROWS and key in NCU_DRAM_BYTES:
+        roofline["traffic"] = NCU_DRAM_BYTES[key]
+        roofline["traffic_source"] = "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch of this case"
 
     # ---- end to end: host buffers in, host buffer out, copies inside the timed region
     e2e = None
