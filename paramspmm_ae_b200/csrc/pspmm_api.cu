@@ -157,20 +157,28 @@ __global__ void __launch_bounds__(256)
 zero_shared_rows_kernel(const int32_t *__restrict__ target_row, int64_t n_seg, int64_t n_out, int rpg,
                         int V, float *C, int64_t ldC, int dim, int vecok)
 {
-    __shared__ long long q_lo[512], q_hi[512];
+    __shared__ int q_lo[512], q_hi[512];
     __shared__ int q_n;
     if (threadIdx.x == 0)
         q_n = 0;
     __syncthreads();
     const int64_t s = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     const int lane = threadIdx.x & 31;
-    int64_t one = -1;  // a straddled row to zero, or -1
-    if (s < n_seg) {
-        const int64_t me = target_row[s];
-        const int64_t next = s + 1 < n_seg ? (int64_t)target_row[s + 1] : n_out;
-        if (s > 0 && s % rpg == 0 && (int64_t)target_row[s - 1] == me) {
+    const bool in = s < n_seg;
+    // Own, previous and next target row: one coalesced load, neighbours by shuffle, warp edges by
+    // a second load.
+    const int me = in ? __ldg(target_row + s) : (int)n_out;
+    int prev = __shfl_up_sync(PSPMM_FULL_MASK, me, 1);
+    int next = __shfl_down_sync(PSPMM_FULL_MASK, me, 1);
+    if (lane == 0)
+        prev = (in && s > 0) ? __ldg(target_row + s - 1) : -1;
+    if (lane == 31)
+        next = (s + 1 < n_seg) ? __ldg(target_row + s + 1) : (int)n_out;
+    int one = -1;  // a straddled row to zero, or -1
+    if (in) {
+        if (s > 0 && s % rpg == 0 && prev == me) {
             const int64_t before = s - rpg - 1;  // last segment ahead of the previous boundary
-            if (before < 0 || (int64_t)target_row[before] != me)
+            if (before < 0 || __ldg(target_row + before) != me)
                 one = me;
         }
         if (next - me - 1 > PSPMM_GAP_MAX) {
@@ -184,29 +192,47 @@ zero_shared_rows_kernel(const int32_t *__restrict__ target_row, int64_t n_seg, i
             q_hi[i] = me;
         }
     }
-    auto zero_row = [&](int64_t r) {
+    // Straddled rows: the finding warp zeroes them, 32 / lanes_per_row rows per step.
+    const int lpr_z = vecok ? ((dim + 3) / 4 < 32 ? (dim + 3) / 4 : 32) : 32;  // lanes that cover one row
+    int lanes_row = 1;
+    while (lanes_row < lpr_z)
+        lanes_row <<= 1;
+    const int rows_step = 32 / lanes_row;
+    const int sub = lane / lanes_row, sl = lane % lanes_row;
+    auto zero_part = [&](int64_t r, int l, int nl) {  // lanes l of nl zero row r
         float *row = C + r * ldC;
         if (vecok) {
-            for (int j = lane * 4; j < dim; j += 128)
+            for (int j = l * 4; j < dim; j += nl * 4)
                 *reinterpret_cast<float4 *>(row + j) = make_float4(0.f, 0.f, 0.f, 0.f);
         } else {
-            for (int j = lane; j < dim; j += 32)
+            for (int j = l; j < dim; j += nl)
                 row[j] = 0.f;
         }
     };
     unsigned todo = __ballot_sync(PSPMM_FULL_MASK, one >= 0);
     while (todo) {
-        const int src = __ffs(todo) - 1;
-        todo &= todo - 1;
-        const int64_t r = __shfl_sync(PSPMM_FULL_MASK, one, src);
-        for (int w = 0; w < V; ++w)
-            zero_row(r * V + w);
+        // pick the sub-th pending lane for this sub-group
+        unsigned t = todo;
+        int src = -1;
+        for (int k = 0; k <= sub && t; ++k) {
+            src = __ffs(t) - 1;
+            t &= t - 1;
+        }
+        const bool have = __popc(todo) > sub;
+        const int r = __shfl_sync(PSPMM_FULL_MASK, one, have ? src : 0);
+        if (have)
+            for (int w = 0; w < V; ++w)
+                zero_part((int64_t)r * V + w, sl, lanes_row);
+        for (int k = 0; k < rows_step && todo; ++k)
+            todo &= todo - 1;
     }
-    __syncthreads();
+    if (__syncthreads_or(q_n > 0) == 0)
+        return;
+    // Long uncovered runs: the whole CTA zeroes them, rows_step * warps rows per step.
     const int warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
     for (int i = 0; i < q_n; ++i)
-        for (int64_t r = q_lo[i] * V + warp; r < q_hi[i] * V; r += nwarp)
-            zero_row(r);
+        for (int64_t r = (int64_t)q_lo[i] * V + warp * rows_step + sub; r < (int64_t)q_hi[i] * V; r += nwarp * rows_step)
+            zero_part(r, sl, lanes_row);
 }
 
 // ----------------------------------------------------------------------------- SpMM

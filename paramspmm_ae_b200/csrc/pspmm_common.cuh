@@ -9,7 +9,7 @@
 #define PSPMM_FULL_MASK 0xffffffffu
 #define PSPMM_MAX_CF 8
 #define PSPMM_RPG_MAX 16  // most consecutive segments one lane group owns
-#define PSPMM_GAP_MAX 16  // longest run of uncovered rows the SpMM kernel zeroes by itself
+#define PSPMM_GAP_MAX 256  // longest run of uncovered rows the SpMM kernel zeroes by itself
 
 // Records the CUDA error text for pspmm_last_cuda_error() and returns PSPMM_E_CUDA.
 int pspmm_note_cuda_error(cudaError_t e);
