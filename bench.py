@@ -48,9 +48,11 @@ def parse():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
-    ap.add_argument("--workload", default="c2_dim_sweep", choices=["c2_dim_sweep", "c4_agnn_layer", "c3_gcn"],
+    ap.add_argument("--workload", default="c2_dim_sweep", choices=["c2_dim_sweep", "c4_agnn_layer", "c3_gcn", "c5_scaleout"],
                     help="c2_dim_sweep is the benchmark proper; the others are one-GPU side measurements")
     ap.add_argument("--rows", type=int, default=N_ROWS, help="rows per matrix (smaller for quick checks)")
+    ap.add_argument("--c5-scale", type=int, default=24, help="c5_scaleout: log2 of the node count")
+    ap.add_argument("--c5-nnz", type=int, default=512_000_000, help="c5_scaleout: entries of the global matrix")
     ap.add_argument("--dims", type=int, nargs="*", default=DIMS)
     ap.add_argument("--e2e-steps", type=int, default=2)
     ap.add_argument("--cpu-seconds", type=float, default=15.0)
@@ -194,6 +196,26 @@ def main():
     from paramspmm_ae_b200 import _lib, decider, ops, synth
 
     _lib.lib()  # no CUDA library, no benchmark
+    if args.workload == "c5_scaleout":
+        from paramspmm_ae_b200 import workloads
+        world = int(os.environ.get("WORLD_SIZE", "1"))
+        rank = int(os.environ.get("RANK", "0"))
+        local = int(os.environ.get("LOCAL_RANK", "0"))
+        torch.cuda.set_device(local)
+        if world > 1:
+            dist.init_process_group(backend="nccl", device_id=torch.device("cuda", local))
+        r = workloads.scaleout_spmm(scale=args.c5_scale, nnz=args.c5_nnz, iters=max(3, args.steps), rank=rank,
+                                    world=world, device="cuda:%d" % local)
+        if rank == 0:
+            print(json.dumps({"metric": "row-sharded SpMM GFLOP/s (2*nnz*dim/t), all-gather of B included",
+                              "value": max(r["allgather_overlapped_gflops"], r["allgather_spmm_gflops"]),
+                              "unit": "GFLOP/s", "n_gpus": world,
+                              "higher_is_better": True, "scaling": "strong", "dtype": "f32", "data": "synthetic",
+                              "config": {"workload": "c5_scaleout", "scale": args.c5_scale, "nnz": r["nnz"],
+                                         "dim": r["dim"]}, "detail": r}))
+        if world > 1:
+            dist.destroy_process_group()
+        return
     if args.workload != "c2_dim_sweep":
         from paramspmm_ae_b200 import workloads
         if args.workload == "c4_agnn_layer":

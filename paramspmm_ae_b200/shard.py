@@ -76,13 +76,31 @@ class ShardedSpMM:
         self.val = v.to(device)
         self.device = torch.device(device)
         self.my_cols = (int(self.col_bounds[rank]), int(self.col_bounds[rank + 1]))
-        if local_spmm is None:
-            from . import ops
-
-            def local_spmm(out, B, rowPtr, colIdx, val):
-                return ops.spmm_into(out, B, rowPtr, colIdx, val)
-        self.local_spmm = local_spmm
+        self.local_spmm = local_spmm if local_spmm is not None else self._planned_spmm()
         self._side = torch.cuda.Stream() if (self.device.type == "cuda" and dim_chunks > 1) else None
+
+    def _planned_spmm(self):
+        """The CUDA operator with the configuration the decider picks for this shard's row-length
+        statistics and the (slice of the) dense width; a split layout, when chosen, is built once on
+        the device from the shard's row pointer and kept."""
+        from . import _lib, decider, ops
+
+        stats = decider.row_stats(self.rowPtr)
+        layouts = {}
+
+        def local_spmm(out, B, rowPtr, colIdx, val):
+            p = decider.choose(stats, B.shape[1])
+            cfg = _lib.make_cfg(**p.kernel_cfg())
+            if p["if_split"]:
+                g = int(p["granularity"])
+                if g not in layouts:
+                    layouts[g] = ops.split_csr_device(rowPtr, g)
+                rps, tr = layouts[g]
+                return ops.spmm_into(out, B, rps, colIdx, val, target_row=tr, n_out_rows=rowPtr.shape[0] - 1,
+                                     cfg=cfg)
+            return ops.spmm_into(out, B, rowPtr, colIdx, val, cfg=cfg)
+
+        return local_spmm
 
     @property
     def local_rows(self):

@@ -151,3 +151,73 @@ def gcn_forward_backward(n=2_449_029, pairs=61_900_000, feats=100, hidden=256, c
     return {"n": n, "nnz": g.nnz, "generate_s": round(gen_s, 1), "ms_per_step": round(ms, 2),
             "loss": float(step()), "spmm_gflop_per_step": round(spmm_flops / 1e9, 1),
             "regime": decider.regime(stats)}
+
+
+def scaleout_spmm(scale=24, nnz=512_000_000, dim=128, seed=51, iters=5, warmup=2, rank=0, world=1,
+                  device="cuda:0", dim_chunks=4):
+    """Row-sharded SpMM of one global R-MAT matrix (strong scaling): every rank holds a contiguous,
+    nnz-balanced row block of A and the matching row block of the dense operand.
+
+    Three timings per rank (CUDA events on the launching stream, maximum over ranks):
+    the local SpMM against a replicated dense operand (no exchange), the all-gather of the dense
+    row blocks followed by the SpMM, and the same with the dense columns cut into `dim_chunks`
+    slices so that the gather of slice s+1 overlaps the SpMM of slice s.
+    Every rank generates the same global matrix from the seed and keeps only its rows.
+    """
+    import torch.distributed as dist
+    from .shard import ShardedSpMM
+
+    dev = torch.device(device)
+    t0 = time.time()
+    m = synth.rmat(scale, nnz, seed=seed, device=dev)
+    gen_s = time.time() - t0
+    n = m.n_rows
+    sh = ShardedSpMM(m.rowPtr, m.colIdx, m.val, n, rank, world, device=dev, dim_chunks=1)
+    a, b = int(m.rowPtr[sh.lo]), int(m.rowPtr[sh.hi])
+    sh.keep_global_columns(m.colIdx[a:b].clone())
+    nnz_total, nnz_local = m.nnz, b - a
+    del m
+    torch.cuda.empty_cache()
+    B_full = synth.dense_uniform(n, dim, seed + 1, dev)
+    c0, c1 = sh.my_cols
+    B_shard = B_full[c0:c1].clone()
+    out_rep = torch.empty(sh.local_rows, dim, device=dev)
+    out_ag = torch.empty(sh.local_rows, dim, device=dev)
+
+    def timed(fn):
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / iters], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    ms_rep = timed(lambda: sh.forward_replicated(B_full, out_rep))
+    ms_ag = timed(lambda: sh.forward(B_shard, out_ag))
+    # Hub rows of this matrix sum 10^5 and more terms, and the pieces of a split row arrive in a
+    # different order on every launch (REDs): the comparison allows for fp32 re-association.
+    tol = dict(rtol=1e-4, atol=2e-3)
+    torch.testing.assert_close(out_ag, out_rep, **tol)
+    sh.dim_chunks = dim_chunks
+    sh._side = torch.cuda.Stream()
+    out_ag.fill_(float("nan"))
+    ms_ov = timed(lambda: sh.forward(B_shard, out_ag))
+    torch.testing.assert_close(out_ag, out_rep, **tol)
+    gf = lambda ms: 2.0 * nnz_total * dim / ms / 1e6
+    by = 4 * (n + 1) + 8 * nnz_total + 4 * dim * n * 2
+    return {"n": n, "nnz": nnz_total, "nnz_local": nnz_local, "rows_local": sh.local_rows, "dim": dim,
+            "generate_s": round(gen_s, 1), "world": world,
+            "spmm_replicated_ms": round(ms_rep, 4), "allgather_spmm_ms": round(ms_ag, 4),
+            "allgather_overlapped_ms": round(ms_ov, 4), "dim_chunks": dim_chunks,
+            "spmm_replicated_gflops": round(gf(ms_rep), 1), "allgather_spmm_gflops": round(gf(ms_ag), 1),
+            "allgather_overlapped_gflops": round(gf(ms_ov), 1),
+            "compulsory_bytes_global": by, "spmm_replicated_gbs_global": round(by / ms_rep / 1e6, 1)}
