@@ -193,6 +193,30 @@ def sddmm_bcsr(rowPtr_b, colIdx_b, val_b, A, B, target_row=None):
     return out
 
 
+def agnn_aggregate(rowPtr, colIdx, A, B, beta=1.0, softmax=True):
+    """out_i = sum_j a_ij B_j over the stored pattern, a_ij = softmax_j(beta <A_i, B_j>) or, with
+    softmax=False, the raw scaled scores: the composition SDDMM -> ``* attention_w`` -> SpMM of the
+    reference's AGNN layer (gnn_conv.py:130-151), with the per-row edge softmax in between when
+    asked for.  Computed row by row in float64 (numpy), returned as float32."""
+    rowPtr, colIdx = np.asarray(rowPtr, dtype=np.int64), np.asarray(colIdx, dtype=np.int64)
+    A64, B64 = np.asarray(A, dtype=np.float64), np.asarray(B, dtype=np.float64)
+    n = rowPtr.shape[0] - 1
+    out = np.zeros((n, B64.shape[1]), dtype=np.float64)
+    for i in range(n):
+        lo, hi = rowPtr[i], rowPtr[i + 1]
+        if hi == lo:
+            continue
+        nb = B64[colIdx[lo:hi]]
+        s = beta * (nb @ A64[i])
+        if softmax:
+            w = np.exp(s - s.max())
+            w /= w.sum()
+        else:
+            w = s
+        out[i] = w @ nb
+    return out.astype(np.float32)
+
+
 def spmm_torch_cpu(rowPtr, colIdx, val, B, n_cols=None):
     """The reference's own acceptance oracle: torch.sparse.mm on a CSR tensor, CPU
     (verification.py:18-23, 44-46)."""

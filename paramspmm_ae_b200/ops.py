@@ -389,6 +389,53 @@ def vec_split_sddmm_profile(A, B, rowPtr_split, colIdx, val, target_row, nnz, CF
                    _sddmm(A, B, rowPtr_split, colIdx, val, target_row, _vec_size(val), CF, blkWarpNum, True))
 
 
+def agnn_fused(A, B, rowPtr, colIdx, beta=1.0, softmax=True, target_row=None, n_out_rows=None, out=None,
+               batch=0, lanes_per_row=0):
+    """out_i = sum_j a_ij B_j with a_ij = softmax_j(beta <A_i, B_j>) (or the raw scaled scores when
+    ``softmax`` is false) over the stored pattern, in one pass and without a per-edge array.
+
+    With ``softmax=False`` and ``A is B`` this equals the reference's AGNN forward composition
+    csr_sddmm -> ``* attention_w`` -> csr_spmm (gnn_conv.py:130-151).  ``rowPtr`` is the CSR row
+    pointer, or the split row pointer when ``target_row`` is given (then ``n_out_rows`` is
+    required).  dim must be a multiple of 4, at most 256.
+    """
+    _check_cuda(A, "A", torch.float32, 2)
+    _check_cuda(B, "B", torch.float32, 2)
+    _check_cuda(rowPtr, "rowPtr", torch.int32, 1)
+    _check_cuda(colIdx, "colIdx", torch.int32, 1)
+    if A.shape[1] != B.shape[1]:
+        raise RuntimeError("A and B must have the same width")
+    if A.stride(1) != 1 or B.stride(1) != 1:
+        raise RuntimeError("dense operands must be row-major")
+    dim = A.shape[1]
+    n_seg = rowPtr.shape[0] - 1
+    split = target_row is not None
+    if split:
+        _check_cuda(target_row, "target_row", torch.int32, 1)
+        if n_out_rows is None:
+            raise RuntimeError("n_out_rows is required for split layouts")
+    else:
+        n_out_rows = n_seg
+    if A.shape[0] < n_out_rows:
+        raise RuntimeError("A has fewer rows than the pattern")
+    if out is None:
+        out = torch.empty(n_out_rows, dim, dtype=torch.float32, device=A.device)
+    null = ctypes.c_void_p(0)
+    scratch, sbytes = None, 0
+    if split:
+        need = ctypes.c_size_t(0)
+        check(lib().pspmm_agnn_scratch_bytes(n_seg, dim, ctypes.byref(need)))
+        sbytes = need.value
+        scratch = torch.empty((sbytes + 15) // 16 * 4, dtype=torch.float32, device=A.device)
+    seg_ptr = _ptr(rowPtr)
+    check(lib().pspmm_agnn_fused_csr(null if split else seg_ptr, _ptr(colIdx), _ptr(A), _ptr(B), _ptr(out),
+                                     n_out_rows, colIdx.shape[0], dim, A.stride(0), B.stride(0), out.stride(0),
+                                     float(beta), 1 if softmax else 0, int(lanes_per_row), int(batch),
+                                     seg_ptr if split else null, _ptr(target_row) if split else null,
+                                     n_seg if split else 0, _ptr(scratch) if split else null, sbytes, _stream()))
+    return out
+
+
 def genmask(rowPtr_bcsr, rowPtr, blkval, nnz):
     """int32[nnz] map from CSR entry order to the flattened [nblk,2] block values
     (SDDMM/sddmm.cpp:663-673)."""

@@ -32,7 +32,7 @@ def _time_ms(fn, warmup=3, iters=10):
     return a.elapsed_time(b) / iters
 
 
-def agnn_layer(n=232_965, pairs=57_180_000, dim=64, seed=41, iters=10, grans=(0, 128, 256, 512), device="cuda:0"):
+def agnn_layer(n=232_965, pairs=57_180_000, dim=64, seed=41, iters=10, grans=(0, 128, 512, 1024, 2048, 4096), device="cuda:0"):
     dev = torch.device(device)
     t0 = time.time()
     g = synth.powerlaw_graph(n, pairs, seed=seed, device=dev, normalize=False)
@@ -108,6 +108,31 @@ def agnn_layer(n=232_965, pairs=57_180_000, dim=64, seed=41, iters=10, grans=(0,
                                   target_row=tr, n_out_rows=n)
     out["layer_granularity"] = gbest
     out["layer_sddmm_scale_spmm_ms"] = round(_time_ms(layer, iters=iters), 4)
+    # the same layer as ONE kernel (scores, optional edge softmax and aggregation in a single pass)
+    fused = []
+    want = Cl.clone()
+    for gran in grans:
+        if not gran:
+            continue
+        rps, tr = layouts[gran]
+        Cf = torch.empty(n, dim, device=dev)
+        for lanes, batch in ((16, 8), (8, 4), (4, 4)):
+            if gran != 1024 and (lanes, batch) != (4, 4):
+                continue  # the shape comparison on one partition length only
+            f_plain = lambda: ops.agnn_fused(X, X, rps, g.colIdx, beta, False, target_row=tr, n_out_rows=n,
+                                             out=Cf, batch=batch, lanes_per_row=lanes)
+            ms_plain = _time_ms(f_plain, iters=iters)
+            f_plain()
+            scale = float(want.abs().max())
+            torch.testing.assert_close(Cf, want, rtol=1e-4, atol=1e-5 * max(1.0, scale))
+            f_soft = lambda: ops.agnn_fused(X, X, rps, g.colIdx, beta, True, target_row=tr, n_out_rows=n,
+                                            out=Cf, batch=batch, lanes_per_row=lanes)
+            ms_soft = _time_ms(f_soft, iters=iters)
+            fused.append({"granularity": gran, "lanes_per_row": lanes, "batch": batch, "fused_ms": round(ms_plain, 4),
+                          "fused_softmax_ms": round(ms_soft, 4)})
+    out["fused"] = fused
+    out["fused_best_ms"] = min(f["fused_ms"] for f in fused)
+    out["fused_softmax_best_ms"] = min(f["fused_softmax_ms"] for f in fused)
     return out
 
 

@@ -356,3 +356,53 @@ def test_full_size_properties(dev):
     torch.testing.assert_close(cs, c1, rtol=1e-5, atol=1e-6 * scale * 50)
     s = torch.sparse_csr_tensor(m.rowPtr, m.colIdx, m.val, size=(n, n))
     torch.testing.assert_close(torch.sparse.mm(s, B1), c1, rtol=1e-5, atol=1e-6 * scale * 50)
+
+
+# ----------------------------------------------------------------------------- fused AGNN aggregation
+@pytest.mark.parametrize("dim", [4, 16, 32, 48, 64, 100, 128, 256])
+@pytest.mark.parametrize("softmax", [True, False])
+def test_agnn_fused_matches_the_oracle(dev, oracle, mats, dim, softmax):
+    """SDDMM -> scale -> (edge softmax) -> SpMM in one kernel, plain CSR and split layouts, against
+    the float64 row-by-row restatement."""
+    from paramspmm_ae_b200 import ops
+    for name in ("powerlaw", "rmat", "hub", "tiny"):
+        m = mats[name]
+        rp, ci, _ = m.numpy()
+        X = torch.nn.functional.normalize(dense(m.n_rows, dim, 900 + dim), dim=1)
+        beta = 1.7
+        want = oracle.agnn_aggregate(rp, ci, X.numpy(), X.numpy(), beta, softmax)
+        d, Xd = m.to(dev), X.to(dev)
+        for lanes, batch in ((0, 0), (4, 4), (8, 4), (8, 8), (16, 8), (16, 16), (32, 8), (32, 16)):
+            got = ops.agnn_fused(Xd, Xd, d.rowPtr, d.colIdx, beta, softmax, batch=batch, lanes_per_row=lanes)
+            close(got, want)
+        for gran in (3, 32):
+            rps, tr = ops.split_csr(m.rowPtr, gran)
+            got = torch.full((m.n_rows, dim), float("nan"), device=dev)
+            ops.agnn_fused(Xd, Xd, rps.to(dev), d.colIdx, beta, softmax, target_row=tr.to(dev),
+                           n_out_rows=m.n_rows, out=got)
+            close(got, want)
+
+
+def test_agnn_fused_equals_the_unfused_composition(dev, mats):
+    """With softmax off and A == B the fused kernel is the reference's AGNN forward:
+    csr_sddmm -> * beta -> csr_spmm."""
+    from paramspmm_ae_b200 import ops
+    m = mats["powerlaw"]
+    d = m.to(dev)
+    X = torch.nn.functional.normalize(dense(m.n_rows, 64, 77), dim=1).to(dev)
+    beta = 0.8
+    e = ops.csr_sddmm(X, X, d.rowPtr, d.colIdx, d.val, 2, 8) * beta
+    want = ops.csr_spmm(X, d.rowPtr, d.colIdx, e, 2, 8)
+    got = ops.agnn_fused(X, X, d.rowPtr, d.colIdx, beta, softmax=False)
+    close(got, want.cpu().numpy())
+
+
+def test_agnn_fused_rejects_what_it_cannot_run(dev):
+    from paramspmm_ae_b200 import _lib, ops
+    rp = torch.tensor([0, 1, 2], dtype=torch.int32, device=dev)
+    ci = torch.tensor([0, 1], dtype=torch.int32, device=dev)
+    X = torch.ones(2, 6, device=dev)  # dim not a multiple of 4
+    with pytest.raises(_lib.PspmmError):
+        ops.agnn_fused(X, X, rp, ci)
+    with pytest.raises(RuntimeError):
+        ops.agnn_fused(X.cpu(), X.cpu(), rp, ci)

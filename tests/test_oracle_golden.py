@@ -201,3 +201,25 @@ def test_pubmed_statistics(oracle, golden_dir):
         rpb, cb, vb = oracle.bcsr_build(csr.indptr, csr.indices, csr.data.astype(np.float32), csr.shape[0], 2)
         assert cb.shape[0] == st["bcsr_blocks"] and rpb.shape[0] == st["len_rowPtr_bcsr"]
         assert abs(csr.nnz / (2 * cb.shape[0]) - st["pack_rate"]) < 1e-12
+
+
+def test_agnn_aggregate_restatement_is_the_sddmm_spmm_composition():
+    """softmax=False must equal SDDMM -> * beta -> SpMM of the oracle's own pieces; softmax=True is
+    checked on a case worked by hand."""
+    import numpy as np
+    from oracle import oracle as orc
+    rng = np.random.default_rng(5)
+    n, dim = 37, 12
+    lens = rng.integers(0, 6, size=n)
+    rowPtr = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    colIdx = rng.integers(0, n, size=int(rowPtr[-1])).astype(np.int32)
+    X = rng.standard_normal((n, dim)).astype(np.float32)
+    e = orc.sddmm_csr(rowPtr, colIdx, X, X) * np.float32(0.6)
+    want = orc.spmm_csr(rowPtr, colIdx, e, X)
+    got = orc.agnn_aggregate(rowPtr, colIdx, X, X, 0.6, softmax=False)
+    np.testing.assert_allclose(got, want, rtol=1e-5, atol=1e-5)
+    # two entries with scores 0 and ln 3: weights 1/4 and 3/4
+    A = np.array([[1.0, 0.0]], dtype=np.float32)
+    B = np.array([[0.0, 2.0], [np.log(3.0), 4.0]], dtype=np.float32)
+    out = orc.agnn_aggregate(np.array([0, 2]), np.array([0, 1]), A, B, 1.0, softmax=True)
+    np.testing.assert_allclose(out, [[0.75 * np.log(3.0), 0.25 * 2.0 + 0.75 * 4.0]], rtol=1e-6)
