@@ -4,7 +4,8 @@ Same module and autograd-function names, constructor arguments and forward signa
 (gnn_conv.py:13-238 of the reference).  The layer semantics are the reference's:
 
 * GCN   forward  A (H W); backward AG = A G (A itself: the normalised adjacency is symmetric),
-        dH = AG W^T, dW = H^T AG.
+        dH = AG W^T, dW = H^T AG.  Layers that widen their input aggregate first instead,
+        (A H) W, see REORDER_NARROW_FIRST.
 * GIN   forward  (A X) W; backward dW = (A X)^T G, dX = A (G W^T).
 * AGNN  forward  X' = X W, e = SDDMM(X', X') * beta, out = SpMM(e, X'); no edge softmax and no
         row normalisation (the reference has none); the gradient w.r.t. beta follows the
@@ -19,17 +20,43 @@ import torch
 n_heads = 1
 
 
+# When a GCN layer widens its input (fan-in < fan-out) the aggregation is cheaper before the
+# projection: A (H W) = (A H) W, and the SpMM then runs at the narrower width.  The reference always
+# aggregates after the projection (SpCONV/SpCONV.h:43-72); results agree to fp32 rounding.  Set to
+# False to keep the reference's order everywhere.
+REORDER_NARROW_FIRST = True
+
+
+def _aggregate(P, X):
+    out = P.GIN_spmm(X.contiguous())
+    return out[: X.shape[0]] if out.shape[0] != X.shape[0] else out  # block layouts pad the row count
+
+
 class GCNFunction(torch.autograd.Function):
     @staticmethod
     def forward(ctx, H, weight, ParamSpMM):
-        ctx.save_for_backward(H, weight)
         ctx.ParamSpMM = ParamSpMM
+        ctx.narrow_first = bool(REORDER_NARROW_FIRST and weight.shape[0] < weight.shape[1])
+        if ctx.narrow_first:
+            AH = _aggregate(ParamSpMM, H)
+            ctx.save_for_backward(AH, weight)
+            return torch.mm(AH, weight)
+        ctx.save_for_backward(H, weight)
         return ParamSpMM.forward(H, weight)
 
     @staticmethod
     def backward(ctx, d_output):
+        P = ctx.ParamSpMM
+        d_output = d_output.contiguous()
+        if ctx.narrow_first:
+            # dW = (A H)^T G with A H kept from the forward; dH = A (G W^T) (A is symmetric),
+            # skipped when the layer input needs no gradient (the first layer).
+            AH, weight = ctx.saved_tensors
+            d_weight = torch.mm(AH.t(), d_output)
+            d_input = _aggregate(P, torch.mm(d_output, weight.t())) if ctx.needs_input_grad[0] else None
+            return d_input, d_weight, None
         H, weight = ctx.saved_tensors
-        d_input, d_weight = ctx.ParamSpMM.backward(d_output.contiguous(), H, weight)
+        d_input, d_weight = P.backward(d_output, H, weight)
         return d_input, d_weight, None
 
 
