@@ -42,6 +42,7 @@ def regime_matrices(n, device, which):
 
 
 VEC1_ONLY = False
+CTA_THREADS = (256,)
 
 
 def candidates(dim, regime, quick):
@@ -60,11 +61,11 @@ def candidates(dim, regime, quick):
     else:
         grans = [0]
     vecs = (1,) if (quick or VEC1_ONLY) else (1, 2)
-    for vec, gran, lpr, rpg, mlp in itertools.product(vecs, grans, lprs, rpgs, mlps):
+    for vec, gran, lpr, rpg, mlp, thr in itertools.product(vecs, grans, lprs, rpgs, mlps, CTA_THREADS):
         if vec != 1 and mlp != 8:
             continue  # block kernels are built with one gather depth
         yield {"vec_size": vec, "if_split": int(gran > 0), "granularity": gran or None,
-               "lanes_per_row": lpr, "vec_width": vw, "rows_per_group": rpg, "cta_threads": 256,
+               "lanes_per_row": lpr, "vec_width": vw, "rows_per_group": rpg, "cta_threads": thr,
                "gather_batch": mlp}
 
 
@@ -96,8 +97,9 @@ class Layouts:
 
 
 def run(args):
-    global VEC1_ONLY
+    global VEC1_ONLY, CTA_THREADS
     VEC1_ONLY = bool(getattr(args, "vec1_only", False))
+    CTA_THREADS = tuple(getattr(args, "cta_threads", None) or (256,))
     dev = torch.device("cuda:0")
     _lib.lib()
     which = args.regimes
@@ -165,6 +167,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--quick", action="store_true")
     ap.add_argument("--vec1-only", action="store_true", help="skip the 2 x 1 block layout")
+    ap.add_argument("--cta-threads", type=int, nargs="*", default=[256], help="CTA sizes to try (128, 256)")
     ap.add_argument("--out", default="gpurun_out/sweep.json")
     ap.add_argument("--table", default=None)
     run(ap.parse_args())
