@@ -328,6 +328,10 @@ def main():
     if n == N_ROWS and key in NCU_DRAM_BYTES:
         roofline["traffic"] = NCU_DRAM_BYTES[key]
         roofline["traffic_source"] = "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch of this case"
+        # the same launch measured on the bytes it actually moves: with uniformly random columns and
+        # B several times the L2, nnz * dim * 4 gathered bytes are DRAM transactions by construction
+        roofline["traffic_gbs"] = round(NCU_DRAM_BYTES[key] / mean_ms[top] / 1e6, 1)
+        roofline["traffic_frac"] = round(NCU_DRAM_BYTES[key] / mean_ms[top] / 1e6 / peak, 4)
 
     # ---- end to end: host buffers in, host buffer out, copies inside the timed region
     e2e = None
