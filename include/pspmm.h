@@ -183,7 +183,9 @@ PSPMM_API int pspmm_split_csr_device_static(const int32_t *rowPtr, int64_t n_row
  * softmax != 0 the per-row edge softmax sits between the two.  Stored values are ignored (the
  * pattern is a mask, as in pspmm_sddmm_csr).  Rows without entries give zero rows.
  * dim must be a multiple of 4 and at most 256, A, B and out 16-byte aligned with leading
- * dimensions that are multiples of 4 (PSPMM_E_UNSUPPORTED otherwise).  `lanes_per_row` (0 = library's
+ * dimensions that are multiples of 4 (PSPMM_E_UNSUPPORTED otherwise).  `vec_width` = floats per lane
+ * per load: 0 (library's choice), 4, or 8 (256-bit loads; needs dim a multiple of 8 and 32-byte
+ * aligned rows, else 4 is used).  `lanes_per_row` (0 = library's
  * choice, 4, 8, 16 or 32) lanes share one row; `batch` (0, 4, 8 or 16) entries are gathered together
  * per lane group; combinations that are not built are rounded to the nearest built one.
  * Split layouts (rowPtr_split/target_row/n_seg as in pspmm_spmm_csr) need scratch of
@@ -194,9 +196,9 @@ PSPMM_API int pspmm_agnn_scratch_bytes(int64_t n_seg, int32_t dim, size_t *bytes
 PSPMM_API int pspmm_agnn_fused_csr(const int32_t *rowPtr, const int32_t *colIdx, const float *A,
                                    const float *B, float *out, int64_t n_rows, int64_t nnz, int32_t dim,
                                    int64_t ldA, int64_t ldB, int64_t ldOut, float beta, int32_t softmax,
-                                   int32_t lanes_per_row, int32_t batch, const int32_t *rowPtr_split,
-                                   const int32_t *target_row, int64_t n_seg, void *scratch,
-                                   size_t scratch_bytes, void *stream);
+                                   int32_t vec_width, int32_t lanes_per_row, int32_t batch,
+                                   const int32_t *rowPtr_split, const int32_t *target_row, int64_t n_seg,
+                                   void *scratch, size_t scratch_bytes, void *stream);
 
 /*
  * Host-side CSR -> V x 1 block CSR, laid out exactly as scipy's tobsr((V,1)) (which the

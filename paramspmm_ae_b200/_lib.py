@@ -60,7 +60,7 @@ _SIGNATURES = {
     "pspmm_split_csr_device_static": [_vp, _i64, _i32, _vp, _vp, _i64, _vp],
     "pspmm_agnn_scratch_bytes": [_i64, _i32, ctypes.POINTER(ctypes.c_size_t)],
     "pspmm_agnn_fused_csr": [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i32, _i64, _i64, _i64, ctypes.c_float, _i32,
-                             _i32, _i32, _vp, _vp, _i64, _vp, ctypes.c_size_t, _vp],
+                             _i32, _i32, _i32, _vp, _vp, _i64, _vp, ctypes.c_size_t, _vp],
     "pspmm_bcsr_count": [_vp, _vp, _i64, _i64, _i32, _vp, ctypes.POINTER(_i64)],
     "pspmm_bcsr_fill": [_vp, _vp, _vp, _i64, _i64, _i32, _vp, _vp, _vp],
     "pspmm_profile_spmm": [_vp, _vp, _vp, _i32, _vp, _vp, _i64, _i64, _i64, _i32, _i64, _i64, _cfgp,

@@ -76,7 +76,7 @@ __device__ __forceinline__ float group_transpose_reduce(float (&p)[BS], int gl)
     return q[0];
 }
 
-template <int LPR, int CF, int BS>
+template <int LPR, int CF, int BS, int VW>
 __global__ void __launch_bounds__(256) agnn_fused_kernel(const AgnnArgs a)
 {
     static_assert(BS <= LPR, "a batch cannot be wider than the lane group");
@@ -101,19 +101,19 @@ __global__ void __launch_bounds__(256) agnn_fused_kernel(const AgnnArgs a)
             single = (prev != me) && (next != me);
         }
     }
-    const int nvec = a.dim / 4;
+    const int nvec = a.dim / VW;
     bool act[CF];
     int voff[CF];
-    FVec<4> av[CF];
-    float acc[CF][4];
+    FVec<VW> av[CF];
+    float acc[CF][VW];
 #pragma unroll
     for (int cf = 0; cf < CF; ++cf) {
         const int v = cf * LPR + gl;
         act[cf] = v < nvec;
-        voff[cf] = act[cf] ? v * 4 : 0;
-        av[cf] = (live && act[cf]) ? ldg_vec<4>(a.A + row * a.ldA + voff[cf]) : zero_vec<4>();
+        voff[cf] = act[cf] ? v * VW : 0;
+        av[cf] = (live && act[cf]) ? ldg_vec<VW>(a.A + row * a.ldA + voff[cf]) : zero_vec<VW>();
 #pragma unroll
-        for (int i = 0; i < 4; ++i)
+        for (int i = 0; i < VW; ++i)
             acc[cf][i] = 0.f;
     }
     float m = -CUDART_INF_F, l = 0.f;
@@ -139,7 +139,7 @@ __global__ void __launch_bounds__(256) agnn_fused_kernel(const AgnnArgs a)
                 break;  // warp-uniform
             const bool mine = (lb + off + sub) < hb;
             const bool full = (off + BS <= len);
-            FVec<4> x[BS][CF];
+            FVec<VW> x[BS][CF];
             float part[BS];
             int ce[BS];
 #pragma unroll
@@ -151,12 +151,12 @@ __global__ void __launch_bounds__(256) agnn_fused_kernel(const AgnnArgs a)
                 if (full) {
 #pragma unroll
                     for (int cf = 0; cf < CF; ++cf)
-                        x[e][cf] = ldg_vec<4>(brow + voff[cf]);
+                        x[e][cf] = ldg_vec<VW>(brow + voff[cf]);
                 } else {
                     const bool on = (off + e) < len;
 #pragma unroll
                     for (int cf = 0; cf < CF; ++cf)
-                        x[e][cf] = ldg_vec_if<4>(brow + voff[cf], on);
+                        x[e][cf] = ldg_vec_if<VW>(brow + voff[cf], on);
                 }
             }
 #pragma unroll
@@ -166,7 +166,7 @@ __global__ void __launch_bounds__(256) agnn_fused_kernel(const AgnnArgs a)
                 for (int cf = 0; cf < CF; ++cf)
                     if (act[cf]) {
 #pragma unroll
-                        for (int i = 0; i < 4; ++i)
+                        for (int i = 0; i < VW; ++i)
                             s = fmaf(av[cf].v[i], x[e][cf].v[i], s);
                     }
                 part[e] = s;
@@ -192,7 +192,7 @@ __global__ void __launch_bounds__(256) agnn_fused_kernel(const AgnnArgs a)
 #pragma unroll
                 for (int cf = 0; cf < CF; ++cf)
 #pragma unroll
-                    for (int i = 0; i < 4; ++i)
+                    for (int i = 0; i < VW; ++i)
                         acc[cf][i] *= sc;
             } else {
                 p = mine ? score : 0.f;
@@ -203,7 +203,7 @@ __global__ void __launch_bounds__(256) agnn_fused_kernel(const AgnnArgs a)
 #pragma unroll
                 for (int cf = 0; cf < CF; ++cf)
 #pragma unroll
-                    for (int i = 0; i < 4; ++i)
+                    for (int i = 0; i < VW; ++i)
                         acc[cf][i] = fmaf(pe, x[e][cf].v[i], acc[cf][i]);
             }
         }
@@ -216,8 +216,11 @@ __global__ void __launch_bounds__(256) agnn_fused_kernel(const AgnnArgs a)
 #pragma unroll
         for (int cf = 0; cf < CF; ++cf)
             if (act[cf]) {
-                const float v[4] = {acc[cf][0] * inv, acc[cf][1] * inv, acc[cf][2] * inv, acc[cf][3] * inv};
-                st_stream_vec<4>(orow + voff[cf], v);
+                float v[VW];
+#pragma unroll
+                for (int i = 0; i < VW; ++i)
+                    v[i] = acc[cf][i] * inv;
+                st_stream_vec<VW>(orow + voff[cf], v);
             }
     } else {
         float *ps = a.scratch + seg * (int64_t)(4 + a.dim_pad);
@@ -228,7 +231,7 @@ __global__ void __launch_bounds__(256) agnn_fused_kernel(const AgnnArgs a)
 #pragma unroll
         for (int cf = 0; cf < CF; ++cf)
             if (act[cf])
-                st_vec<4>(ps + 4 + voff[cf], acc[cf]);
+                st_vec<VW>(ps + 4 + voff[cf], acc[cf]);
     }
 }
 
@@ -275,12 +278,12 @@ __global__ void __launch_bounds__(256) agnn_combine_kernel(const AgnnArgs a)
     }
 }
 
-template <int LPR, int CF, int BS>
+template <int LPR, int CF, int BS, int VW>
 void launch_fused(const AgnnArgs &a, cudaStream_t st)
 {
     const int gpc = 256 / LPR;
     const int64_t gx = (a.n_seg + gpc - 1) / gpc;
-    agnn_fused_kernel<LPR, CF, BS><<<(unsigned)gx, 256, 0, st>>>(a);
+    agnn_fused_kernel<LPR, CF, BS, VW><<<(unsigned)gx, 256, 0, st>>>(a);
 }
 
 }  // namespace
@@ -297,8 +300,8 @@ extern "C" int pspmm_agnn_scratch_bytes(int64_t n_seg, int32_t dim, size_t *byte
 extern "C" int pspmm_agnn_fused_csr(const int32_t *rowPtr, const int32_t *colIdx, const float *A,
                                     const float *B, float *out, int64_t n_rows, int64_t nnz, int32_t dim,
                                     int64_t ldA, int64_t ldB, int64_t ldOut, float beta, int32_t softmax,
-                                    int32_t lanes_per_row, int32_t batch, const int32_t *rowPtr_split,
-                                    const int32_t *target_row,
+                                    int32_t vec_width, int32_t lanes_per_row, int32_t batch,
+                                    const int32_t *rowPtr_split, const int32_t *target_row,
                                     int64_t n_seg, void *scratch, size_t scratch_bytes, void *stream)
 {
     if (n_rows < 0 || nnz < 0 || dim <= 0)
@@ -350,41 +353,52 @@ extern "C" int pspmm_agnn_fused_csr(const int32_t *rowPtr, const int32_t *colIdx
         if (n_seg == 0)
             return PSPMM_OK;
     }
-    // Launch shape: lanes per row (LPR), 16-byte slices per lane (CF = ceil(dim / 4 / LPR)) and
-    // entries per batch (BS).  Fewer lanes per row put more entries into every warp instruction,
-    // which is what counts for this instruction-bound kernel; the defaults are the measured best.
-    const int nvec = dim / 4;
+    // Launch shape: floats per lane per load (VW: 8 = 256-bit loads when the rows are 32-byte
+    // aligned, else 4), lanes per row (LPR), slices per lane (CF = ceil(dim / VW / LPR)) and
+    // entries per batch (BS).  Few lanes per row put more entries into every warp instruction (the
+    // 128-bit form at 16 lanes is bound by instruction issue); wide loads keep the L1 wavefronts
+    // full (the 128-bit form at 4 lanes is bound by the L1 data pipe).  Defaults = measured best.
+    const bool can8 = dim % 8 == 0 && dim >= 32 && ldA % 8 == 0 && ldB % 8 == 0 && ((uintptr_t)A) % 32 == 0 &&
+                      ((uintptr_t)B) % 32 == 0;
+    if (vec_width != 0 && vec_width != 4 && vec_width != 8)
+        return PSPMM_E_CONFIG;
+    const int vw = (vec_width == 8 && !can8) ? 4 : (vec_width ? vec_width : (can8 ? 8 : 4));
+    const int nvec = dim / vw;
     int lpr = lanes_per_row;
     if (lpr == 0)
-        lpr = nvec <= 16 ? 4 : (nvec <= 32 ? 8 : 16);  // four slices per lane from dim 64 on
+        lpr = vw == 8 ? (nvec <= 8 ? 4 : (nvec <= 16 ? 8 : 16)) : (nvec <= 16 ? 4 : (nvec <= 32 ? 8 : 16));
+    const int cf_max = vw == 8 ? 2 : 4;
     int cf = (nvec + lpr - 1) / lpr;
-    while (cf > 4 || (cf == 3)) {  // instantiated: 1, 2, 4 slices per lane
-        if (cf == 3) {
-            cf = 4;
-            break;
-        }
+    while (cf > cf_max && lpr < 32) {
         lpr *= 2;
-        if (lpr > 32)
-            return PSPMM_E_UNSUPPORTED;
         cf = (nvec + lpr - 1) / lpr;
     }
+    if (cf > cf_max)
+        return PSPMM_E_UNSUPPORTED;
+    if (cf == 3)
+        cf = 4;
     int bs = batch ? batch : 4;
     if (bs > lpr)
         bs = lpr;
-    if (cf == 4 && bs > 4)
+    if (cf * vw >= 16 && bs > 4)
         bs = 4;
-    if (cf == 2 && bs > 8)
+    if (cf * vw >= 8 && bs > 8)
         bs = 8;
     bool ok = false;
-#define AGNN_CASE(LPR_, CF_, BS_)                    \
-    if (!ok && lpr == LPR_ && cf == CF_ && bs == BS_) { \
-        launch_fused<LPR_, CF_, BS_>(a, st);         \
-        ok = true;                                   \
+#define AGNN_CASE(LPR_, CF_, BS_, VW_)                             \
+    if (!ok && vw == VW_ && lpr == LPR_ && cf == CF_ && bs == BS_) { \
+        launch_fused<LPR_, CF_, BS_, VW_>(a, st);                  \
+        ok = true;                                                 \
     }
-    AGNN_CASE(4, 1, 4) AGNN_CASE(4, 2, 4) AGNN_CASE(4, 4, 4)
-    AGNN_CASE(8, 1, 4) AGNN_CASE(8, 1, 8) AGNN_CASE(8, 2, 4) AGNN_CASE(8, 2, 8) AGNN_CASE(8, 4, 4)
-    AGNN_CASE(16, 1, 4) AGNN_CASE(16, 1, 8) AGNN_CASE(16, 1, 16) AGNN_CASE(16, 2, 4) AGNN_CASE(16, 2, 8) AGNN_CASE(16, 4, 4)
-    AGNN_CASE(32, 1, 4) AGNN_CASE(32, 1, 8) AGNN_CASE(32, 1, 16) AGNN_CASE(32, 2, 4) AGNN_CASE(32, 2, 8)
+    AGNN_CASE(4, 1, 4, 4) AGNN_CASE(4, 2, 4, 4) AGNN_CASE(4, 4, 4, 4)
+    AGNN_CASE(8, 1, 4, 4) AGNN_CASE(8, 1, 8, 4) AGNN_CASE(8, 2, 4, 4) AGNN_CASE(8, 2, 8, 4) AGNN_CASE(8, 4, 4, 4)
+    AGNN_CASE(16, 1, 4, 4) AGNN_CASE(16, 1, 8, 4) AGNN_CASE(16, 1, 16, 4) AGNN_CASE(16, 2, 4, 4) AGNN_CASE(16, 2, 8, 4)
+    AGNN_CASE(16, 4, 4, 4)
+    AGNN_CASE(32, 1, 4, 4) AGNN_CASE(32, 1, 8, 4) AGNN_CASE(32, 1, 16, 4) AGNN_CASE(32, 2, 4, 4) AGNN_CASE(32, 2, 8, 4)
+    AGNN_CASE(4, 1, 4, 8) AGNN_CASE(4, 2, 4, 8)
+    AGNN_CASE(8, 1, 4, 8) AGNN_CASE(8, 1, 8, 8) AGNN_CASE(8, 2, 4, 8)
+    AGNN_CASE(16, 1, 4, 8) AGNN_CASE(16, 1, 8, 8) AGNN_CASE(16, 2, 4, 8)
+    AGNN_CASE(32, 1, 4, 8) AGNN_CASE(32, 1, 8, 8)
 #undef AGNN_CASE
     if (!ok)
         return PSPMM_E_UNSUPPORTED;

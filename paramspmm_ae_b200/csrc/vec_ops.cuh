@@ -13,7 +13,13 @@ template <int VW>
 __device__ __forceinline__ FVec<VW> ldg_vec(const float *p)
 {
     FVec<VW> r;
-    if constexpr (VW == 4) {
+    if constexpr (VW == 8) {
+        // 256-bit read-only load (sm_100): p must be 32-byte aligned
+        asm("ld.global.nc.v8.f32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+            : "=f"(r.v[0]), "=f"(r.v[1]), "=f"(r.v[2]), "=f"(r.v[3]), "=f"(r.v[4]), "=f"(r.v[5]), "=f"(r.v[6]),
+              "=f"(r.v[7])
+            : "l"(p));
+    } else if constexpr (VW == 4) {
         float4 t = __ldg(reinterpret_cast<const float4 *>(p));
         r.v[0] = t.x; r.v[1] = t.y; r.v[2] = t.z; r.v[3] = t.w;
     } else if constexpr (VW == 2) {
@@ -98,7 +104,17 @@ __device__ __forceinline__ FVec<VW> ldg_vec_if(const float *p, bool on)
 {
     FVec<VW> r;
     const int flag = on ? 1 : 0;
-    if constexpr (VW == 4) {
+    if constexpr (VW == 8) {
+        asm("{\n\t.reg .pred q;\n\tsetp.ne.s32 q, %9, 0;\n\t"
+            "mov.f32 %0, 0f00000000;\n\tmov.f32 %1, 0f00000000;\n\t"
+            "mov.f32 %2, 0f00000000;\n\tmov.f32 %3, 0f00000000;\n\t"
+            "mov.f32 %4, 0f00000000;\n\tmov.f32 %5, 0f00000000;\n\t"
+            "mov.f32 %6, 0f00000000;\n\tmov.f32 %7, 0f00000000;\n\t"
+            "@q ld.global.nc.v8.f32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];\n\t}"
+            : "=f"(r.v[0]), "=f"(r.v[1]), "=f"(r.v[2]), "=f"(r.v[3]), "=f"(r.v[4]), "=f"(r.v[5]), "=f"(r.v[6]),
+              "=f"(r.v[7])
+            : "l"(p), "r"(flag));
+    } else if constexpr (VW == 4) {
         asm("{\n\t.reg .pred q;\n\tsetp.ne.s32 q, %5, 0;\n\t"
             "mov.f32 %0, 0f00000000;\n\tmov.f32 %1, 0f00000000;\n\t"
             "mov.f32 %2, 0f00000000;\n\tmov.f32 %3, 0f00000000;\n\t"
@@ -135,7 +151,10 @@ __device__ __forceinline__ FVec<VW> zero_vec()
 template <int VW>
 __device__ __forceinline__ void st_stream_vec(float *p, const float *v)
 {
-    if constexpr (VW == 4) {
+    if constexpr (VW == 8) {
+        __stcs(reinterpret_cast<float4 *>(p), make_float4(v[0], v[1], v[2], v[3]));
+        __stcs(reinterpret_cast<float4 *>(p) + 1, make_float4(v[4], v[5], v[6], v[7]));
+    } else if constexpr (VW == 4) {
         __stcs(reinterpret_cast<float4 *>(p), make_float4(v[0], v[1], v[2], v[3]));
     } else if constexpr (VW == 2) {
         __stcs(reinterpret_cast<float2 *>(p), make_float2(v[0], v[1]));
@@ -148,7 +167,10 @@ __device__ __forceinline__ void st_stream_vec(float *p, const float *v)
 template <int VW>
 __device__ __forceinline__ void st_vec(float *p, const float *v)
 {
-    if constexpr (VW == 4) {
+    if constexpr (VW == 8) {
+        *reinterpret_cast<float4 *>(p) = make_float4(v[0], v[1], v[2], v[3]);
+        *(reinterpret_cast<float4 *>(p) + 1) = make_float4(v[4], v[5], v[6], v[7]);
+    } else if constexpr (VW == 4) {
         *reinterpret_cast<float4 *>(p) = make_float4(v[0], v[1], v[2], v[3]);
     } else if constexpr (VW == 2) {
         *reinterpret_cast<float2 *>(p) = make_float2(v[0], v[1]);

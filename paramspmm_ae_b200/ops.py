@@ -390,7 +390,7 @@ def vec_split_sddmm_profile(A, B, rowPtr_split, colIdx, val, target_row, nnz, CF
 
 
 def agnn_fused(A, B, rowPtr, colIdx, beta=1.0, softmax=True, target_row=None, n_out_rows=None, out=None,
-               batch=0, lanes_per_row=0):
+               batch=0, lanes_per_row=0, vec_width=0):
     """out_i = sum_j a_ij B_j with a_ij = softmax_j(beta <A_i, B_j>) (or the raw scaled scores when
     ``softmax`` is false) over the stored pattern, in one pass and without a per-edge array.
 
@@ -430,7 +430,7 @@ def agnn_fused(A, B, rowPtr, colIdx, beta=1.0, softmax=True, target_row=None, n_
     seg_ptr = _ptr(rowPtr)
     check(lib().pspmm_agnn_fused_csr(null if split else seg_ptr, _ptr(colIdx), _ptr(A), _ptr(B), _ptr(out),
                                      n_out_rows, colIdx.shape[0], dim, A.stride(0), B.stride(0), out.stride(0),
-                                     float(beta), 1 if softmax else 0, int(lanes_per_row), int(batch),
+                                     float(beta), 1 if softmax else 0, int(vec_width), int(lanes_per_row), int(batch),
                                      seg_ptr if split else null, _ptr(target_row) if split else null,
                                      n_seg if split else 0, _ptr(scratch) if split else null, sbytes, _stream()))
     return out

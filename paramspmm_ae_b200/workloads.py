@@ -116,19 +116,19 @@ def agnn_layer(n=232_965, pairs=57_180_000, dim=64, seed=41, iters=10, grans=(0,
             continue
         rps, tr = layouts[gran]
         Cf = torch.empty(n, dim, device=dev)
-        for lanes, batch in ((16, 8), (8, 4), (4, 4)):
-            if gran != 1024 and (lanes, batch) != (4, 4):
+        for vw, lanes, batch in ((4, 16, 8), (4, 4, 4), (8, 8, 4), (8, 8, 8), (8, 4, 4), (0, 0, 0)):
+            if gran != 2048 and (vw, lanes, batch) != (0, 0, 0):
                 continue  # the shape comparison on one partition length only
             f_plain = lambda: ops.agnn_fused(X, X, rps, g.colIdx, beta, False, target_row=tr, n_out_rows=n,
-                                             out=Cf, batch=batch, lanes_per_row=lanes)
+                                             out=Cf, batch=batch, lanes_per_row=lanes, vec_width=vw)
             ms_plain = _time_ms(f_plain, iters=iters)
             f_plain()
             scale = float(want.abs().max())
             torch.testing.assert_close(Cf, want, rtol=1e-4, atol=1e-5 * max(1.0, scale))
             f_soft = lambda: ops.agnn_fused(X, X, rps, g.colIdx, beta, True, target_row=tr, n_out_rows=n,
-                                            out=Cf, batch=batch, lanes_per_row=lanes)
+                                            out=Cf, batch=batch, lanes_per_row=lanes, vec_width=vw)
             ms_soft = _time_ms(f_soft, iters=iters)
-            fused.append({"granularity": gran, "lanes_per_row": lanes, "batch": batch, "fused_ms": round(ms_plain, 4),
+            fused.append({"granularity": gran, "vec_width": vw, "lanes_per_row": lanes, "batch": batch, "fused_ms": round(ms_plain, 4),
                           "fused_softmax_ms": round(ms_soft, 4)})
     out["fused"] = fused
     out["fused_best_ms"] = min(f["fused_ms"] for f in fused)

@@ -372,9 +372,11 @@ def test_agnn_fused_matches_the_oracle(dev, oracle, mats, dim, softmax):
         beta = 1.7
         want = oracle.agnn_aggregate(rp, ci, X.numpy(), X.numpy(), beta, softmax)
         d, Xd = m.to(dev), X.to(dev)
-        for lanes, batch in ((0, 0), (4, 4), (8, 4), (8, 8), (16, 8), (16, 16), (32, 8), (32, 16)):
-            got = ops.agnn_fused(Xd, Xd, d.rowPtr, d.colIdx, beta, softmax, batch=batch, lanes_per_row=lanes)
-            close(got, want)
+        for vw in (0, 4, 8):
+            for lanes, batch in ((0, 0), (4, 4), (8, 4), (8, 8), (16, 8), (16, 16), (32, 8), (32, 16)):
+                got = ops.agnn_fused(Xd, Xd, d.rowPtr, d.colIdx, beta, softmax, batch=batch, lanes_per_row=lanes,
+                                     vec_width=vw)
+                close(got, want)
         for gran in (3, 32):
             rps, tr = ops.split_csr(m.rowPtr, gran)
             got = torch.full((m.n_rows, dim), float("nan"), device=dev)
