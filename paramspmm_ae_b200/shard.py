@@ -12,6 +12,14 @@ other, and the column indices of the local shard of A are remapped ONCE, at set-
 positions in that padded layout (column c owned by rank q at local row i becomes
 q * max_rows + i).  The gathered buffer is then the dense operand as it stands.
 
+``exchange="needed"`` replaces the dense all-gather by a sparse one: at set-up every rank works out
+which rows of the dense operand its shard of A references at all (the distinct column ids), asks
+each owner for exactly those, and renumbers its columns to positions in the compact receive
+buffer.  Per product every rank then gathers the requested rows into one send buffer and a single
+all-to-all with uneven splits moves them.  On power-law graphs a shard touches a fraction of the
+columns, so the bytes on NVLink shrink by that fraction, and the SpMM gathers from a smaller
+operand.
+
 ``dim_chunks > 1`` splits the dense columns into slices and gathers slice s+1 on a side
 stream while the SpMM of slice s runs (the kernels take explicit leading dimensions, so a
 slice of C is written in place).
@@ -61,8 +69,11 @@ class ShardedSpMM:
     """
 
     def __init__(self, rowPtr, colIdx, val, n_cols, rank, world, row_bounds=None, col_bounds=None,
-                 device="cuda", group=None, local_spmm=None, dim_chunks=1):
+                 device="cuda", group=None, local_spmm=None, dim_chunks=1, exchange="allgather"):
+        if exchange not in ("allgather", "needed"):
+            raise ValueError("exchange must be 'allgather' or 'needed'")
         self.rank, self.world, self.group, self.dim_chunks = rank, world, group, dim_chunks
+        self.exchange = exchange
         self.row_bounds = partition_rows_by_nnz(rowPtr, world) if row_bounds is None else torch.as_tensor(row_bounds).long()
         self.col_bounds = partition_rows_even(n_cols, world) if col_bounds is None else torch.as_tensor(col_bounds).long()
         if int(self.col_bounds[-1]) != n_cols or int(self.row_bounds[-1]) != len(rowPtr) - 1:
@@ -72,12 +83,54 @@ class ShardedSpMM:
         self.lo, self.hi = lo, hi
         rp, ci, v = extract_rows(rowPtr, colIdx, val, lo, hi)
         self.rowPtr = rp.to(device)
-        self.colIdx = remap_columns(ci.to(device), self.col_bounds, self.max_rows)
         self.val = v.to(device)
         self.device = torch.device(device)
         self.my_cols = (int(self.col_bounds[rank]), int(self.col_bounds[rank + 1]))
+        if exchange == "needed":
+            self._plan_needed_rows(ci.to(device))
+        else:
+            self.colIdx = remap_columns(ci.to(device), self.col_bounds, self.max_rows)
         self.local_spmm = local_spmm if local_spmm is not None else self._planned_spmm()
         self._side = torch.cuda.Stream() if (self.device.type == "cuda" and dim_chunks > 1) else None
+
+    def _plan_needed_rows(self, cols_global):
+        """Set-up of the sparse exchange: which rows this rank needs from every owner, which rows
+        every other rank needs from this one, and the local column ids renumbered to positions in
+        the receive buffer (rows arrive grouped by owner, ascending inside a group, i.e. in the
+        order of the sorted distinct column ids)."""
+        import torch.distributed as dist
+
+        dev = cols_global.device
+        need = torch.unique(cols_global.long())  # sorted distinct global column ids
+        cb = self.col_bounds.to(dev)
+        cuts = torch.searchsorted(need, cb)  # need[cuts[q]:cuts[q+1]] is owned by rank q
+        recv_counts = (cuts[1:] - cuts[:-1]).cpu()
+        owner = torch.repeat_interleave(torch.arange(self.world, device=dev), recv_counts.to(dev))
+        wanted = (need - cb[owner]).to(torch.int64)  # row ids inside the owners' shards
+        self.colIdx = torch.searchsorted(need, cols_global.long()).to(torch.int32)
+        self.n_needed = int(need.numel())
+        self.recv_splits = [int(x) for x in recv_counts]
+        if self.world == 1:
+            self.send_splits, self.send_rows = list(self.recv_splits), wanted
+            return
+        counts_out = torch.empty(self.world, dtype=torch.int64, device=dev)
+        dist.all_to_all_single(counts_out, recv_counts.to(dev), group=self.group)
+        self.send_splits = [int(x) for x in counts_out.cpu()]
+        self.send_rows = torch.empty(sum(self.send_splits), dtype=torch.int64, device=dev)
+        dist.all_to_all_single(self.send_rows, wanted, output_split_sizes=self.send_splits,
+                               input_split_sizes=self.recv_splits, group=self.group)
+
+    def _exchange_needed(self, B_shard):
+        """Rows of the dense operand this rank's columns reference, in receive-buffer order."""
+        import torch.distributed as dist
+
+        send = B_shard.index_select(0, self.send_rows)
+        if self.world == 1:
+            return send
+        recv = torch.empty(self.n_needed, B_shard.shape[1], dtype=B_shard.dtype, device=B_shard.device)
+        dist.all_to_all_single(recv, send, output_split_sizes=self.recv_splits,
+                               input_split_sizes=self.send_splits, group=self.group)
+        return recv
 
     def _planned_spmm(self):
         """The CUDA operator with the configuration the decider picks for this shard's row-length
@@ -130,6 +183,9 @@ class ShardedSpMM:
         dim = B_shard.shape[1]
         if out is None:
             out = torch.empty(self.local_rows, dim, dtype=B_shard.dtype, device=B_shard.device)
+        if self.exchange == "needed":
+            self.local_spmm(out, self._exchange_needed(B_shard), self.rowPtr, self.colIdx, self.val)
+            return out
         k = max(1, min(self.dim_chunks, dim // 4)) if self.dim_chunks > 1 else 1
         if k == 1:
             self.local_spmm(out, self._gather(B_shard), self.rowPtr, self.colIdx, self.val)

@@ -185,8 +185,9 @@ def scaleout_spmm(scale=24, nnz=512_000_000, dim=128, seed=51, iters=5, warmup=2
 
     Three timings per rank (CUDA events on the launching stream, maximum over ranks):
     the local SpMM against a replicated dense operand (no exchange), the all-gather of the dense
-    row blocks followed by the SpMM, and the same with the dense columns cut into `dim_chunks`
-    slices so that the gather of slice s+1 overlaps the SpMM of slice s.
+    row blocks followed by the SpMM, the exchange of only the rows each shard references (one
+    all-to-all) followed by the SpMM on the compact operand, and the all-gather with the dense
+    columns cut into `dim_chunks` slices so that the gather of slice s+1 overlaps the SpMM of slice s.
     Every rank generates the same global matrix from the seed and keeps only its rows.
     """
     import torch.distributed as dist
@@ -200,6 +201,7 @@ def scaleout_spmm(scale=24, nnz=512_000_000, dim=128, seed=51, iters=5, warmup=2
     sh = ShardedSpMM(m.rowPtr, m.colIdx, m.val, n, rank, world, device=dev, dim_chunks=1)
     a, b = int(m.rowPtr[sh.lo]), int(m.rowPtr[sh.hi])
     sh.keep_global_columns(m.colIdx[a:b].clone())
+    sh_needed = ShardedSpMM(m.rowPtr, m.colIdx, m.val, n, rank, world, device=dev, exchange="needed")
     nnz_total, nnz_local = m.nnz, b - a
     del m
     torch.cuda.empty_cache()
@@ -232,6 +234,9 @@ def scaleout_spmm(scale=24, nnz=512_000_000, dim=128, seed=51, iters=5, warmup=2
     # different order on every launch (REDs): the comparison allows for fp32 re-association.
     tol = dict(rtol=1e-4, atol=2e-3)
     torch.testing.assert_close(out_ag, out_rep, **tol)
+    out_ag.fill_(float("nan"))
+    ms_needed = timed(lambda: sh_needed.forward(B_shard, out_ag))
+    torch.testing.assert_close(out_ag, out_rep, **tol)
     sh.dim_chunks = dim_chunks
     sh._side = torch.cuda.Stream()
     out_ag.fill_(float("nan"))
@@ -243,6 +248,9 @@ def scaleout_spmm(scale=24, nnz=512_000_000, dim=128, seed=51, iters=5, warmup=2
             "generate_s": round(gen_s, 1), "world": world,
             "spmm_replicated_ms": round(ms_rep, 4), "allgather_spmm_ms": round(ms_ag, 4),
             "allgather_overlapped_ms": round(ms_ov, 4), "dim_chunks": dim_chunks,
+            "needed_rows_exchange_spmm_ms": round(ms_needed, 4),
+            "needed_rows_exchange_spmm_gflops": round(gf(ms_needed), 1),
+            "needed_rows_fraction": round(sh_needed.n_needed / n, 4),
             "spmm_replicated_gflops": round(gf(ms_rep), 1), "allgather_spmm_gflops": round(gf(ms_ag), 1),
             "allgather_overlapped_gflops": round(gf(ms_ov), 1),
             "compulsory_bytes_global": by, "spmm_replicated_gbs_global": round(by / ms_rep / 1e6, 1)}

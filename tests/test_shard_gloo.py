@@ -43,7 +43,7 @@ def _free_port():
     return p
 
 
-def _worker(rank, world, port, dim_chunks, q):
+def _worker(rank, world, port, dim_chunks, q, exchange="allgather"):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -59,7 +59,8 @@ def _worker(rank, world, port, dim_chunks, q):
 
         row_b = shard.partition_rows_by_nnz(m.rowPtr, world)
         op = shard.ShardedSpMM(m.rowPtr, m.colIdx, m.val, m.n_cols, rank, world, row_bounds=row_b,
-                               col_bounds=row_b, device="cpu", local_spmm=local_spmm, dim_chunks=1)
+                               col_bounds=row_b, device="cpu", local_spmm=local_spmm, dim_chunks=1,
+                               exchange=exchange)
         lo, hi = op.my_cols
         C_local = op.forward(B[lo:hi].contiguous())
         want = orc.spmm_csr(*m.numpy(), B.numpy())[op.lo: op.hi]
@@ -73,12 +74,13 @@ def _worker(rank, world, port, dim_chunks, q):
         dist.destroy_process_group()
 
 
+@pytest.mark.parametrize("exchange", ["allgather", "needed"])
 @pytest.mark.parametrize("world", [2, 3])
-def test_sharded_spmm_two_layers_gloo(world):
+def test_sharded_spmm_two_layers_gloo(world, exchange):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, 1, q)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, 1, q, exchange)) for r in range(world)]
     for p in procs:
         p.start()
     res = [q.get(timeout=120) for _ in range(world)]
