@@ -433,11 +433,13 @@ def main():
                         ms = baselines.time_plan_ms(plan, warmup=3, iters=20)
                         plan.close()
                         rec[label + "_ms"] = round(ms, 5)
+                    rec["gespmm_ms"] = round(baselines.gespmm_time_ms(Bs[dim], m.rowPtr, m.colIdx, m.val, warmup=3, iters=20), 5)
                     rec["speedup_vs_best_cusparse"] = round(min(rec["cusparse_csr_default_ms"], rec["cusparse_csr_alg2_ms"]) / ours, 3)
                     rows.append(rec)
             sp = [r["speedup_vs_best_cusparse"] for r in rows]
             comparators = {"note": "cusparseSpMM fp32 CSR, row-major B/C, plan and workspace created outside the loop, "
-                                   "20 back-to-back launches without L2 flush (our column is flushed): favours cuSPARSE",
+                                   "20 back-to-back launches without L2 flush (our column is flushed): favours cuSPARSE; "
+                                   "gespmm = this library's restatement of the published GE-SpMM algorithm, same protocol",
                            "geomean_speedup_vs_best_cusparse": round(float(torch.tensor(sp).log().mean().exp()), 3),
                            "rows": rows}
         except Exception as e:

@@ -3,8 +3,9 @@
 separate from the product library and links cuSPARSE; they are measurement baselines, not
 part of the SpMM/SDDMM path.
 
-``gespmm_*`` (a third-party kernel the reference vendors in SpMM/Baseline_kernel.cu:601-857)
-is not re-implemented; calling it raises.
+``gespmm_*``: the reference vendors a third-party kernel (SpMM/Baseline_kernel.cu:601-857); here the
+comparator is this library's own restatement of the published GE-SpMM algorithm (coalesced row
+caching + coarse-grained warp merging), see csrc/baselines.cu.
 """
 from __future__ import annotations
 
@@ -160,9 +161,34 @@ def cusparse_sddmm_profile(A, B, rowPtr, colIdx, val):
     return _gflops(colIdx.shape[0], A.shape[1], ms)
 
 
+def _gespmm(X, rowPtr, colIdx, val, out):
+    _check_cuda(X, "input", torch.float32, 2)
+    _check_cuda(rowPtr, "rowPtr", torch.int32, 1)
+    _check_cuda(colIdx, "colIdx", torch.int32, 1)
+    _check_cuda(val, "values", torch.float32, 1)
+    _ok(_bl().pspmm_baselines_gespmm(_ptr(rowPtr), _ptr(colIdx), _ptr(val), _ptr(X), _ptr(out),
+                                     ctypes.c_int64(rowPtr.shape[0] - 1), ctypes.c_int32(X.shape[1]),
+                                     ctypes.c_int64(X.stride(0)), ctypes.c_int64(out.stride(0)), _stream()))
+    return out
+
+
 def gespmm_compute(X, rowPtr, colIdx, val):
-    raise NotImplementedError("GE-SpMM is third-party code that is not part of this library")
+    out = torch.empty(rowPtr.shape[0] - 1, X.shape[1], dtype=torch.float32, device=X.device)
+    return _gespmm(X, rowPtr, colIdx, val, out)
+
+
+def gespmm_time_ms(X, rowPtr, colIdx, val, warmup=PROFILE_WARMUP, iters=PROFILE_ITERS):
+    out = torch.empty(rowPtr.shape[0] - 1, X.shape[1], dtype=torch.float32, device=X.device)
+    for _ in range(warmup):
+        _gespmm(X, rowPtr, colIdx, val, out)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        _gespmm(X, rowPtr, colIdx, val, out)
+    e1.record()
+    e1.synchronize()
+    return e0.elapsed_time(e1) / iters
 
 
 def gespmm_profile(X, rowPtr, colIdx, val):
-    raise NotImplementedError("GE-SpMM is third-party code that is not part of this library")
+    return _gflops(val.shape[0], X.shape[1], gespmm_time_ms(X, rowPtr, colIdx, val))

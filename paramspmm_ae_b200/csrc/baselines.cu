@@ -146,3 +146,72 @@ PB_API int pspmm_baselines_run(void *plan, void *stream)
                                   CUDA_R_32F, CUSPARSE_SDDMM_ALG_DEFAULT, p->workspace));
     return 0;
 }
+
+// ----------------------------------------------------------------------------- GE-SpMM comparator
+// A restatement, in this library's own code, of the algorithm published as GE-SpMM (Huang et al.,
+// SC 2020), which the reference times its kernels against (its vendored copy is
+// SpMM/Baseline_kernel.cu:601-857): one warp per row and per tile of 32*CF dense columns;
+// "coalesced row caching" = the warp loads 32 (column, value) pairs of the row into shared memory
+// with one coalesced access and every lane then walks them; "coarse-grained warp merging" = each
+// lane produces CF output columns (stride 32) so the cached pairs are reused CF times.
+// It is a comparator only: nothing in libpspmm uses it.
+template <int CF>
+__global__ void __launch_bounds__(256) gespmm_like_kernel(const int32_t *__restrict__ rowPtr,
+                                                          const int32_t *__restrict__ colIdx,
+                                                          const float *__restrict__ val,
+                                                          const float *__restrict__ B, float *__restrict__ C,
+                                                          int64_t n_rows, int dim, int64_t ldB, int64_t ldC)
+{
+    __shared__ int s_col[8][32];
+    __shared__ float s_val[8][32];
+    const int lane = threadIdx.x, w = threadIdx.y;
+    const int64_t row = (int64_t)blockIdx.x * blockDim.y + w;
+    if (row >= n_rows)
+        return;  // whole warps leave: row is warp-uniform
+    const int col0 = blockIdx.y * 32 * CF + lane;
+    const int lb = rowPtr[row], hb = rowPtr[row + 1];
+    float acc[CF];
+#pragma unroll
+    for (int j = 0; j < CF; ++j)
+        acc[j] = 0.f;
+    for (int ptr = lb; ptr < hb; ptr += 32) {
+        if (ptr + lane < hb) {
+            s_col[w][lane] = colIdx[ptr + lane];
+            s_val[w][lane] = val[ptr + lane];
+        }
+        __syncwarp();
+        const int n = hb - ptr < 32 ? hb - ptr : 32;
+        for (int k = 0; k < n; ++k) {
+            const float *brow = B + (int64_t)s_col[w][k] * ldB;
+            const float v = s_val[w][k];
+#pragma unroll
+            for (int j = 0; j < CF; ++j)
+                if (col0 + 32 * j < dim)
+                    acc[j] = fmaf(v, brow[col0 + 32 * j], acc[j]);
+        }
+        __syncwarp();
+    }
+#pragma unroll
+    for (int j = 0; j < CF; ++j)
+        if (col0 + 32 * j < dim)
+            C[row * ldC + col0 + 32 * j] = acc[j];
+}
+
+PB_API int pspmm_baselines_gespmm(const int32_t *rowPtr, const int32_t *colIdx, const float *val,
+                                  const float *B, float *C, int64_t n_rows, int32_t dim, int64_t ldB,
+                                  int64_t ldC, void *stream)
+{
+    if (!rowPtr || !B || !C || n_rows < 0 || dim <= 0)
+        return -1;
+    if (n_rows == 0)
+        return 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    const dim3 block(32, 8);
+    const unsigned gx = (unsigned)((n_rows + 7) / 8);
+    if (dim <= 32)
+        gespmm_like_kernel<1><<<dim3(gx, (dim + 31) / 32), block, 0, st>>>(rowPtr, colIdx, val, B, C, n_rows, dim, ldB, ldC);
+    else
+        gespmm_like_kernel<2><<<dim3(gx, (dim + 63) / 64), block, 0, st>>>(rowPtr, colIdx, val, B, C, n_rows, dim, ldB, ldC);
+    PB_CUDA(cudaGetLastError());
+    return 0;
+}

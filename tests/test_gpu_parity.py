@@ -323,6 +323,10 @@ def test_cusparse_comparators_agree(dev, oracle, mats):
     want = oracle.spmm_csr(rp, ci, v, B.numpy())
     close(baselines.cusparse_compute(B.to(dev), d.rowPtr, d.colIdx, d.val), want)
     close(baselines.cusparse_compute_csr_alg2(B.to(dev), d.rowPtr, d.colIdx, d.val), want)
+    close(baselines.gespmm_compute(B.to(dev), d.rowPtr, d.colIdx, d.val), want)
+    for dim in (20, 100):  # the row-caching comparator on ragged widths
+        B2 = dense(m.n_cols, dim, 8)
+        close(baselines.gespmm_compute(B2.to(dev), d.rowPtr, d.colIdx, d.val), oracle.spmm_csr(rp, ci, v, B2.numpy()))
     A = dense(m.n_rows, 64, 6)
     vals = d.val.clone()
     baselines.cusparse_sddmm_compute(A.to(dev), B.to(dev), d.rowPtr, d.colIdx, vals)
