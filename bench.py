@@ -72,6 +72,14 @@ def measured_peak():
     return FALLBACK_HBM_GBS, "fallback"
 
 
+def bench_config(n, dims):
+    """The workload description both arms print."""
+    return {"workload": "c2_dim_sweep", "rows_per_gpu": n, "nnz_per_row": NNZ_PER_ROW,
+            "matrices": list(MATRICES), "dims": list(dims), "launches_per_step": 3 * len(dims),
+            "l2": "flushed before every launch (256 MiB memset outside the timed events)",
+            "sharding": "row blocks, dense operand replicated, no collective"}
+
+
 def spmm_bytes(n_rows, n_cols, nnz, dim, n_seg=None):
     """Compulsory traffic of one SpMM: every array touched exactly once."""
     b = 4 * (n_rows + 1) + 8 * nnz + 4 * dim * n_cols + 4 * dim * n_rows
@@ -178,7 +186,7 @@ def run_reference(args):
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "c2_dim_sweep", "rows": args.rows, "nnz_per_row": NNZ_PER_ROW},
+        "config": bench_config(args.rows, args.dims),
         "cpu_baseline": {"value": val, "unit": "GFLOP/s", "cores": torch.get_num_threads(), "kind": "reference",
                          "sample": sample + "; torch.sparse.mm(CSR) on the host, the reference's CPU path"},
         "e2e": {"value": val, "unit": "GFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -460,10 +468,7 @@ def main():
             "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": step_ms_max,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
             "data": "synthetic",
-            "config": {"workload": "c2_dim_sweep", "rows_per_gpu": n, "nnz_per_row": NNZ_PER_ROW,
-                       "matrices": list(MATRICES), "dims": dims, "launches_per_step": len(cases),
-                       "l2": "flushed before every launch (256 MiB memset outside the timed events)",
-                       "sharding": "row blocks, dense operand replicated, no collective"},
+            "config": bench_config(n, dims),
             "e2e": e2e, "gpu_launches": launches, "clocks": clocks, "roofline": roofline,
             "cpu_baseline": cpu, "comparators": comparators, "wall_ms_per_step_incl_flush": wall / args.steps * 1e3, "sweep": sweep,
         }))
