@@ -18,7 +18,15 @@ Two targets:
   the oracle's restatement.  Skipped silently when the reference tree is not
   mounted (e.g. on a GPU box).
 
-The reference's CUDA kernels themselves are not built here: as shipped they do
+* ``build_ref_sddmm()`` -> ``oracle/_ref/ParamSDDMM_ref.so``: the reference's
+  complete SDDMM extension (``SDDMM/sddmm.cpp``, ``sddmm_kernel.cu``,
+  ``sddmm_baseline_kernel.cu``), compiled unmodified with nvcc for sm_100a from
+  the sources where they lie and linked against the installed libtorch and
+  cuSPARSE.  It needs a GPU to run: the GPU tests import it (when the file
+  travelled with the tree) to pin the oracle's SDDMM and ``genmask``
+  restatements against the reference's own CUDA kernels.  About three minutes.
+
+The reference's SpMM / SpCONV CUDA kernels are not built: as shipped they do
 not compile against the installed torch (removed ``Tensor::type()`` dispatch
 overload), so they are treated as unbuildable.
 """
@@ -99,6 +107,57 @@ def build_ref(force=False):
     return out
 
 
+def build_ref_sddmm(force=False):
+    """Compile the reference's SDDMM torch extension (host + CUDA) into oracle/_ref."""
+    src_dir = os.path.join(REF_ROOT, "SDDMM")
+    sources = [os.path.join(src_dir, f) for f in ("sddmm_kernel.cu", "sddmm_baseline_kernel.cu", "sddmm.cpp")]
+    if not all(os.path.isfile(f) for f in sources):
+        return None
+    out = os.path.join(REF_OUT, "ParamSDDMM_ref.so")
+    if not force and os.path.exists(out):
+        return out
+    import torch
+    from torch.utils import cpp_extension as ce
+
+    os.makedirs(REF_OUT, exist_ok=True)
+    nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+    incs = []
+    for p in ce.include_paths() + [sysconfig.get_paths()["include"], "/usr/local/cuda/include", src_dir]:
+        incs += ["-I", p]
+    defs = ["-DTORCH_EXTENSION_NAME=ParamSDDMM_ref", "-DTORCH_API_INCLUDE_EXTENSION_H",
+            "-D_GLIBCXX_USE_CXX11_ABI=%d" % int(torch._C._GLIBCXX_USE_CXX11_ABI)]
+    objs = []
+    for f in sources:
+        obj = os.path.join(REF_OUT, os.path.basename(f) + ".o")
+        if f.endswith(".cu"):
+            _run([nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-O1", "-std=c++17", "-Xcompiler",
+                  "-fPIC,-fopenmp", "--expt-relaxed-constexpr", "-c"] + defs + incs + [f, "-o", obj])
+        else:
+            _run(["g++", "-O2", "-fopenmp", "-fPIC", "-std=c++17", "-c"] + defs + incs + [f, "-o", obj])
+        objs.append(obj)
+    libdir = ce.library_paths()[0]
+    _run(["g++", "-shared", "-fopenmp"] + objs + ["-o", out, "-L", libdir, "-Wl,-rpath," + libdir,
+          "-L/usr/local/cuda/lib64", "-Wl,-rpath,/usr/local/cuda/lib64", "-ltorch", "-ltorch_cpu", "-ltorch_cuda",
+          "-lc10", "-lc10_cuda", "-ltorch_python", "-lcudart", "-lcusparse"])
+    for o in objs:
+        os.remove(o)
+    return out
+
+
+def load_ref_sddmm():
+    """Import the compiled reference SDDMM extension, or return None when it is not there."""
+    path = os.path.join(REF_OUT, "ParamSDDMM_ref.so")
+    if not os.path.exists(path):
+        return None
+    import importlib.util
+    import torch  # noqa: F401  (libtorch must be loaded first)
+
+    spec = importlib.util.spec_from_file_location("ParamSDDMM_ref", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
 def load_ref():
     """Import the compiled reference host module, or return None when it is not there."""
     path = os.path.join(REF_OUT, "ParamSpMM_ref.so")
@@ -116,3 +175,4 @@ def load_ref():
 if __name__ == "__main__":
     print(build_oracle(force="--force" in sys.argv))
     print(build_ref(force="--force" in sys.argv))
+    print(build_ref_sddmm(force="--force" in sys.argv))

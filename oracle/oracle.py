@@ -15,10 +15,12 @@ Pinning status
   the reference calls) and golden vectors.
 * ``spmm_*``: pinned against ``torch.sparse.mm`` on CPU, the reference's own
   acceptance oracle (verification.py:18-46), and scipy ``csr @ dense``.
-* ``genmask``, ``sddmm_*``: the reference holds no golden vectors for them and
-  its CUDA code cannot run without a GPU: parity unpinned here beyond
-  hand-worked cases; on a GPU box the CUDA kernels are compared to this
-  restatement.
+* ``genmask``, ``sddmm_*``: the reference holds no golden vectors for them;
+  they are pinned on a GPU box against the reference's own CUDA kernels
+  (``oracle/_ref/ParamSDDMM_ref.so``, the reference's SDDMM extension compiled
+  unmodified for sm_100a, tests/test_gpu_reference_cuda.py: ``genmask`` bit for
+  bit, SDDMM within 1e-5 relative).  Without a GPU only hand-worked cases pin
+  them.
 * decider decode rules: pinned by hand-evaluated cases of decider.py:63-80.
 """
 from __future__ import annotations

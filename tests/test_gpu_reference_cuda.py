@@ -1,0 +1,89 @@
+"""GPU parity against the reference's OWN CUDA kernels for SDDMM and genmask.
+
+oracle/build_oracle.py::build_ref_sddmm compiles the reference's SDDMM extension (sddmm.cpp,
+sddmm_kernel.cu, sddmm_baseline_kernel.cu) unmodified for sm_100a into oracle/_ref/; these tests
+run it next to the oracle's restatement (which this pins) and next to this library's kernels.
+They are skipped when that file is absent (it is built only where the reference tree is mounted and
+travels with the tree as a binary).
+
+The reference kernels are called inside the domain their launchers support (read from
+SDDMM/sddmm_kernel.cu:144-185, 249-290): CF = ceil(dim / 32) <= 4, so that the launch has one
+column tile, contiguous fp32 operands, int32 indices, A with one row per (block-)row."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+RTOL, ATOL = 1e-5, 1e-4
+
+
+@pytest.fixture(scope="module")
+def ref():
+    from oracle import build_oracle
+    mod = build_oracle.load_ref_sddmm()
+    if mod is None:
+        pytest.skip("oracle/_ref/ParamSDDMM_ref.so is not there (built only where the reference tree is mounted)")
+    return mod
+
+
+@pytest.fixture(scope="module")
+def graphs():
+    from paramspmm_ae_b200 import synth
+    return {"powerlaw": synth.powerlaw_graph(3001, 24000, seed=1),
+            "rmat": synth.with_empty_rows(synth.rmat(12, 60000, seed=23), every=5)}
+
+
+def _close(got, want):
+    np.testing.assert_allclose(got.detach().cpu().numpy(), np.asarray(want), rtol=RTOL, atol=ATOL)
+
+
+@pytest.mark.parametrize("name", ["powerlaw", "rmat"])
+@pytest.mark.parametrize("dim", [32, 48, 64, 100, 128])
+def test_csr_sddmm_against_reference_cuda(ref, graphs, name, dim):
+    from oracle import oracle as orc
+    from paramspmm_ae_b200 import ops, synth
+    dev = torch.device("cuda:0")
+    m = graphs[name]
+    d = m.to(dev)
+    A = synth.dense_uniform(m.n_rows, dim, 700 + dim).to(dev)
+    B = synth.dense_uniform(m.n_cols, dim, 800 + dim).to(dev)
+    CF = (dim + 31) // 32
+    theirs = ref.csr_sddmm(A, B, d.rowPtr, d.colIdx, d.val, CF, 8)
+    torch.cuda.synchronize()
+    # the restatement is pinned by the reference's kernel ...
+    want = orc.sddmm_csr(*m.numpy()[:2], A.cpu().numpy(), B.cpu().numpy())
+    _close(theirs, want)
+    # ... and this library's kernel agrees with it
+    _close(ops.csr_sddmm(A, B, d.rowPtr, d.colIdx, d.val, CF, 8), theirs.cpu().numpy())
+    rps, tr = ops.split_csr(m.rowPtr, 32)
+    rps, tr = rps.to(dev), tr.to(dev)
+    theirs_split = ref.csr_split_sddmm(A, B, rps, d.colIdx, d.val, tr, CF, 8)
+    torch.cuda.synchronize()
+    _close(theirs_split, want)
+    _close(ops.csr_split_sddmm(A, B, rps, d.colIdx, d.val, tr, CF, 8), theirs_split.cpu().numpy())
+
+
+@pytest.mark.parametrize("name", ["powerlaw", "rmat"])
+def test_genmask_and_block_sddmm_against_reference_cuda(ref, graphs, name):
+    from oracle import oracle as orc
+    from paramspmm_ae_b200 import ops, synth
+    dev = torch.device("cuda:0")
+    m = graphs[name]
+    rpb, cb, vb = ops.bcsr_from_csr(m.rowPtr, m.colIdx, m.val, m.n_cols, 2)
+    rpb_d, cb_d, vb_d, rp_d = rpb.to(dev), cb.to(dev), vb.to(dev), m.rowPtr.to(dev)
+    theirs = ref.genmask(rpb_d, rp_d, vb_d, m.nnz)
+    torch.cuda.synchronize()
+    want = orc.genmask(rpb.numpy(), m.rowPtr.numpy(), vb.numpy(), m.nnz)
+    assert np.array_equal(theirs.cpu().numpy(), want)                      # pins the restatement, bit for bit
+    assert torch.equal(ops.genmask(rpb_d, rp_d, vb_d, m.nnz), theirs)      # and this library's kernel
+    nbr = rpb.shape[0] - 1
+    for dim in (64, 100):
+        A = synth.dense_uniform(nbr * 2, dim, 500 + dim).to(dev)
+        B = synth.dense_uniform(m.n_cols, dim, 600 + dim).to(dev)
+        CF = (dim + 31) // 32
+        theirs_b = ref.bcsr_sddmm(A, B, rpb_d, cb_d, vb_d, CF, 8)
+        torch.cuda.synchronize()
+        want_b = orc.sddmm_bcsr(rpb.numpy(), cb.numpy(), vb.numpy(), A.cpu().numpy(), B.cpu().numpy())
+        _close(theirs_b, want_b)
+        _close(ops.bcsr_sddmm(A, B, rpb_d, cb_d, vb_d, CF, 8), theirs_b.cpu().numpy())
