@@ -26,9 +26,13 @@ Two targets:
   travelled with the tree) to pin the oracle's SDDMM and ``genmask``
   restatements against the reference's own CUDA kernels.  About three minutes.
 
-The reference's SpMM / SpCONV CUDA kernels are not built: as shipped they do
-not compile against the installed torch (removed ``Tensor::type()`` dispatch
-overload), so they are treated as unbuildable.
+* ``build_ref_spmm_cuda()`` -> ``oracle/_ref/ParamSpMM_cuda_ref.so``: the
+  reference's complete SpMM extension (``SpMM/SpMM.cpp``, ``SpMM_kernel.cu``,
+  ``Baseline_kernel.cu``), sources unmodified.  They dispatch on the deprecated
+  ``Tensor::type()``, whose ATen overload newer torch releases removed;
+  ``oracle/torch_compat_shim.h`` (force-included) restores that one overload.
+  About seven minutes.  (The SpCONV extension is the same kernels behind a
+  GEMM and is not built.)
 """
 from __future__ import annotations
 
@@ -107,13 +111,24 @@ def build_ref(force=False):
     return out
 
 
-def build_ref_sddmm(force=False):
-    """Compile the reference's SDDMM torch extension (host + CUDA) into oracle/_ref."""
-    src_dir = os.path.join(REF_ROOT, "SDDMM")
-    sources = [os.path.join(src_dir, f) for f in ("sddmm_kernel.cu", "sddmm_baseline_kernel.cu", "sddmm.cpp")]
+_REF_EXTENSIONS = {
+    # module name -> (directory in the reference tree, sources, needs the ATen compatibility shim)
+    "ParamSDDMM_ref": ("SDDMM", ("sddmm_kernel.cu", "sddmm_baseline_kernel.cu", "sddmm.cpp"), False),
+    "ParamSpMM_cuda_ref": ("SpMM", ("SpMM_kernel.cu", "Baseline_kernel.cu", "SpMM.cpp"), True),
+}
+
+
+def build_ref_extension(module, force=False):
+    """Compile one of the reference's torch extensions (host + CUDA, unmodified, from where the
+    sources lie) for sm_100a into oracle/_ref/<module>.so.  The SpMM sources dispatch on the
+    deprecated ``Tensor::type()``; ``oracle/torch_compat_shim.h`` is force-included to restore the
+    ATen overload they rely on."""
+    sub, names, shim = _REF_EXTENSIONS[module]
+    src_dir = os.path.join(REF_ROOT, sub)
+    sources = [os.path.join(src_dir, f) for f in names]
     if not all(os.path.isfile(f) for f in sources):
         return None
-    out = os.path.join(REF_OUT, "ParamSDDMM_ref.so")
+    out = os.path.join(REF_OUT, module + ".so")
     if not force and os.path.exists(out):
         return out
     import torch
@@ -124,11 +139,13 @@ def build_ref_sddmm(force=False):
     incs = []
     for p in ce.include_paths() + [sysconfig.get_paths()["include"], "/usr/local/cuda/include", src_dir]:
         incs += ["-I", p]
-    defs = ["-DTORCH_EXTENSION_NAME=ParamSDDMM_ref", "-DTORCH_API_INCLUDE_EXTENSION_H",
+    defs = ["-DTORCH_EXTENSION_NAME=" + module, "-DTORCH_API_INCLUDE_EXTENSION_H",
             "-D_GLIBCXX_USE_CXX11_ABI=%d" % int(torch._C._GLIBCXX_USE_CXX11_ABI)]
+    if shim:
+        defs += ["-include", os.path.join(HERE, "torch_compat_shim.h")]
     objs = []
     for f in sources:
-        obj = os.path.join(REF_OUT, os.path.basename(f) + ".o")
+        obj = os.path.join(REF_OUT, module + "." + os.path.basename(f) + ".o")
         if f.endswith(".cu"):
             _run([nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-O1", "-std=c++17", "-Xcompiler",
                   "-fPIC,-fopenmp", "--expt-relaxed-constexpr", "-c"] + defs + incs + [f, "-o", obj])
@@ -144,18 +161,34 @@ def build_ref_sddmm(force=False):
     return out
 
 
-def load_ref_sddmm():
-    """Import the compiled reference SDDMM extension, or return None when it is not there."""
-    path = os.path.join(REF_OUT, "ParamSDDMM_ref.so")
+def build_ref_sddmm(force=False):
+    return build_ref_extension("ParamSDDMM_ref", force)
+
+
+def build_ref_spmm_cuda(force=False):
+    return build_ref_extension("ParamSpMM_cuda_ref", force)
+
+
+def load_ref_extension(module):
+    """Import a compiled reference extension, or return None when it is not there."""
+    path = os.path.join(REF_OUT, module + ".so")
     if not os.path.exists(path):
         return None
     import importlib.util
     import torch  # noqa: F401  (libtorch must be loaded first)
 
-    spec = importlib.util.spec_from_file_location("ParamSDDMM_ref", path)
+    spec = importlib.util.spec_from_file_location(module, path)
     mod = importlib.util.module_from_spec(spec)
     spec.loader.exec_module(mod)
     return mod
+
+
+def load_ref_sddmm():
+    return load_ref_extension("ParamSDDMM_ref")
+
+
+def load_ref_spmm_cuda():
+    return load_ref_extension("ParamSpMM_cuda_ref")
 
 
 def load_ref():
@@ -176,3 +209,4 @@ if __name__ == "__main__":
     print(build_oracle(force="--force" in sys.argv))
     print(build_ref(force="--force" in sys.argv))
     print(build_ref_sddmm(force="--force" in sys.argv))
+    print(build_ref_spmm_cuda(force="--force" in sys.argv))
