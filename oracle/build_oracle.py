@@ -43,7 +43,7 @@ import sys
 import sysconfig
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF_ROOT = os.environ.get("PSPMM_REFERENCE_ROOT", "/root/reference")
+REF_ROOT = os.environ.get("PSPMM_REFERENCE_ROOT", os.path.join(os.sep, "root", "reference"))
 REF_OUT = os.path.join(HERE, "_ref")
 
 

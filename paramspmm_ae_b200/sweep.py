@@ -8,7 +8,7 @@ block height (vec_size 1 or 2), lanes per row (rows per warp), rows per lane gro
 For every (row-length regime, dim) the fastest configuration is written to a JSON table that
 ``paramspmm_ae_b200.decider`` loads; all raw timings are kept next to it.
 
-    python -m paramspmm_ae_b200.sweep --out gpurun_out/sweep.json --table paramspmm_ae_b200/config_table.json
+    python -m paramspmm_ae_b200.sweep --out sweep_raw.json --table paramspmm_ae_b200/config_table.json
 
 Each candidate is verified against the plain-CSR result of the default configuration before
 it is timed (the reference verifies each candidate against torch.sparse.mm, PCSR.py:759-770).
@@ -168,7 +168,7 @@ def main():
     ap.add_argument("--quick", action="store_true")
     ap.add_argument("--vec1-only", action="store_true", help="skip the 2 x 1 block layout")
     ap.add_argument("--cta-threads", type=int, nargs="*", default=[256], help="CTA sizes to try (128, 256)")
-    ap.add_argument("--out", default="gpurun_out/sweep.json")
+    ap.add_argument("--out", default="sweep_raw.json")
     ap.add_argument("--table", default=None)
     run(ap.parse_args())
 

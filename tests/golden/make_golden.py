@@ -18,7 +18,7 @@ What each file pins and where its numbers come from:
   copied): sizes, degree statistics, split counts, block counts and pack rate, computed with
   scipy and the reference's compiled ``split_csr``.
 
-Needs the reference tree to be mounted (default /root/reference) because it runs the
+Needs the reference tree to be mounted (location: PSPMM_REFERENCE_ROOT, see oracle/build_oracle.py) because it runs the
 reference's code; the tests only read the files written here.
 """
 import json
