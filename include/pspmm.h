@@ -55,6 +55,8 @@ typedef struct pspmm_cfg {
     int32_t cta_threads;     /* 128 or 256 */
     int32_t rows_per_group;  /* consecutive (split-)rows one lane group owns: 1..16 */
     int32_t gather_batch;    /* 16-byte gathers a lane keeps in flight: 2, 4, 8 or 16 (registers vs occupancy) */
+    int32_t col_tile;        /* SpMM only: dense columns per launch (a multiple of 4, e.g. 128); wider products run as
+                                several launches over column ranges.  0 = one launch */
     int32_t hint_CF;         /* legacy coarsening factor, validated only */
     int32_t hint_blkWarpNum; /* legacy warps per block, validated only */
 } pspmm_cfg;

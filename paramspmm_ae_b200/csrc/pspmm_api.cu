@@ -56,6 +56,8 @@ int pspmm_validate_cfg(const pspmm_cfg *cfg, bool sddmm)
     if (cfg->gather_batch != 0 && cfg->gather_batch != 2 && cfg->gather_batch != 4 &&
         cfg->gather_batch != 8 && cfg->gather_batch != 16)
         return PSPMM_E_CONFIG;
+    if (cfg->col_tile < 0 || cfg->col_tile % 4 != 0)
+        return PSPMM_E_CONFIG;
     return PSPMM_OK;
 }
 
@@ -281,6 +283,22 @@ static int spmm_launch(const int32_t *segPtr, const int32_t *target_row, int64_t
     if (n_seg == 0) {  // nothing stored: the product is zero
         PSPMM_CUDA_TRY(cudaMemset2DAsync(C, (size_t)ldC * 4, 0, (size_t)dim * 4,
                                          (size_t)(n_out_blk_rows * V), st));
+        return PSPMM_OK;
+    }
+    if (cfg && cfg->col_tile > 0 && cfg->col_tile < dim) {
+        // Column ranges as separate launches: a 128-wide launch keeps one 16-byte slice per lane,
+        // and a narrow remainder gets a narrow lane group instead of idle lanes in a wide one.
+        for (int32_t off = 0; off < dim; off += cfg->col_tile) {
+            const int32_t w = dim - off < cfg->col_tile ? dim - off : cfg->col_tile;
+            pspmm_cfg sub = *cfg;
+            sub.col_tile = 0;
+            if (sub.lanes_per_row * (sub.vec_width ? sub.vec_width : 4) > w)
+                sub.lanes_per_row = 0;  // let the launch pick the group width for the narrow range
+            rc = spmm_launch(segPtr, target_row, n_seg, colIdx, val, V, B + off, C + off, n_out_blk_rows, n_cols, w,
+                             ldB, ldC, &sub, st);
+            if (rc)
+                return rc;
+        }
         return PSPMM_OK;
     }
     LaunchShape s;

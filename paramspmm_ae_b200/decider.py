@@ -97,7 +97,7 @@ class Plan(dict):
 
     def kernel_cfg(self):
         return {k: int(self.get(k, 0) or 0)
-                for k in ("lanes_per_row", "vec_width", "cta_threads", "rows_per_group", "gather_batch")}
+                for k in ("lanes_per_row", "vec_width", "cta_threads", "rows_per_group", "gather_batch", "col_tile")}
 
 
 def choose(stats, dim, op="spmm"):
@@ -108,7 +108,7 @@ def choose(stats, dim, op="spmm"):
     if e is None:
         e = {"if_split": 1 if reg.endswith("skewed") else 0, "vec_size": 1}
     plan = Plan(if_split=0, vec_size=1, granularity=None, lanes_per_row=0, vec_width=0, cta_threads=0,
-                rows_per_group=0, gather_batch=0)
+                rows_per_group=0, gather_batch=0, col_tile=0)
     plan.update(e)
     plan["regime"] = reg
     if plan["if_split"] and not plan.get("granularity"):
@@ -167,7 +167,7 @@ def install_tuner():
         size = "short" if mean_len < 24 else ("medium" if mean_len < 128 else "long")
         ent = table().get("entries", {}).get(op, {})
         e = (ent.get(size + "_even", {}) or {}).get(_dim_key(dim)) or {}
-        return {k: int(e.get(k, 0) or 0) for k in ("lanes_per_row", "vec_width", "cta_threads", "rows_per_group", "gather_batch")}
+        return {k: int(e.get(k, 0) or 0) for k in ("lanes_per_row", "vec_width", "cta_threads", "rows_per_group", "gather_batch", "col_tile")}
 
     ops.tuner = tuner
     return tuner

@@ -61,12 +61,15 @@ def candidates(dim, regime, quick):
     else:
         grans = [0]
     vecs = (1,) if (quick or VEC1_ONLY) else (1, 2)
-    for vec, gran, lpr, rpg, mlp, thr in itertools.product(vecs, grans, lprs, rpgs, mlps, CTA_THREADS):
+    tiles = (0, 128) if dim > 128 else (0,)
+    for vec, gran, lpr, rpg, mlp, thr, tile in itertools.product(vecs, grans, lprs, rpgs, mlps, CTA_THREADS, tiles):
         if vec != 1 and mlp != 8:
             continue  # block kernels are built with one gather depth
+        if tile and (vec != 1 or lpr != 32):
+            continue  # column ranges of 128: one 16-byte slice per lane of a full warp
         yield {"vec_size": vec, "if_split": int(gran > 0), "granularity": gran or None,
                "lanes_per_row": lpr, "vec_width": vw, "rows_per_group": rpg, "cta_threads": thr,
-               "gather_batch": mlp}
+               "gather_batch": mlp, "col_tile": tile}
 
 
 class Layouts:
@@ -125,7 +128,7 @@ def run(args):
                     out = torch.empty(nbr * V, dim, device=dev)
                     cfg = _lib.make_cfg(lanes_per_row=cand["lanes_per_row"], vec_width=cand["vec_width"],
                                         cta_threads=cand["cta_threads"], rows_per_group=cand["rows_per_group"],
-                                        gather_batch=cand["gather_batch"])
+                                        gather_batch=cand["gather_batch"], col_tile=cand.get("col_tile", 0))
                     ops.spmm_into(out, B, rp, ci, v, target_row=tr, V=V, n_out_rows=nbr, cfg=cfg)
                     # hub rows sum thousands of terms in a different order: scale the floor
                     bad = ((out[: m.n_rows] - ref).abs() > tol * 50).sum().item()

@@ -362,6 +362,32 @@ def test_full_size_properties(dev):
     torch.testing.assert_close(torch.sparse.mm(s, B1), c1, rtol=1e-5, atol=1e-6 * scale * 50)
 
 
+def test_spmm_column_tiles(dev, oracle, mats):
+    """col_tile runs a wide product as several launches over column ranges: same result, plain and
+    split layouts, widths that are and are not multiples of the tile, strided output."""
+    from paramspmm_ae_b200 import _lib, ops
+    m = mats["rmat"]
+    rp, ci, v = m.numpy()
+    d = m.to(dev)
+    rps, tr = ops.split_csr(m.rowPtr, 32)
+    rps, tr = rps.to(dev), tr.to(dev)
+    for dim in (132, 144, 256, 260):
+        B = dense(m.n_cols, dim, 600 + dim)
+        want = oracle.spmm_csr(rp, ci, v, B.numpy())
+        Bd = B.to(dev)
+        for tile, lanes in ((128, 32), (64, 0), (4, 0)):
+            cfg = _lib.make_cfg(lanes_per_row=lanes, col_tile=tile, rows_per_group=4, gather_batch=8)
+            out = torch.full((m.n_rows, dim + 8), float("nan"), device=dev)[:, :dim]
+            ops.spmm_into(out, Bd, d.rowPtr, d.colIdx, d.val, cfg=cfg)
+            close(out, want)
+            out = torch.full((m.n_rows, dim), float("nan"), device=dev)
+            ops.spmm_into(out, Bd, rps, d.colIdx, d.val, target_row=tr, n_out_rows=m.n_rows, cfg=cfg)
+            close(out, want)
+    with pytest.raises(_lib.PspmmError):
+        ops.spmm_into(torch.empty(m.n_rows, 132, device=dev), dense(m.n_cols, 132, 1).to(dev), d.rowPtr, d.colIdx,
+                      d.val, cfg=_lib.make_cfg(col_tile=6))
+
+
 # ----------------------------------------------------------------------------- fused AGNN aggregation
 @pytest.mark.parametrize("dim", [4, 16, 32, 48, 64, 100, 128, 256])
 @pytest.mark.parametrize("softmax", [True, False])
