@@ -14,7 +14,9 @@ Pinning status
 * ``bcsr_build``: pinned against scipy's ``tobsr`` (the third-party routine
   the reference calls) and golden vectors.
 * ``spmm_*``: pinned against ``torch.sparse.mm`` on CPU, the reference's own
-  acceptance oracle (verification.py:18-46), and scipy ``csr @ dense``.
+  acceptance oracle (verification.py:18-46), and scipy ``csr @ dense``; on a
+  GPU box also against the reference's own CUDA SpMM kernels
+  (``oracle/_ref/ParamSpMM_cuda_ref.so``, tests/test_gpu_reference_cuda.py).
 * ``genmask``, ``sddmm_*``: the reference holds no golden vectors for them;
   they are pinned on a GPU box against the reference's own CUDA kernels
   (``oracle/_ref/ParamSDDMM_ref.so``, the reference's SDDMM extension compiled

@@ -76,6 +76,15 @@ class GINFunction(torch.autograd.Function):
         return d_input, d_weight, None
 
 
+# Under torch.no_grad() an AGNN layer on a plain or split CSR operator runs as the fused kernel
+# (SDDMM -> scale -> SpMM in one pass).  Set to False to always use the three-kernel composition.
+FUSE_AGNN_INFERENCE = True
+
+
+def _can_fuse(P, dim):
+    return getattr(P, "vec_size", 1) == 1 and dim % 4 == 0 and dim <= 256
+
+
 class AGNNFunction(torch.autograd.Function):
     @staticmethod
     def forward(ctx, X, weights, attention_w, ParamSpMM, colIdx):
@@ -136,4 +145,13 @@ class AGNNConv(_Conv):
         self.attention_w = torch.nn.Parameter(torch.randn(1, n_heads))
 
     def forward(self, X, spmm_dict, colIdx):
-        return AGNNFunction.apply(X, self.weights, self.attention_w, self._operator(spmm_dict), colIdx)
+        P = self._operator(spmm_dict)
+        if FUSE_AGNN_INFERENCE and not torch.is_grad_enabled() and _can_fuse(P, self.weights.size(1)):
+            # No gradient will be asked for: scores, scaling and aggregation in one kernel, without
+            # the per-edge array the backward would need.
+            from . import ops
+            Xp = torch.mm(X, self.weights)
+            split = P.target_row is not None
+            return ops.agnn_fused(Xp, Xp, P.rowPtr, P.colIdx, float(self.attention_w.reshape(())), softmax=False,
+                                  target_row=P.target_row, n_out_rows=P.mtx_nodes if split else None)
+        return AGNNFunction.apply(X, self.weights, self.attention_w, P, colIdx)

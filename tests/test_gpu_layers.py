@@ -80,6 +80,12 @@ def test_gin_and_agnn_layers_match_dense_algebra():
     mask = (A != 0).double()
     E = (Xp @ Xp.t()) * mask * float(agnn.attention_w.detach().reshape(()))
     _close(out.detach(), E @ Xp)
+    # inference (no gradient): the layer itself switches to the fused kernel
+    with torch.no_grad():
+        _close(agnn(X, {32: Ps}, g.colIdx.to(dev)), E @ Xp)
+        rps, tr = ops.split_csr(g.rowPtr, 8)
+        Pss = pcsr.pcsr_sddmm(None, 1, True, g.n_rows, g.nnz, rps, g.colIdx, g.val, tr, CF=1, blkWarpNum=8)
+        _close(agnn(X, {32: Pss}, g.colIdx.to(dev)), E @ Xp)
     # the one-kernel form of the same forward
     fused = ops.agnn_fused(Xp.float().contiguous(), Xp.float().contiguous(), g.rowPtr.to(dev), g.colIdx.to(dev),
                            float(agnn.attention_w.detach().reshape(())), softmax=False)

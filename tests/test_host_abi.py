@@ -192,3 +192,25 @@ def test_dropin_modules_expose_reference_names():
     for mod, names in ((ParamSpMM, spmm_names), (ParamSDDMM, sddmm_names), (ParamSpCONV, conv_names)):
         for n in names:
             assert callable(getattr(mod, n)), "%s.%s missing" % (mod.__name__, n)
+
+
+def test_table_plans_become_valid_kernel_configurations():
+    """Every entry of the measured table decodes into a pspmm_cfg the library accepts (including
+    the column-tile field), for every regime and every dim key."""
+    import ctypes
+    from paramspmm_ae_b200 import _lib, decider
+    lib = _lib.lib()
+    tab = decider.load_table()
+    seen = 0
+    for regime, per_dim in tab["entries"]["spmm"].items():
+        for dim_key, e in per_dim.items():
+            plan = decider.Plan(if_split=0, vec_size=1, granularity=None)
+            plan.update(e)
+            cfg = _lib.make_cfg(**plan.kernel_cfg())
+            assert cfg.col_tile in (0, 128)
+            dim = int(dim_key)
+            rc = lib.pspmm_resolve_cfg(ctypes.byref(cfg), dim, dim, dim, 1, ctypes.c_void_p(256), ctypes.c_void_p(256))
+            assert rc == _lib.PSPMM_OK, (regime, dim_key, e)
+            assert cfg.lanes_per_row in (2, 4, 8, 16, 32) and cfg.cta_threads in (128, 256)
+            seen += 1
+    assert seen >= 64
