@@ -89,3 +89,25 @@ def test_sharded_spmm_two_layers_gloo(world, exchange):
         assert p.exitcode == 0
     assert all(r[1] and r[2] for r in res), res
     assert sum(r[3] for r in res) == 1201
+
+
+def test_needed_rows_exchange_single_rank():
+    """world = 1: the compact operand holds exactly the referenced rows, in column order, and the
+    renumbered columns reproduce the product (no process group involved)."""
+    from oracle import oracle as orc
+    m = synth.with_empty_rows(synth.powerlaw_graph(801, 3000, seed=9), every=3)
+    B = synth.dense_uniform(m.n_cols, 12, 4)
+
+    def local_spmm(out, Bc, rowPtr, colIdx, val):
+        out.copy_(torch.from_numpy(orc.spmm_csr(rowPtr.numpy(), colIdx.numpy(), val.numpy(),
+                                                np.ascontiguousarray(Bc.numpy()))))
+        return out
+
+    op = shard.ShardedSpMM(m.rowPtr, m.colIdx, m.val, m.n_cols, 0, 1, device="cpu", local_spmm=local_spmm,
+                           exchange="needed")
+    used = torch.unique(m.colIdx.long())
+    assert op.n_needed == used.numel() < m.n_cols
+    assert torch.equal(op.send_rows, used)
+    got = op.forward(B)
+    want = orc.spmm_csr(*m.numpy(), B.numpy())
+    assert np.allclose(got.numpy(), want, rtol=1e-5, atol=1e-5)
