@@ -103,8 +103,20 @@ class Plan(dict):
 def choose(stats, dim, op="spmm"):
     """Table lookup (regime x dim); falls back to a rule when the table has no entry."""
     reg = regime(stats)
-    ent = table().get("entries", {}).get(op, {}).get(reg, {})
+    per_regime = table().get("entries", {}).get(op, {})
+    ent = per_regime.get(reg, {})
+    if not ent:
+        # A regime the sweep has not measured borrows from the nearest measured one of the same
+        # skew class (kernel shape depends on the dim first, the row-length class second).
+        size, skew = reg.split("_")
+        order = {"short": ("medium", "long"), "medium": ("short", "long"), "long": ("medium", "short")}[size]
+        for other in order:
+            ent = per_regime.get(other + "_" + skew, {})
+            if ent:
+                break
     e = ent.get(_dim_key(dim)) or ent.get("*")
+    if e is not None and ent is not per_regime.get(reg) and e.get("if_split"):
+        e = dict(e, granularity=None)  # a borrowed partition length does not transfer: use the rule
     if e is None:
         e = {"if_split": 1 if reg.endswith("skewed") else 0, "vec_size": 1}
     plan = Plan(if_split=0, vec_size=1, granularity=None, lanes_per_row=0, vec_width=0, cta_threads=0,
