@@ -214,3 +214,27 @@ def test_table_plans_become_valid_kernel_configurations():
             assert cfg.lanes_per_row in (2, 4, 8, 16, 32) and cfg.cta_threads in (128, 256)
             seen += 1
     assert seen >= 64
+
+
+def test_header_is_plain_c_and_declares_what_the_python_shim_binds(tmp_path):
+    """include/pspmm.h must compile as C99 and as C++ on its own (it is what a foreign-language
+    binding includes), and every function the ctypes shim binds must be declared in it."""
+    import os
+    import re
+    import subprocess
+    from paramspmm_ae_b200 import _lib
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    hdr = os.path.join(root, "include", "pspmm.h")
+    subprocess.run(["gcc", "-std=c99", "-Wall", "-Werror", "-fsyntax-only", "-x", "c", hdr], check=True)
+    subprocess.run(["g++", "-std=c++14", "-Wall", "-Werror", "-fsyntax-only", "-x", "c++", hdr], check=True)
+    text = open(hdr).read()
+    declared = set(re.findall(r"PSPMM_API\s+[\w\s\*]+?\b(pspmm_\w+)\s*\(", text))
+    assert set(_lib.EXPORTED) <= declared, sorted(set(_lib.EXPORTED) - declared)
+    # a C caller can fill the configuration struct by name
+    src = tmp_path / "use.c"
+    src.write_text('#include "pspmm.h"\nint main(void) { pspmm_cfg c = {0}; c.col_tile = 128; c.hint_CF = 2; '
+                   'return pspmm_version() > 0 && c.col_tile == 128 ? 0 : 1; }\n')
+    exe = tmp_path / "use"
+    subprocess.run(["gcc", "-std=c99", "-I", os.path.join(root, "include"), str(src), "-o", str(exe),
+                    _lib.LIB_PATH, "-Wl,-rpath," + os.path.dirname(_lib.LIB_PATH)], check=True)
+    assert subprocess.run([str(exe)]).returncode == 0
