@@ -52,7 +52,7 @@ extern "C" {
 typedef struct pspmm_cfg {
     int32_t lanes_per_row;   /* lanes that share one (split-)row: 1,2,4,8,16,32; rows per warp = 32 / this */
     int32_t vec_width;       /* floats per lane per load of a dense row: 1, 2 or 4 (128-bit) */
-    int32_t cta_threads;     /* 128 or 256 */
+    int32_t cta_threads;     /* 32, 64, 128 or 256 */
     int32_t rows_per_group;  /* consecutive (split-)rows one lane group owns: 1..16 */
     int32_t gather_batch;    /* 16-byte gathers a lane keeps in flight: 2, 4, 8 or 16 (registers vs occupancy) */
     int32_t col_tile;        /* SpMM only: dense columns per launch (a multiple of 4, e.g. 128); wider products run as

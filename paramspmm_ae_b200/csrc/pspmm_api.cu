@@ -25,7 +25,7 @@ extern "C" const char *pspmm_strerror(int code)
     switch (code) {
     case PSPMM_OK: return "ok";
     case PSPMM_E_ARG: return "invalid argument (null pointer, negative size or leading dimension smaller than dim)";
-    case PSPMM_E_CONFIG: return "invalid configuration (CF must be 1..8 (1..4 for SDDMM), blkWarpNum 4 or 8, lanes_per_row a power of two <= 32, vec_width 1/2/4, cta_threads 128/256, rows_per_group 1..16)";
+    case PSPMM_E_CONFIG: return "invalid configuration (CF must be 1..8 (1..4 for SDDMM), blkWarpNum 4 or 8, lanes_per_row a power of two <= 32, vec_width 1/2/4, cta_threads 32/64/128/256, rows_per_group 1..16)";
     case PSPMM_E_CUDA: return "CUDA error (see pspmm_last_cuda_error)";
     case PSPMM_E_UNSUPPORTED: return "unsupported combination";
     case PSPMM_E_RANGE: return "size exceeds the int32 index range";
@@ -49,7 +49,8 @@ int pspmm_validate_cfg(const pspmm_cfg *cfg, bool sddmm)
         return PSPMM_E_CONFIG;
     if (cfg->vec_width != 0 && cfg->vec_width != 1 && cfg->vec_width != 2 && cfg->vec_width != 4)
         return PSPMM_E_CONFIG;
-    if (cfg->cta_threads != 0 && cfg->cta_threads != 128 && cfg->cta_threads != 256)
+    if (cfg->cta_threads != 0 && cfg->cta_threads != 32 && cfg->cta_threads != 64 && cfg->cta_threads != 128 &&
+        cfg->cta_threads != 256)
         return PSPMM_E_CONFIG;
     if (cfg->rows_per_group < 0 || cfg->rows_per_group > PSPMM_RPG_MAX)
         return PSPMM_E_CONFIG;

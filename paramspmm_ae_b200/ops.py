@@ -151,6 +151,17 @@ def _spmm_inputs(X, rowPtr, colIdx, val, target_row, V):
             raise RuntimeError("target_row must have one entry per split row")
 
 
+def _check_output(out, rowPtr, split, n_out_rows, V, dim):
+    # The kernels index rowPtr and the output by n_out_rows without looking at their sizes.
+    # (the output may be a column slice of a wider array: only its row stride is passed on)
+    if not out.is_cuda or out.dtype != torch.float32 or out.dim() != 2 or out.stride(1) != 1:
+        raise RuntimeError("output must be a 2-D float32 CUDA tensor with unit column stride")
+    if out.shape[1] != dim or out.shape[0] < n_out_rows * V:
+        raise RuntimeError("output must hold %d rows of %d columns" % (n_out_rows * V, dim))
+    if not split and rowPtr.shape[0] - 1 != n_out_rows:
+        raise RuntimeError("rowPtr must have one entry per output row plus one")
+
+
 def spmm_into(out, X, rowPtr, colIdx, val, target_row=None, V=1, n_out_rows=None, CF=0, W=0,
               cfg=None):
     """Launch the SpMM into a caller-provided output (also used by the multi-GPU row shards).
@@ -165,6 +176,7 @@ def spmm_into(out, X, rowPtr, colIdx, val, target_row=None, V=1, n_out_rows=None
         if split:
             raise RuntimeError("n_out_rows is required for split layouts")
         n_out_rows = n_seg
+    _check_output(out, rowPtr, split, n_out_rows, V, dim)
     nent = colIdx.shape[0]
     if cfg is None:
         cfg = _cfg("spmm", CF, W, dim, nent, n_seg, V, split)
@@ -235,15 +247,20 @@ def vec_split_spmm(X, rowPtr_bcsr_split, colIdx, val, target_row, CF, blkWarpNum
 
 
 def spmm_time_ms(X, rowPtr, colIdx, val, target_row=None, V=1, CF=0, W=0, cfg=None,
-                 warmup=PROFILE_WARMUP, iters=PROFILE_ITERS, out=None):
-    """Mean milliseconds per launch over `iters` back-to-back launches (CUDA events)."""
+                 warmup=PROFILE_WARMUP, iters=PROFILE_ITERS, out=None, n_out_rows=None):
+    """Mean milliseconds per launch over `iters` back-to-back launches (CUDA events).
+
+    ``n_out_rows`` counts (block-)rows of the output; it defaults to the square case
+    ceil(input rows / V) that the reference's profile functions assume.
+    """
     _spmm_inputs(X, rowPtr, colIdx, val, target_row, V)
     n, dim = X.shape
     n_seg = rowPtr.shape[0] - 1
     split = target_row is not None
-    n_out = (n + V - 1) // V
+    n_out = (n + V - 1) // V if n_out_rows is None else n_out_rows
     if out is None:
         out = torch.empty((n_out * V, dim), dtype=torch.float32, device=X.device)
+    _check_output(out, rowPtr, split, n_out, V, dim)
     nent = colIdx.shape[0]
     if cfg is None:
         cfg = _cfg("spmm", CF, W, dim, nent, n_seg, V, split)

@@ -153,7 +153,7 @@ def test_spmm_explicit_configs(dev, oracle, mats):
         Bd = B.to(dev)
         for lpr in (2, 4, 8, 16, 32):
             for vw in (1, 2, 4):
-                for thr, rpg, mlp in ((128, 1, 4), (256, 4, 8), (256, 16, 16), (256, 2, 2)):
+                for thr, rpg, mlp in ((128, 1, 4), (256, 4, 8), (256, 16, 16), (256, 2, 2), (64, 4, 4), (32, 2, 8)):
                     cfg = _lib.make_cfg(lanes_per_row=lpr, vec_width=vw, cta_threads=thr, rows_per_group=rpg,
                                         gather_batch=mlp)
                     out = torch.full((m.n_rows, dim), float("nan"), device=dev)
@@ -188,6 +188,29 @@ def test_spmm_strided_operands_and_row_shards(dev, oracle, mats):
     out = torch.empty(hi - lo, 64, device=dev)
     ops.spmm_into(out, B.to(dev), rp_s.to(dev), d.colIdx[a:b].contiguous(), d.val[a:b].contiguous())
     close(out, want)
+
+
+def test_spmm_rejects_inconsistent_sizes(dev, mats):
+    """A row pointer or an output that does not match the row count raises before any launch
+    (the kernels index both by the row count alone)."""
+    from paramspmm_ae_b200 import ops
+    d = mats["powerlaw"].to(dev)
+    n = d.n_rows
+    B = dense(d.n_cols, 32, 5).to(dev)
+    short_rp = d.rowPtr[: n // 2 + 1].contiguous()
+    with pytest.raises(RuntimeError):  # plain CSR: n rows asked for, n/2 + 1 row pointers given
+        ops.spmm_time_ms(B, short_rp, d.colIdx, d.val, warmup=1, iters=1)
+    with pytest.raises(RuntimeError):
+        ops.spmm_into(torch.empty(n, 32, device=dev), B, short_rp, d.colIdx, d.val, n_out_rows=n)
+    with pytest.raises(RuntimeError):  # output with too few rows
+        ops.spmm_into(torch.empty(n - 1, 32, device=dev), B, d.rowPtr, d.colIdx, d.val)
+    with pytest.raises(RuntimeError):  # output of another width
+        ops.spmm_into(torch.empty(n, 16, device=dev), B, d.rowPtr, d.colIdx, d.val)
+    rps, tr = ops.split_csr(mats["powerlaw"].rowPtr, 32)
+    with pytest.raises(RuntimeError):
+        ops.spmm_time_ms(B, rps.to(dev), d.colIdx, d.val, tr.to(dev), out=torch.empty(n // 2, 32, device=dev),
+                         warmup=1, iters=1)
+    torch.cuda.synchronize()
 
 
 def test_spmm_empty_inputs(dev):

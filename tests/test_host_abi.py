@@ -211,7 +211,7 @@ def test_table_plans_become_valid_kernel_configurations():
             dim = int(dim_key)
             rc = lib.pspmm_resolve_cfg(ctypes.byref(cfg), dim, dim, dim, 1, ctypes.c_void_p(256), ctypes.c_void_p(256))
             assert rc == _lib.PSPMM_OK, (regime, dim_key, e)
-            assert cfg.lanes_per_row in (2, 4, 8, 16, 32) and cfg.cta_threads in (128, 256)
+            assert cfg.lanes_per_row in (2, 4, 8, 16, 32) and cfg.cta_threads in (32, 64, 128, 256)
             seen += 1
     assert seen >= 64
 
