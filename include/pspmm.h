@@ -42,6 +42,9 @@ extern "C" {
 #define PSPMM_E_CUDA (-3)     /* a CUDA runtime call or kernel launch failed */
 #define PSPMM_E_UNSUPPORTED (-4)
 #define PSPMM_E_RANGE (-5)    /* a size exceeds what int32 indices can address */
+#define PSPMM_E_IO (-6)       /* a file cannot be opened, mapped, written or renamed */
+#define PSPMM_E_FORMAT (-7)   /* a file's contents contradict its header (or its checksum) */
+#define PSPMM_E_NOMEM (-8)    /* host memory for temporary arrays could not be obtained */
 
 /*
  * Kernel parameters.  Zero in any field means "let the library choose".  These replace the
@@ -214,6 +217,55 @@ PSPMM_API int pspmm_bcsr_count(const int32_t *rowPtr, const int32_t *colIdx, int
 PSPMM_API int pspmm_bcsr_fill(const int32_t *rowPtr, const int32_t *colIdx, const float *val, int64_t n_rows,
                     int64_t n_cols, int32_t V, const int32_t *rowPtr_b, int32_t *colIdx_b,
                     float *val_b);
+
+/*
+ * MatrixMarket coordinate file -> canonical CSR on the host (columns ascending inside a row,
+ * entries with equal coordinates summed in double precision), parsed in parallel from a memory
+ * mapping.  Stands in for scipy's mmread followed by tocsr() in the reference's loader
+ * (graph_input.py:226-232) and yields the same arrays: symmetric and skew-symmetric files are
+ * expanded by mirroring their off-diagonal entries, indices become 0-based.  force_ones != 0
+ * replaces every stored value by 1 before the summation, as the reference does
+ * (`mtx.data = np.ones_like(mtx.data)`, graph_input.py:227).  pattern / real / integer fields
+ * are read; complex or hermitian files and the dense "array" format give PSPMM_E_UNSUPPORTED.
+ *
+ * pspmm_mtx_info_read parses only the banner and the size line; nnz_max (2 x stored entries for a
+ * symmetric file) bounds the CSR entry count, so the caller can size colIdx / val before
+ * pspmm_mtx_read_csr, which fills rowPtr[n_rows + 1], colIdx and val (at most `capacity` entries)
+ * and returns the entry count through *nnz.  If `capacity` is too small the call returns
+ * PSPMM_E_ARG with *nnz set to the count that is needed and colIdx / val untouched.
+ */
+typedef struct pspmm_mtx_info {
+    int64_t n_rows, n_cols;
+    int64_t stored;    /* coordinate lines in the file */
+    int64_t nnz_max;   /* upper bound of the CSR entry count after expansion */
+    int32_t symmetric; /* 0 general, 1 symmetric, 2 skew-symmetric */
+    int32_t field;     /* 0 pattern, 1 real, 2 integer */
+} pspmm_mtx_info;
+PSPMM_API int pspmm_mtx_info_read(const char *path, pspmm_mtx_info *info);
+PSPMM_API int pspmm_mtx_read_csr(const char *path, int32_t force_ones, int32_t *rowPtr, int32_t *colIdx,
+                                 float *val, int64_t capacity, int64_t *nnz);
+
+/*
+ * Binary CSR container, so that a matrix is parsed once and re-loaded at memory-copy speed (the
+ * reference re-parses the text file on every run).  Little endian: a 64-byte header (magic
+ * "PSPMMCSR", version, n_rows, n_cols, nnz, size and modification time in ns of the text file the
+ * arrays came from, checksum of the arrays), then rowPtr, colIdx, val, each section starting on a
+ * 64-byte boundary.  pspmm_csr_file_write writes to a temporary name beside `path` and renames;
+ * pspmm_csr_file_info reads the header (a caller compares source_size / source_mtime_ns with the
+ * text file to detect a stale container); pspmm_csr_file_read copies the arrays into host arrays
+ * sized from the header and, with verify != 0, recomputes the checksum (PSPMM_E_FORMAT if it
+ * differs, if the header is not a container's, or if the file length disagrees with the header).
+ */
+typedef struct pspmm_csr_file_info_t {
+    int64_t n_rows, n_cols, nnz;
+    int64_t source_size, source_mtime_ns;
+} pspmm_csr_file_info_t;
+PSPMM_API int pspmm_csr_file_write(const char *path, int64_t n_rows, int64_t n_cols, int64_t nnz,
+                                   const int32_t *rowPtr, const int32_t *colIdx, const float *val,
+                                   int64_t source_size, int64_t source_mtime_ns);
+PSPMM_API int pspmm_csr_file_info(const char *path, pspmm_csr_file_info_t *info);
+PSPMM_API int pspmm_csr_file_read(const char *path, int32_t *rowPtr, int32_t *colIdx, float *val,
+                                  int64_t n_rows, int64_t nnz, int32_t verify);
 
 /*
  * Timing loops.  Stand in for the *_spmm_profile / *_sddmm_profile functions

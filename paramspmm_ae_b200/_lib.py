@@ -18,6 +18,9 @@ PSPMM_E_CONFIG = -2
 PSPMM_E_CUDA = -3
 PSPMM_E_UNSUPPORTED = -4
 PSPMM_E_RANGE = -5
+PSPMM_E_IO = -6
+PSPMM_E_FORMAT = -7
+PSPMM_E_NOMEM = -8
 
 _i32 = ctypes.c_int32
 _i64 = ctypes.c_int64
@@ -30,6 +33,20 @@ class PspmmCfg(ctypes.Structure):
     _fields_ = [("lanes_per_row", _i32), ("vec_width", _i32), ("cta_threads", _i32),
                 ("rows_per_group", _i32), ("gather_batch", _i32), ("col_tile", _i32), ("hint_CF", _i32),
                 ("hint_blkWarpNum", _i32)]
+
+
+class MtxInfo(ctypes.Structure):
+    """Mirror of ``pspmm_mtx_info``."""
+
+    _fields_ = [("n_rows", _i64), ("n_cols", _i64), ("stored", _i64), ("nnz_max", _i64),
+                ("symmetric", _i32), ("field", _i32)]
+
+
+class CsrFileInfo(ctypes.Structure):
+    """Mirror of ``pspmm_csr_file_info_t``."""
+
+    _fields_ = [("n_rows", _i64), ("n_cols", _i64), ("nnz", _i64), ("source_size", _i64),
+                ("source_mtime_ns", _i64)]
 
 
 class PspmmError(RuntimeError):
@@ -63,6 +80,11 @@ _SIGNATURES = {
                              _i32, _i32, _i32, _vp, _vp, _i64, _vp, ctypes.c_size_t, _vp],
     "pspmm_bcsr_count": [_vp, _vp, _i64, _i64, _i32, _vp, ctypes.POINTER(_i64)],
     "pspmm_bcsr_fill": [_vp, _vp, _vp, _i64, _i64, _i32, _vp, _vp, _vp],
+    "pspmm_mtx_info_read": [ctypes.c_char_p, ctypes.POINTER(MtxInfo)],
+    "pspmm_mtx_read_csr": [ctypes.c_char_p, _i32, _vp, _vp, _vp, _i64, ctypes.POINTER(_i64)],
+    "pspmm_csr_file_write": [ctypes.c_char_p, _i64, _i64, _i64, _vp, _vp, _vp, _i64, _i64],
+    "pspmm_csr_file_info": [ctypes.c_char_p, ctypes.POINTER(CsrFileInfo)],
+    "pspmm_csr_file_read": [ctypes.c_char_p, _vp, _vp, _vp, _i64, _i64, _i32],
     "pspmm_profile_spmm": [_vp, _vp, _vp, _i32, _vp, _vp, _i64, _i64, _i64, _i32, _i64, _i64, _cfgp,
                            _vp, _vp, _i64, _i32, _i32, ctypes.POINTER(ctypes.c_float), _vp],
     "pspmm_profile_sddmm": [_vp, _vp, _vp, _i32, _vp, _vp, _vp, _i64, _i64, _i32, _i64, _i64, _cfgp,

@@ -26,7 +26,7 @@ NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC,-fopenmp,-f
               "-cudart", "shared", "-I", os.path.join(ROOT, "include"), "-I", CSRC]
 
 CORE_SOURCES = ["pspmm_api.cu", "spmm_vw4.cu", "spmm_vw2.cu", "spmm_vw1.cu", "sddmm_vw4.cu",
-                "sddmm_vw2.cu", "sddmm_vw1.cu", "host_builders.cpp", "device_builders.cu", "agnn_fused.cu"]
+                "sddmm_vw2.cu", "sddmm_vw1.cu", "host_builders.cpp", "mtx_io.cpp", "device_builders.cu", "agnn_fused.cu"]
 BASELINE_SOURCES = ["baselines.cu"]
 PROBE = os.path.join(PKG, "gather_probe")  # stand-alone microbenchmark, see csrc/gather_probe.cu
 

@@ -29,6 +29,9 @@ extern "C" const char *pspmm_strerror(int code)
     case PSPMM_E_CUDA: return "CUDA error (see pspmm_last_cuda_error)";
     case PSPMM_E_UNSUPPORTED: return "unsupported combination";
     case PSPMM_E_RANGE: return "size exceeds the int32 index range";
+    case PSPMM_E_IO: return "file cannot be opened, mapped, written or renamed";
+    case PSPMM_E_FORMAT: return "file contents contradict the header or the checksum";
+    case PSPMM_E_NOMEM: return "out of host memory";
     default: return "unknown error code";
     }
 }

@@ -12,12 +12,17 @@ work is done by libpspmm's native builders:
   scipy's single-threaded ``tobsr`` (graph_input.py:245-266); the arrays are bit-identical;
 * ``mask`` is ``pspmm_genmask`` on the device (graph_input.py:277-286).
 
+* a MatrixMarket file is parsed by ``pspmm_mtx_read_csr`` (parallel, memory-mapped) instead of
+  scipy's ``mmread`` + ``tocsr`` (graph_input.py:226-232) and can be kept as a binary CSR container
+  (``cache_dir``) so that later runs skip the parse.
+
 A matrix can come from a MatrixMarket file (``load``, as in the reference) or from CSR arrays
 already in memory (``load_csr``).
 """
 from __future__ import annotations
 
 import math
+import os
 
 import numpy as np
 import torch
@@ -100,8 +105,12 @@ class csr_data(object):
 class graph_input(object):
     """One matrix in every representation the kernels accept (graph_input.py:180-430)."""
 
-    def __init__(self, mtx_name=None, path=None):
+    def __init__(self, mtx_name=None, path=None, cache_dir=None):
+        """``cache_dir`` (default: the environment variable PSPMM_CACHE_DIR, else none): where the
+        parsed CSR arrays of a MatrixMarket file are kept as a binary container, so that later
+        loads skip the text parse."""
         self.path, self.mtx_name = path, mtx_name
+        self.cache_dir = cache_dir if cache_dir is not None else os.environ.get("PSPMM_CACHE_DIR")
         self.loaded_flag = self.reordered_flag = False
         self.csr_split_flag = self.bcsr_split_flag = self.bcsr_flag = False
         self.mtx_nodes = self.mtx_edges = self.density = None
@@ -116,17 +125,21 @@ class graph_input(object):
             raise ValueError("Graph path must be assigned first")
         if not load_from_mtx:
             raise ValueError("only MatrixMarket input is supported; use load_csr for in-memory arrays")
-        from scipy.io import mmread
+        # The library's parallel reader (or its binary container) replaces scipy's mmread + tocsr
+        # (graph_input.py:226-232 of the reference); stored values become 1 as there (:227).
+        rowPtr, colIdx, val, n_rows, n_cols = ops.load_matrix(self.path + self.mtx_name + ".mtx",
+                                                              self.cache_dir, force_ones=True)
+        if is_normalize or GIN_epsilon is not None:
+            from scipy.sparse import csr_matrix
 
-        mtx = mmread(self.path + self.mtx_name + ".mtx")
-        mtx.data = np.ones_like(mtx.data)
-        if is_normalize:
-            mtx = self.normalize_adj(mtx)
-        elif GIN_epsilon is not None:
-            mtx = self.normalize_adj_GIN(mtx, GIN_epsilon)
-        csr = mtx.tocsr()
-        return self.load_csr(csr.indptr, csr.indices, csr.data, csr.shape[0], manual_granularity,
-                             is_avg_granularity, blk_size, if_mask)
+            mtx = csr_matrix((val.numpy().astype(np.float64), colIdx.numpy(), rowPtr.numpy()),
+                             shape=(n_rows, n_cols))
+            mtx = self.normalize_adj(mtx) if is_normalize else self.normalize_adj_GIN(mtx, GIN_epsilon)
+            csr = mtx.tocsr()
+            csr.sort_indices()
+            rowPtr, colIdx, val = csr.indptr, csr.indices, csr.data
+        return self.load_csr(rowPtr, colIdx, val, n_rows, manual_granularity, is_avg_granularity,
+                             blk_size, if_mask)
 
     def load_csr(self, rowPtr, colIdx, val, n_nodes=None, manual_granularity=None,
                  is_avg_granularity=False, blk_size=2, if_mask=False):

@@ -12,11 +12,12 @@ an error, never a reason to fall back to a torch implementation.
 from __future__ import annotations
 
 import ctypes
+import os
 
 import torch
 
 from . import _lib
-from ._lib import check, lib, make_cfg
+from ._lib import PspmmError, check, lib, make_cfg
 
 PROFILE_ITERS = 200   # SpMM/SpMM.h:12 (PROFILE)
 PROFILE_WARMUP = 20
@@ -84,6 +85,92 @@ def split_csr(rowPtr, granularity):
     tr = torch.empty(nseg.value, dtype=torch.int32)
     check(lib().pspmm_split_csr(_ptr(rowPtr), n, int(granularity), _ptr(rps), _ptr(tr), nseg.value))
     return [rps, tr]
+
+
+def mtx_info(path):
+    """Banner and size line of a MatrixMarket file -> dict (n_rows, n_cols, stored, nnz_max,
+    symmetric, field)."""
+    from ._lib import MtxInfo
+    info = MtxInfo()
+    check(lib().pspmm_mtx_info_read(os.fsencode(path), ctypes.byref(info)))
+    return {k: int(getattr(info, k)) for k, _ in MtxInfo._fields_}
+
+
+def mtx_read_csr(path, force_ones=True):
+    """MatrixMarket coordinate file -> (rowPtr, colIdx, val, n_rows, n_cols) as CPU tensors in
+    canonical CSR: what ``scipy.io.mmread(path).tocsr()`` gives in the reference's loader
+    (graph_input.py:226-232), with every stored value replaced by 1 first when ``force_ones``
+    (graph_input.py:227).  Parsed by the library's parallel reader."""
+    info = mtx_info(path)
+    rowPtr = torch.empty(info["n_rows"] + 1, dtype=torch.int32)
+    colIdx = torch.empty(info["nnz_max"], dtype=torch.int32)
+    val = torch.empty(info["nnz_max"], dtype=torch.float32)
+    nnz = ctypes.c_int64(0)
+    check(lib().pspmm_mtx_read_csr(os.fsencode(path), 1 if force_ones else 0, _ptr(rowPtr), _ptr(colIdx),
+                                   _ptr(val), info["nnz_max"], ctypes.byref(nnz)))
+    k = nnz.value
+    if k != info["nnz_max"]:  # duplicates or a diagonal in a symmetric file: give the surplus back
+        colIdx, val = colIdx[:k].clone(), val[:k].clone()
+    return rowPtr, colIdx, val, info["n_rows"], info["n_cols"]
+
+
+def csr_file_write(path, rowPtr, colIdx, val, n_cols, source=None):
+    """Write CSR arrays (CPU tensors) as a binary container; ``source`` = the text file they were
+    parsed from, whose size and modification time are recorded for staleness checks."""
+    _check_cpu(rowPtr, "rowPtr")
+    _check_cpu(colIdx, "colIdx")
+    if val.dtype != torch.float32 or val.is_cuda or not val.is_contiguous() or val.shape != colIdx.shape:
+        raise RuntimeError("values must be a contiguous CPU float32 tensor with one entry per column index")
+    size = mtime = 0
+    if source is not None:
+        st = os.stat(source)
+        size, mtime = st.st_size, st.st_mtime_ns
+    check(lib().pspmm_csr_file_write(os.fsencode(path), rowPtr.shape[0] - 1, int(n_cols), colIdx.shape[0],
+                                     _ptr(rowPtr), _ptr(colIdx), _ptr(val), size, mtime))
+
+
+def csr_file_info(path):
+    from ._lib import CsrFileInfo
+    info = CsrFileInfo()
+    check(lib().pspmm_csr_file_info(os.fsencode(path), ctypes.byref(info)))
+    return {k: int(getattr(info, k)) for k, _ in CsrFileInfo._fields_}
+
+
+def csr_file_read(path, verify=True, info=None):
+    """Binary container -> (rowPtr, colIdx, val, n_rows, n_cols) as CPU tensors."""
+    info = info or csr_file_info(path)
+    rowPtr = torch.empty(info["n_rows"] + 1, dtype=torch.int32)
+    colIdx = torch.empty(info["nnz"], dtype=torch.int32)
+    val = torch.empty(info["nnz"], dtype=torch.float32)
+    check(lib().pspmm_csr_file_read(os.fsencode(path), _ptr(rowPtr), _ptr(colIdx), _ptr(val), info["n_rows"],
+                                    info["nnz"], 1 if verify else 0))
+    return rowPtr, colIdx, val, info["n_rows"], info["n_cols"]
+
+
+def load_matrix(mtx_path, cache_dir=None, force_ones=True, verify=True):
+    """CSR arrays of a MatrixMarket file, through a binary container in ``cache_dir`` when one is
+    given: a container whose recorded size and modification time match the text file is read
+    instead of parsing; otherwise the file is parsed and the container (re)written.  A cache
+    directory that cannot be written to is not an error, the arrays are still returned."""
+    if cache_dir is None:
+        return mtx_read_csr(mtx_path, force_ones)
+    st = os.stat(mtx_path)
+    tag = "ones" if force_ones else "vals"
+    cached = os.path.join(cache_dir, "%s.%s.pspmmcsr" % (os.path.basename(mtx_path), tag))
+    if os.path.exists(cached):
+        try:
+            info = csr_file_info(cached)
+            if info["source_size"] == st.st_size and info["source_mtime_ns"] == st.st_mtime_ns:
+                return csr_file_read(cached, verify, info)
+        except PspmmError:
+            pass  # unreadable or damaged container: parse again and replace it
+    out = mtx_read_csr(mtx_path, force_ones)
+    try:
+        os.makedirs(cache_dir, exist_ok=True)
+        csr_file_write(cached, out[0], out[1], out[2], out[4], source=mtx_path)
+    except (OSError, PspmmError):
+        pass
+    return out
 
 
 def split_csr_par(rowPtr, row_split_offset, granularity):
