@@ -62,6 +62,10 @@ typedef struct pspmm_cfg {
                                 several launches over column ranges.  0 = one launch */
     int32_t hint_CF;         /* legacy coarsening factor, validated only */
     int32_t hint_blkWarpNum; /* legacy warps per block, validated only */
+    int32_t accumulate;      /* SpMM only: 0 = C is overwritten (every row is written, empty rows with zeros);
+                                1 = the product is added to what C holds (reduction instructions; the order in
+                                which contributions reach a row is not fixed).  Lets a caller sum products over
+                                column blocks of A, e.g. as blocks of B arrive from other GPUs */
 } pspmm_cfg;
 
 PSPMM_API int pspmm_version(void);

@@ -57,6 +57,8 @@ int pspmm_validate_cfg(const pspmm_cfg *cfg, bool sddmm)
         return PSPMM_E_CONFIG;
     if (cfg->rows_per_group < 0 || cfg->rows_per_group > PSPMM_RPG_MAX)
         return PSPMM_E_CONFIG;
+    if (cfg->accumulate != 0 && (cfg->accumulate != 1 || sddmm))
+        return PSPMM_E_CONFIG;
     if (cfg->gather_batch != 0 && cfg->gather_batch != 2 && cfg->gather_batch != 4 &&
         cfg->gather_batch != 8 && cfg->gather_batch != 16)
         return PSPMM_E_CONFIG;
@@ -284,6 +286,9 @@ static int spmm_launch(const int32_t *segPtr, const int32_t *target_row, int64_t
         return rc;
     if (n_out_blk_rows == 0)
         return PSPMM_OK;
+    const bool accumulate = cfg && cfg->accumulate;
+    if (n_seg == 0 && accumulate)
+        return PSPMM_OK;  // nothing stored: nothing to add
     if (n_seg == 0) {  // nothing stored: the product is zero
         PSPMM_CUDA_TRY(cudaMemset2DAsync(C, (size_t)ldC * 4, 0, (size_t)dim * 4,
                                          (size_t)(n_out_blk_rows * V), st));
@@ -307,8 +312,20 @@ static int spmm_launch(const int32_t *segPtr, const int32_t *target_row, int64_t
     }
     LaunchShape s;
     pspmm_resolve_shape(cfg, dim, pspmm_vw_max(dim, ldB, ldC, B, C), V, &s);
+    if (accumulate) {
+        // built for 128-bit loads on CSR / split CSR with at least four lanes per row
+        if (s.vw != 4 || V != 1)
+            return PSPMM_E_UNSUPPORTED;
+        if (s.lpr < 4) {
+            LaunchShape t = s;
+            pspmm_cfg wide = *cfg;
+            wide.lanes_per_row = 4;
+            pspmm_resolve_shape(&wide, dim, 4, V, &t);
+            s = t;
+        }
+    }
 
-    if (target_row) {
+    if (target_row && !accumulate) {
         const int vecok = (dim % 4 == 0 && ldC % 4 == 0 && ((uintptr_t)C) % 16 == 0) ? 1 : 0;
         zero_shared_rows_kernel<<<(unsigned)((n_seg + 255) / 256), 256, 0, st>>>(
             target_row, n_seg, n_out_blk_rows, s.rpg, V, C, ldC, dim, vecok);
@@ -334,7 +351,9 @@ static int spmm_launch(const int32_t *segPtr, const int32_t *target_row, int64_t
         return PSPMM_E_RANGE;
     dim3 grid((unsigned)gx, (unsigned)s.tiles, 1);
     bool ok = false;
-    if (s.vw == 4)
+    if (accumulate)
+        ok = pspmm_launch_spmm_vw4_acc(s, a, grid, st);
+    else if (s.vw == 4)
         ok = pspmm_launch_spmm_vw4(s, V, a, grid, st);
     else if (s.vw == 2)
         ok = pspmm_launch_spmm_vw2(s, V, a, grid, st);

@@ -61,6 +61,7 @@ struct LaunchShape {
 // Per-translation-unit dispatchers (one per vector width so the files compile in parallel).
 // Return false when (lpr, cf, V) is not instantiated for that width.
 bool pspmm_launch_spmm_vw4(const LaunchShape &s, int V, const SpmmArgs &a, dim3 grid, cudaStream_t st);
+bool pspmm_launch_spmm_vw4_acc(const LaunchShape &s, const SpmmArgs &a, dim3 grid, cudaStream_t st);
 bool pspmm_launch_spmm_vw2(const LaunchShape &s, int V, const SpmmArgs &a, dim3 grid, cudaStream_t st);
 bool pspmm_launch_spmm_vw1(const LaunchShape &s, int V, const SpmmArgs &a, dim3 grid, cudaStream_t st);
 bool pspmm_launch_sddmm_vw4(const LaunchShape &s, int V, const SddmmArgs &a, dim3 grid, cudaStream_t st);

@@ -95,7 +95,9 @@ struct SpmmOcc {
     static constexpr int MIN_CTAS = MLP >= 16 ? 2 : (MLP >= 8 ? 3 : (MLP >= 4 ? 5 : 8));
 };
 
-template <int LPR, int VW, int CF, int V, int MLP>
+// ACC = true adds the product to C instead of overwriting it: every contribution is a RED, rows
+// without entries add nothing, and nothing is zeroed (no pre-pass either).
+template <int LPR, int VW, int CF, int V, int MLP, bool ACC = false>
 __global__ void __launch_bounds__(256, SpmmOcc<MLP>::MIN_CTAS) spmm_seg_kernel(const SpmmArgs a)
 {
     using Tile = SpmmTile<LPR, V>;
@@ -226,13 +228,15 @@ __global__ void __launch_bounds__(256, SpmmOcc<MLP>::MIN_CTAS) spmm_seg_kernel(c
                 shared = (run_start == 0 && st[0] == me) || (next == me);
                 run_start = row + 1;
             }
+            // (pieces of a split layout are never empty)
+            const bool emit = !ACC || split || re > rb;
 #pragma unroll
             for (int w = 0; w < V; ++w) {
                 float *crow = a.C + (orow * V + w) * a.ldC;
 #pragma unroll
                 for (int cf = 0; cf < CF; ++cf) {
-                    if (act[cf]) {
-                        if (shared)
+                    if (act[cf] && emit) {
+                        if (ACC || shared)
                             red_add_vec<VW>(crow + voff[cf], acc[w][cf]);
                         else
                             st_vec_hint<VW>(crow + voff[cf], acc[w][cf], stream);
@@ -242,7 +246,7 @@ __global__ void __launch_bounds__(256, SpmmOcc<MLP>::MIN_CTAS) spmm_seg_kernel(c
                         acc[w][cf][i] = 0.f;
                 }
             }
-            if (split) {
+            if (!ACC && split) {
                 // Rows strictly between this segment's row and the next segment's row (and, for
                 // the very first segment, the rows before it) have no entries: zero short runs
                 // here; runs longer than PSPMM_GAP_MAX are left to the pre-pass.
@@ -272,11 +276,11 @@ __global__ void __launch_bounds__(256, SpmmOcc<MLP>::MIN_CTAS) spmm_seg_kernel(c
     }
 }
 
-template <int LPR, int VW, int CF, int V, int MLP>
+template <int LPR, int VW, int CF, int V, int MLP, bool ACC = false>
 static inline void spmm_launch_one(const SpmmArgs &a, dim3 grid, int threads, cudaStream_t st)
 {
     const int smem = (threads / LPR) * SpmmTile<LPR, V>::GROUP_WORDS * 4;
-    auto kern = spmm_seg_kernel<LPR, VW, CF, V, MLP>;
+    auto kern = spmm_seg_kernel<LPR, VW, CF, V, MLP, ACC>;
     if (smem > 48 * 1024)
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     kern<<<grid, threads, smem, st>>>(a);
@@ -299,5 +303,11 @@ static inline void spmm_launch_one(const SpmmArgs &a, dim3 grid, int threads, cu
             spmm_launch_one<LPR_, VW_, CF_, V_, 16>(a, grid, s.threads, st); \
         else                                                                 \
             spmm_launch_one<LPR_, VW_, CF_, V_, 8>(a, grid, s.threads, st);  \
+        return true;                                                         \
+    }
+// The accumulating form is built for the 128-bit CSR family at one gather-batch depth.
+#define PSPMM_SPMM_CASE_ACC(LPR_, CF_)                                       \
+    if (s.lpr == LPR_ && s.cf == CF_) {                                      \
+        spmm_launch_one<LPR_, 4, CF_, 1, 8, true>(a, grid, s.threads, st);   \
         return true;                                                         \
     }

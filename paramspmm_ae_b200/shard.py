@@ -20,6 +20,15 @@ all-to-all with uneven splits moves them.  On power-law graphs a shard touches a
 columns, so the bytes on NVLink shrink by that fraction, and the SpMM gathers from a smaller
 operand.
 
+``exchange="pipelined"`` hides the SpMM under the exchange.  Every rank's block of the dense
+operand is cut into ``row_chunks`` runs of rows; chunk k of all ranks is gathered by one
+all-gather into its own region of the receive buffer, and the local shard of A is cut, at set-up,
+into the matching column blocks (block k holds the entries whose column lies in chunk k of its
+owner).  C is then the sum over k of A_k B_k: the product of block k starts as soon as chunk k has
+arrived, while chunk k+1 is still on the wire; the first product overwrites C, the others add to
+it (``pspmm_cfg.accumulate``).  Unlike slicing the dense columns, this reads every entry of A
+once and keeps full-width row gathers.
+
 ``dim_chunks > 1`` splits the dense columns into slices and gathers slice s+1 on a side
 stream while the SpMM of slice s runs (the kernels take explicit leading dimensions, so a
 slice of C is written in place).
@@ -69,11 +78,14 @@ class ShardedSpMM:
     """
 
     def __init__(self, rowPtr, colIdx, val, n_cols, rank, world, row_bounds=None, col_bounds=None,
-                 device="cuda", group=None, local_spmm=None, dim_chunks=1, exchange="allgather"):
-        if exchange not in ("allgather", "needed"):
-            raise ValueError("exchange must be 'allgather' or 'needed'")
+                 device="cuda", group=None, local_spmm=None, dim_chunks=1, exchange="allgather",
+                 row_chunks=4):
+        if exchange not in ("allgather", "needed", "pipelined"):
+            raise ValueError("exchange must be 'allgather', 'needed' or 'pipelined'")
+        if row_chunks < 1:
+            raise ValueError("row_chunks must be at least 1")
         self.rank, self.world, self.group, self.dim_chunks = rank, world, group, dim_chunks
-        self.exchange = exchange
+        self.exchange, self.row_chunks = exchange, row_chunks
         self.row_bounds = partition_rows_by_nnz(rowPtr, world) if row_bounds is None else torch.as_tensor(row_bounds).long()
         self.col_bounds = partition_rows_even(n_cols, world) if col_bounds is None else torch.as_tensor(col_bounds).long()
         if int(self.col_bounds[-1]) != n_cols or int(self.row_bounds[-1]) != len(rowPtr) - 1:
@@ -88,10 +100,92 @@ class ShardedSpMM:
         self.my_cols = (int(self.col_bounds[rank]), int(self.col_bounds[rank + 1]))
         if exchange == "needed":
             self._plan_needed_rows(ci.to(device))
+        elif exchange == "pipelined":
+            self._plan_row_chunks(ci.to(device))
         else:
             self.colIdx = remap_columns(ci.to(device), self.col_bounds, self.max_rows)
-        self.local_spmm = local_spmm if local_spmm is not None else self._planned_spmm()
-        self._side = torch.cuda.Stream() if (self.device.type == "cuda" and dim_chunks > 1) else None
+        if exchange == "pipelined":
+            self.block_spmm = [local_spmm if local_spmm is not None else self._planned_spmm(rp_k)
+                               for rp_k, _, _ in self.blocks]
+        else:
+            self.local_spmm = local_spmm if local_spmm is not None else self._planned_spmm()
+        overlap = dim_chunks > 1 or exchange == "pipelined"
+        self._side = torch.cuda.Stream() if (self.device.type == "cuda" and overlap) else None
+
+    def _plan_row_chunks(self, cols_global):
+        """Set-up of the pipelined exchange: the receive buffer is [row_chunks][world][chunk_rows]
+        rows; column c, row i of owner q's block, lives at ((i // chunk_rows) * world + q) *
+        chunk_rows + i % chunk_rows.  The shard of A is regrouped into one CSR matrix per chunk
+        (entries keep their row order), all of them indexing that one buffer."""
+        dev = cols_global.device
+        K, W, n_loc = self.row_chunks, self.world, self.hi - self.lo
+        cr = max(1, -(-self.max_rows // K))
+        self.chunk_rows = cr
+        cb = self.col_bounds.to(dev)
+        c = cols_global.long()
+        owner = torch.searchsorted(cb, c, right=True) - 1
+        local = c - cb[owner]
+        k = torch.div(local, cr, rounding_mode="floor")
+        pos = ((k * W + owner) * cr + (local - k * cr)).to(torch.int32)
+        rows = torch.repeat_interleave(torch.arange(n_loc, device=dev),
+                                       (self.rowPtr[1:] - self.rowPtr[:-1]).long())
+        key = k * n_loc + rows
+        del c, owner, local, k
+        order = torch.argsort(key, stable=True)
+        counts = torch.bincount(key, minlength=K * n_loc).view(K, n_loc)
+        del key, rows
+        pos, val = pos[order], self.val[order]
+        del order
+        sizes = [int(x) for x in counts.sum(1).cpu()]
+        self.blocks, a = [], 0
+        for kk in range(K):
+            rp = torch.zeros(n_loc + 1, dtype=torch.int32, device=dev)
+            rp[1:] = counts[kk].cumsum(0)
+            self.blocks.append((rp, pos[a: a + sizes[kk]].contiguous(), val[a: a + sizes[kk]].contiguous()))
+            a += sizes[kk]
+        self.val = self.colIdx = None  # held per block from here on
+
+    def _forward_pipelined(self, B_shard, out):
+        import torch.distributed as dist
+
+        K, W, cr = self.row_chunks, self.world, self.chunk_rows
+        rows, dim = B_shard.shape
+        full = torch.empty(K * W * cr, dim, dtype=B_shard.dtype, device=B_shard.device)
+        cuda = self._side is not None
+        main = torch.cuda.current_stream() if cuda else None
+        events = []
+
+        def gather(kk):
+            lo, hi = min(kk * cr, rows), min((kk + 1) * cr, rows)
+            piece = B_shard[lo:hi]
+            if hi - lo != cr:  # the ragged end of a block (or a block shorter than the longest one)
+                padded = torch.zeros(cr, dim, dtype=B_shard.dtype, device=B_shard.device)
+                padded[: hi - lo] = piece
+                piece = padded
+            dst = full[kk * W * cr: (kk + 1) * W * cr]
+            if W == 1:
+                dst.copy_(piece)
+            else:
+                dist.all_gather_into_tensor(dst, piece, group=self.group)
+
+        if cuda:
+            self._side.wait_stream(main)
+            with torch.cuda.stream(self._side):
+                for kk in range(K):
+                    gather(kk)
+                    ev = torch.cuda.Event()
+                    ev.record(self._side)
+                    events.append(ev)
+            B_shard.record_stream(self._side)
+            full.record_stream(self._side)
+        for kk in range(K):
+            if cuda:
+                main.wait_event(events[kk])
+            else:
+                gather(kk)
+            rp, ci, v = self.blocks[kk]
+            self.block_spmm[kk](out, full, rp, ci, v, accumulate=kk > 0)
+        return out
 
     def _plan_needed_rows(self, cols_global):
         """Set-up of the sparse exchange: which rows this rank needs from every owner, which rows
@@ -132,18 +226,21 @@ class ShardedSpMM:
                                input_split_sizes=self.send_splits, group=self.group)
         return recv
 
-    def _planned_spmm(self):
-        """The CUDA operator with the configuration the decider picks for this shard's row-length
-        statistics and the (slice of the) dense width; a split layout, when chosen, is built once on
-        the device from the shard's row pointer and kept."""
+    def _planned_spmm(self, rowPtr=None):
+        """The CUDA operator with the configuration the decider picks for the row-length statistics
+        of this shard (or of one column block of it) and the (slice of the) dense width; a split
+        layout, when chosen, is built once on the device from the row pointer and kept."""
         from . import _lib, decider, ops
 
-        stats = decider.row_stats(self.rowPtr)
+        stats = decider.row_stats(self.rowPtr if rowPtr is None else rowPtr)
         layouts = {}
 
-        def local_spmm(out, B, rowPtr, colIdx, val):
+        def local_spmm(out, B, rowPtr, colIdx, val, accumulate=False):
             p = decider.choose(stats, B.shape[1])
-            cfg = _lib.make_cfg(**p.kernel_cfg())
+            kw = p.kernel_cfg()
+            if accumulate:  # built for 128-bit loads at one gather-batch depth
+                kw.update(vec_width=0, gather_batch=0, accumulate=1)
+            cfg = _lib.make_cfg(**kw)
             if p["if_split"]:
                 g = int(p["granularity"])
                 if g not in layouts:
@@ -186,6 +283,10 @@ class ShardedSpMM:
         if self.exchange == "needed":
             self.local_spmm(out, self._exchange_needed(B_shard), self.rowPtr, self.colIdx, self.val)
             return out
+        if self.exchange == "pipelined":
+            if dim % 4 != 0:
+                raise ValueError("the pipelined exchange adds into C with 128-bit accesses: dim must be a multiple of 4")
+            return self._forward_pipelined(B_shard, out)
         k = max(1, min(self.dim_chunks, dim // 4)) if self.dim_chunks > 1 else 1
         if k == 1:
             self.local_spmm(out, self._gather(B_shard), self.rowPtr, self.colIdx, self.val)

@@ -12,6 +12,7 @@ device, checks the result against an independent computation, and returns a dict
 """
 from __future__ import annotations
 
+import sys
 import time
 
 import torch
@@ -179,15 +180,17 @@ def gcn_forward_backward(n=2_449_029, pairs=61_900_000, feats=100, hidden=256, c
 
 
 def scaleout_spmm(scale=24, nnz=512_000_000, dim=128, seed=51, iters=5, warmup=2, rank=0, world=1,
-                  device="cuda:0", dim_chunks=4):
+                  device="cuda:0", dim_chunks=4, row_chunks=4):
     """Row-sharded SpMM of one global R-MAT matrix (strong scaling): every rank holds a contiguous,
     nnz-balanced row block of A and the matching row block of the dense operand.
 
-    Three timings per rank (CUDA events on the launching stream, maximum over ranks):
+    Timings per rank (CUDA events on the launching stream, maximum over ranks):
     the local SpMM against a replicated dense operand (no exchange), the all-gather of the dense
     row blocks followed by the SpMM, the exchange of only the rows each shard references (one
-    all-to-all) followed by the SpMM on the compact operand, and the all-gather with the dense
-    columns cut into `dim_chunks` slices so that the gather of slice s+1 overlaps the SpMM of slice s.
+    all-to-all) followed by the SpMM on the compact operand, the all-gather in `row_chunks` row
+    chunks with the product of column block k running while chunk k+1 is on the wire, and the
+    all-gather with the dense columns cut into `dim_chunks` slices so that the gather of slice s+1
+    overlaps the SpMM of slice s.
     Every rank generates the same global matrix from the seed and keeps only its rows.
     """
     import torch.distributed as dist
@@ -202,6 +205,8 @@ def scaleout_spmm(scale=24, nnz=512_000_000, dim=128, seed=51, iters=5, warmup=2
     a, b = int(m.rowPtr[sh.lo]), int(m.rowPtr[sh.hi])
     sh.keep_global_columns(m.colIdx[a:b].clone())
     sh_needed = ShardedSpMM(m.rowPtr, m.colIdx, m.val, n, rank, world, device=dev, exchange="needed")
+    sh_pipe = ShardedSpMM(m.rowPtr, m.colIdx, m.val, n, rank, world, device=dev, exchange="pipelined",
+                          row_chunks=row_chunks)
     nnz_total, nnz_local = m.nnz, b - a
     del m
     torch.cuda.empty_cache()
@@ -211,7 +216,7 @@ def scaleout_spmm(scale=24, nnz=512_000_000, dim=128, seed=51, iters=5, warmup=2
     out_rep = torch.empty(sh.local_rows, dim, device=dev)
     out_ag = torch.empty(sh.local_rows, dim, device=dev)
 
-    def timed(fn):
+    def timed(fn, label):
         for _ in range(warmup):
             fn()
         torch.cuda.synchronize()
@@ -226,21 +231,26 @@ def scaleout_spmm(scale=24, nnz=512_000_000, dim=128, seed=51, iters=5, warmup=2
         t = torch.tensor([e0.elapsed_time(e1) / iters], device=dev, dtype=torch.float64)
         if world > 1:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        if rank == 0:  # progress on stderr: a later step that fails does not take these along
+            print("scaleout_spmm world %d: %s %.4f ms" % (world, label, float(t.item())), file=sys.stderr, flush=True)
         return float(t.item())
 
-    ms_rep = timed(lambda: sh.forward_replicated(B_full, out_rep))
-    ms_ag = timed(lambda: sh.forward(B_shard, out_ag))
+    ms_rep = timed(lambda: sh.forward_replicated(B_full, out_rep), "replicated")
+    ms_ag = timed(lambda: sh.forward(B_shard, out_ag), "allgather")
     # Hub rows of this matrix sum 10^5 and more terms, and the pieces of a split row arrive in a
     # different order on every launch (REDs): the comparison allows for fp32 re-association.
     tol = dict(rtol=1e-4, atol=2e-3)
     torch.testing.assert_close(out_ag, out_rep, **tol)
     out_ag.fill_(float("nan"))
-    ms_needed = timed(lambda: sh_needed.forward(B_shard, out_ag))
+    ms_needed = timed(lambda: sh_needed.forward(B_shard, out_ag), "needed rows")
+    torch.testing.assert_close(out_ag, out_rep, **tol)
+    out_ag.fill_(float("nan"))
+    ms_pipe = timed(lambda: sh_pipe.forward(B_shard, out_ag), "pipelined row chunks")
     torch.testing.assert_close(out_ag, out_rep, **tol)
     sh.dim_chunks = dim_chunks
     sh._side = torch.cuda.Stream()
     out_ag.fill_(float("nan"))
-    ms_ov = timed(lambda: sh.forward(B_shard, out_ag))
+    ms_ov = timed(lambda: sh.forward(B_shard, out_ag), "dim slices")
     torch.testing.assert_close(out_ag, out_rep, **tol)
     gf = lambda ms: 2.0 * nnz_total * dim / ms / 1e6
     by = 4 * (n + 1) + 8 * nnz_total + 4 * dim * n * 2
@@ -248,6 +258,8 @@ def scaleout_spmm(scale=24, nnz=512_000_000, dim=128, seed=51, iters=5, warmup=2
             "generate_s": round(gen_s, 1), "world": world,
             "spmm_replicated_ms": round(ms_rep, 4), "allgather_spmm_ms": round(ms_ag, 4),
             "allgather_overlapped_ms": round(ms_ov, 4), "dim_chunks": dim_chunks,
+            "allgather_pipelined_ms": round(ms_pipe, 4), "row_chunks": row_chunks,
+            "allgather_pipelined_gflops": round(gf(ms_pipe), 1),
             "needed_rows_exchange_spmm_ms": round(ms_needed, 4),
             "needed_rows_exchange_spmm_gflops": round(gf(ms_needed), 1),
             "needed_rows_fraction": round(sh_needed.n_needed / n, 4),

@@ -190,6 +190,55 @@ def test_spmm_strided_operands_and_row_shards(dev, oracle, mats):
     close(out, want)
 
 
+def test_spmm_accumulate_over_column_blocks(dev, oracle, mats):
+    """cfg.accumulate adds the product to C: summing the products of the column blocks of A, the
+    first one in overwrite mode, gives A B; plain and split layouts, empty rows add nothing."""
+    from paramspmm_ae_b200 import _lib, ops
+    m = mats["rmat"]
+    rp, ci, v = m.numpy()
+    n = m.n_rows
+    rows = np.repeat(np.arange(n), np.diff(rp))
+    K = 3
+    block = ci * K // m.n_cols  # column block of every entry
+    for dim in (16, 64, 100, 256):
+        B = dense(m.n_cols, dim, 900 + dim)
+        want = oracle.spmm_csr(rp, ci, v, B.numpy())
+        Bd = B.to(dev)
+        for split in (False, True):
+            for lpr in (0, 2, 32):
+                out = torch.full((n, dim), float("nan"), device=dev)
+                for k in range(K):
+                    sel = block == k
+                    rp_k = np.concatenate([[0], np.cumsum(np.bincount(rows[sel], minlength=n))]).astype(np.int32)
+                    rp_k, ci_k, v_k = (torch.from_numpy(x).to(dev) for x in (rp_k, ci[sel], v[sel]))
+                    cfg = _lib.make_cfg(lanes_per_row=lpr, accumulate=1 if k else 0,
+                                        col_tile=128 if (dim == 256 and lpr == 32) else 0)
+                    if split:
+                        rps, tr = ops.split_csr_device(rp_k, 32)
+                        ops.spmm_into(out, Bd, rps, ci_k, v_k, target_row=tr, n_out_rows=n, cfg=cfg)
+                    else:
+                        ops.spmm_into(out, Bd, rp_k, ci_k, v_k, cfg=cfg)
+                close(out, want)
+    # adding into an existing C, and a matrix without entries adds nothing
+    C0 = dense(n, 64, 3).to(dev)
+    B = dense(m.n_cols, 64, 4)
+    d = m.to(dev)
+    out = C0.clone()
+    ops.spmm_into(out, B.to(dev), d.rowPtr, d.colIdx, d.val, cfg=_lib.make_cfg(accumulate=1))
+    close(out - C0, oracle.spmm_csr(rp, ci, v, B.numpy()))
+    out = C0.clone()
+    ops.spmm_into(out, B.to(dev), torch.zeros(n + 1, dtype=torch.int32, device=dev), d.colIdx[:0], d.val[:0],
+                  cfg=_lib.make_cfg(accumulate=1))
+    assert torch.equal(out, C0)
+    # built for 128-bit rows only: other widths are refused, not silently overwritten
+    with pytest.raises(_lib.PspmmError) as e:
+        ops.spmm_into(torch.zeros(n, 18, device=dev), dense(m.n_cols, 18, 1).to(dev), d.rowPtr, d.colIdx, d.val,
+                      cfg=_lib.make_cfg(accumulate=1))
+    assert e.value.code == _lib.PSPMM_E_UNSUPPORTED
+    with pytest.raises(_lib.PspmmError):
+        ops.spmm_into(out, B.to(dev), d.rowPtr, d.colIdx, d.val, cfg=_lib.make_cfg(accumulate=2))
+
+
 def test_spmm_rejects_inconsistent_sizes(dev, mats):
     """A row pointer or an output that does not match the row count raises before any launch
     (the kernels index both by the row count alone)."""

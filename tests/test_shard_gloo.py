@@ -52,9 +52,10 @@ def _worker(rank, world, port, dim_chunks, q, exchange="allgather"):
         m = synth.powerlaw_graph(1201, 9000, seed=7)          # same seed on every rank
         B = synth.dense_uniform(m.n_cols, 24, 5)
 
-        def local_spmm(out, Bfull, rowPtr, colIdx, val):
-            out.copy_(torch.from_numpy(orc.spmm_csr(rowPtr.numpy(), colIdx.numpy(), val.numpy(),
-                                                    np.ascontiguousarray(Bfull.numpy()))))
+        def local_spmm(out, Bfull, rowPtr, colIdx, val, accumulate=False):
+            prod = torch.from_numpy(orc.spmm_csr(rowPtr.numpy(), colIdx.numpy(), val.numpy(),
+                                                 np.ascontiguousarray(Bfull.numpy())))
+            out.add_(prod) if accumulate else out.copy_(prod)
             return out
 
         row_b = shard.partition_rows_by_nnz(m.rowPtr, world)
@@ -62,7 +63,7 @@ def _worker(rank, world, port, dim_chunks, q, exchange="allgather"):
                                col_bounds=row_b, device="cpu", local_spmm=local_spmm, dim_chunks=1,
                                exchange=exchange)
         lo, hi = op.my_cols
-        C_local = op.forward(B[lo:hi].contiguous())
+        C_local = op.forward(B[lo:hi].contiguous(), torch.full((op.local_rows, 24), float("nan")))
         want = orc.spmm_csr(*m.numpy(), B.numpy())[op.lo: op.hi]
         ok = np.allclose(C_local.numpy(), want, rtol=1e-5, atol=1e-5)
         # a second layer: the output shard is the next dense shard (row_bounds == col_bounds)
@@ -74,7 +75,7 @@ def _worker(rank, world, port, dim_chunks, q, exchange="allgather"):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("exchange", ["allgather", "needed"])
+@pytest.mark.parametrize("exchange", ["allgather", "needed", "pipelined"])
 @pytest.mark.parametrize("world", [2, 3])
 def test_sharded_spmm_two_layers_gloo(world, exchange):
     ctx = mp.get_context("spawn")
@@ -111,3 +112,34 @@ def test_needed_rows_exchange_single_rank():
     got = op.forward(B)
     want = orc.spmm_csr(*m.numpy(), B.numpy())
     assert np.allclose(got.numpy(), want, rtol=1e-5, atol=1e-5)
+
+
+@pytest.mark.parametrize("row_chunks", [1, 3, 4, 1000])
+def test_pipelined_exchange_single_rank(row_chunks):
+    """world = 1: the column blocks partition the entries of the shard, every block indexes its own
+    region of the chunked receive buffer, and the block products sum to the full product."""
+    from oracle import oracle as orc
+    m = synth.with_empty_rows(synth.powerlaw_graph(801, 3000, seed=9), every=3)
+    B = synth.dense_uniform(m.n_cols, 12, 4)
+    calls = []
+
+    def local_spmm(out, Bc, rowPtr, colIdx, val, accumulate=False):
+        calls.append(accumulate)
+        prod = torch.from_numpy(orc.spmm_csr(rowPtr.numpy(), colIdx.numpy(), val.numpy(),
+                                             np.ascontiguousarray(Bc.numpy())))
+        out.add_(prod) if accumulate else out.copy_(prod)
+        return out
+
+    op = shard.ShardedSpMM(m.rowPtr, m.colIdx, m.val, m.n_cols, 0, 1, device="cpu", local_spmm=local_spmm,
+                           exchange="pipelined", row_chunks=row_chunks)
+    assert sum(int(b[1].numel()) for b in op.blocks) == m.nnz
+    for k, (rp, ci, v) in enumerate(op.blocks):
+        assert rp.numel() == m.n_rows + 1 and int(rp[-1]) == ci.numel() == v.numel()
+        if ci.numel():
+            assert int(ci.min()) >= k * op.chunk_rows and int(ci.max()) < (k + 1) * op.chunk_rows
+    got = op.forward(B, torch.full((m.n_rows, 12), float("nan")))
+    assert calls == [False] + [True] * (row_chunks - 1)
+    want = orc.spmm_csr(*m.numpy(), B.numpy())
+    assert np.allclose(got.numpy(), want, rtol=1e-5, atol=1e-5)
+    with pytest.raises(ValueError):
+        op.forward(synth.dense_uniform(m.n_cols, 10, 4))
