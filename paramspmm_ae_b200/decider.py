@@ -183,3 +183,90 @@ def install_tuner():
 
     ops.tuner = tuner
     return tuner
+
+
+def main(argv=None):
+    """Command line of the reference's decider.py (:96-173): for every MatrixMarket file under
+    ``--path`` (or the one named by ``--mtx_name``) and every dim, choose the configuration, check
+    the product against ``torch.sparse.mm`` with the reference's rule, time it (200 back-to-back
+    launches) and time cuSPARSE and the GE-SpMM restatement on the same arrays.  Prints the
+    reference's separator lines plus one summary line per dim; ``--json`` also writes one JSON
+    object per (matrix, dim)."""
+    import argparse
+    import glob
+
+    ap = argparse.ArgumentParser(description=main.__doc__)
+    ap.add_argument("--path", type=str, default="./dataset/all-mtx/", help="path to the mtx files")
+    ap.add_argument("--dim_list", nargs="*", type=int, default=[16, 32, 48, 64, 80, 96, 112, 128])
+    ap.add_argument("--mtx_name", type=str, default="", help="mtx file name (without .mtx)")
+    ap.add_argument("--json", type=str, default="", help="write one JSON line per (matrix, dim) to this file")
+    ap.add_argument("--cache_dir", type=str, default=None, help="keep parsed matrices here as binary CSR")
+    ap.add_argument("--no_baselines", action="store_true", help="skip the cuSPARSE and GE-SpMM timings")
+    args = ap.parse_args(argv)
+    print(args)
+
+    import torch
+
+    from . import _lib, baselines, ops
+    from .graph_input import graph_input
+    from .verification import SpMM_verification
+
+    path = args.path if args.path.endswith(os.sep) else args.path + os.sep
+    if args.mtx_name:
+        names = [args.mtx_name]
+    else:
+        names = sorted(os.path.basename(f)[:-4] for f in glob.glob(os.path.join(path, "*.mtx")))
+    decider = SpMMDecider()
+    decider.gen_model_dict(args.dim_list)
+    dev = torch.device("cuda")
+    records = []
+    for name in names:
+        graph = graph_input(mtx_name=name, path=path, cache_dir=args.cache_dir)
+        print("-------------mtx: {}-------------".format(name))
+        graph.load(load_from_mtx=True)
+        c = graph.csr_data
+        n, nnz = graph.mtx_nodes, graph.mtx_edges
+        veri = SpMM_verification(1, c.rowPtr, c.colIdx, c.val)
+        rp, ci, v = c.rowPtr.to(dev), c.colIdx.to(dev), c.val.to(dev)
+        layouts = {}
+        for dim in args.dim_list:
+            plan = decider.plan(graph, dim)
+            legacy = decider.config_PCSR(graph, dim)
+            X = torch.ones(n, dim, device=dev)
+            cfg = _lib.make_cfg(**plan.kernel_cfg())
+            out = torch.empty(n, dim, device=dev)
+            if plan["if_split"]:
+                g = int(plan["granularity"])
+                if g not in layouts:
+                    layouts[g] = ops.split_csr_device(rp, g)
+                seg, tr = layouts[g]
+            else:
+                seg, tr = rp, None
+            ops.spmm_into(out, X, seg, ci, v, target_row=tr, n_out_rows=n, cfg=cfg)
+            veri.reference(dim)
+            veri.compare(out.cpu(), name)
+            ms = ops.spmm_time_ms(X, seg, ci, v, tr, cfg=cfg, n_out_rows=n)
+            rec = {"mtx": name, "nodes": n, "edges": nnz, "dim": dim, "regime": plan["regime"],
+                   "if_split": int(plan["if_split"]), "vec_size": int(plan["vec_size"]),
+                   "granularity": plan["granularity"], "kernel": plan.kernel_cfg(), "legacy_tuple": list(legacy),
+                   "ms": round(ms, 5), "gflops": int(nnz / 1e6 * dim * 2 / ms)}
+            if not args.no_baselines:
+                rec["cusparse_gflops"] = baselines.cusparse_profile(X, rp, ci, v)
+                rec["gespmm_gflops"] = baselines.gespmm_profile(X, rp, ci, v)
+            print("=======================================")
+            line = "dim: {dim} regime: {regime} if_split: {if_split} vec_size: {vec_size} gflops: {gflops}".format(**rec)
+            if not args.no_baselines:
+                line += " cusparse: {} ({:.2f}x) gespmm: {} ({:.2f}x)".format(
+                    rec["cusparse_gflops"], rec["gflops"] / max(1, rec["cusparse_gflops"]),
+                    rec["gespmm_gflops"], rec["gflops"] / max(1, rec["gespmm_gflops"]))
+            print(line)
+            records.append(rec)
+    if args.json:
+        with open(args.json, "w") as f:
+            for rec in records:
+                f.write(json.dumps(rec) + "\n")
+    return records
+
+
+if __name__ == "__main__":
+    main()
