@@ -283,39 +283,94 @@ extern "C" int pspmm_mtx_read_csr(const char *path, int32_t force_ones, int32_t 
     if (stored != info.stored)
         return PSPMM_E_FORMAT;
 
-    // 2. entries per row after mirroring the off-diagonal part of (skew-)symmetric files
+    // 2. partition by row bucket.  A direct scatter by row is 16-byte stores at random places of
+    //    the whole array; buckets of consecutive rows whose entries fit the cache are filled with
+    //    sequential streams instead (per thread and bucket, in file order: the layout does not
+    //    depend on timing), and the scatter by row happens inside one bucket at a time.
     try {
-    std::vector<int64_t> off((size_t)n + 1, 0);
     const bool mirror = info.symmetric != 0;
-#pragma omp parallel for num_threads(T) schedule(static, 1)
-    for (int t = 0; t < T; ++t)
-        for (const Entry &e : parts[(size_t)t]) {
-            __atomic_fetch_add(&off[(size_t)e.row + 1], 1, __ATOMIC_RELAXED);
-            if (mirror && e.row != e.col)
-                __atomic_fetch_add(&off[(size_t)e.col + 1], 1, __ATOMIC_RELAXED);
-        }
-    for (int64_t r = 0; r < n; ++r)
-        off[(size_t)r + 1] += off[(size_t)r];
-    const int64_t expanded = off[(size_t)n];
-
-    // 3. scatter by row (order inside a row is fixed by the sort that follows)
-    // (left uninitialised: every slot is written by the scatter)
-    std::unique_ptr<Entry[]> byrow(new Entry[(size_t)expanded + 1]);
+    // the reference overwrites the values after the expansion, so forced ones stay +1
+    const double sign = (info.symmetric == 2 && !force_ones) ? -1.0 : 1.0;
+    int shift = 0;  // rows per bucket = 1 << shift: about 16 K entries (256 KiB) per bucket
     {
-        std::vector<int64_t> cur(off.begin(), off.end() - 1);
-        // the reference overwrites the values after the expansion, so forced ones stay +1
-        const double sign = (info.symmetric == 2 && !force_ones) ? -1.0 : 1.0;
+        const int64_t want_buckets = std::max<int64_t>(1, std::min<int64_t>(4096, info.nnz_max / 16384));
+        while (((n + ((int64_t)1 << shift) - 1) >> shift) > want_buckets)
+            ++shift;
+    }
+    const int64_t NB = std::max<int64_t>(1, (n + ((int64_t)1 << shift) - 1) >> shift);
+    std::vector<int64_t> hist((size_t)T * (size_t)NB, 0);  // [thread][bucket], then start offsets
 #pragma omp parallel for num_threads(T) schedule(static, 1)
-        for (int t = 0; t < T; ++t) {
-            for (const Entry &e : parts[(size_t)t]) {
-                byrow[(size_t)__atomic_fetch_add(&cur[(size_t)e.row], 1, __ATOMIC_RELAXED)] = e;
-                if (mirror && e.row != e.col)
-                    byrow[(size_t)__atomic_fetch_add(&cur[(size_t)e.col], 1, __ATOMIC_RELAXED)] =
-                        Entry{e.col, e.row, sign * e.val};
-            }
-            std::vector<Entry>().swap(parts[(size_t)t]);
+    for (int t = 0; t < T; ++t) {
+        int64_t *h = hist.data() + (size_t)t * (size_t)NB;
+        for (const Entry &e : parts[(size_t)t]) {
+            ++h[e.row >> shift];
+            if (mirror && e.row != e.col)
+                ++h[e.col >> shift];
         }
     }
+    std::vector<int64_t> bstart((size_t)NB + 1, 0);
+    {
+        int64_t run = 0;
+        for (int64_t bk = 0; bk < NB; ++bk) {
+            bstart[(size_t)bk] = run;
+            for (int t = 0; t < T; ++t) {
+                int64_t &h = hist[(size_t)t * (size_t)NB + (size_t)bk];
+                const int64_t c = h;
+                h = run;
+                run += c;
+            }
+        }
+        bstart[(size_t)NB] = run;
+    }
+    const int64_t expanded = bstart[(size_t)NB];
+    // (left uninitialised: every slot is written below)
+    std::unique_ptr<Entry[]> byrow(new Entry[(size_t)expanded + 1]);
+#pragma omp parallel for num_threads(T) schedule(static, 1)
+    for (int t = 0; t < T; ++t) {
+        int64_t *cur = hist.data() + (size_t)t * (size_t)NB;
+        for (const Entry &e : parts[(size_t)t]) {
+            byrow[(size_t)cur[e.row >> shift]++] = e;
+            if (mirror && e.row != e.col)
+                byrow[(size_t)cur[e.col >> shift]++] = Entry{e.col, e.row, sign * e.val};
+        }
+        std::vector<Entry>().swap(parts[(size_t)t]);
+    }
+
+    // 3. inside every bucket: count per row, then place the entries row by row (through a copy of
+    //    the bucket, which is cache-sized)
+    std::vector<int64_t> off((size_t)n + 1, 0);
+    int fail = 0;
+#pragma omp parallel
+    {
+        std::vector<Entry> tmp;
+        std::vector<int64_t> cnt;
+#pragma omp for schedule(dynamic, 1)
+        for (int64_t bk = 0; bk < NB; ++bk) {
+            const int64_t r0 = bk << shift, r1 = std::min<int64_t>(n, (bk + 1) << shift);
+            const int64_t lo = bstart[(size_t)bk], hi = bstart[(size_t)bk + 1];
+            try {
+                tmp.assign(byrow.get() + lo, byrow.get() + hi);
+                cnt.assign((size_t)(r1 - r0) + 1, 0);
+            } catch (const std::bad_alloc &) {
+                __atomic_store_n(&fail, 1, __ATOMIC_RELAXED);
+                continue;
+            }
+            for (const Entry &e : tmp)
+                ++cnt[(size_t)(e.row - r0) + 1];
+            int64_t run = lo;
+            for (int64_t r = r0; r < r1; ++r) {
+                const int64_t c = cnt[(size_t)(r - r0) + 1];
+                off[(size_t)r] = run;
+                cnt[(size_t)(r - r0)] = run;  // becomes the write cursor of row r
+                run += c;
+            }
+            for (const Entry &e : tmp)
+                byrow[(size_t)cnt[(size_t)(e.row - r0)]++] = e;
+        }
+    }
+    if (fail)
+        return PSPMM_E_NOMEM;
+    off[(size_t)n] = expanded;
 
     // 4. canonical rows: columns ascending, equal coordinates summed (in double, as scipy does)
     std::vector<int64_t> uniq((size_t)n + 1, 0);

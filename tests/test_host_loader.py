@@ -46,6 +46,7 @@ HAND_WRITTEN = {
     "symmetric_pattern_no_final_newline": "%%MatrixMarket matrix coordinate pattern symmetric\n3 3 4\n1 1\n2 1\n3 1\n3 3",
     "skew_integer_crlf_mixed_case": "%%MatrixMarket MATRIX Coordinate Integer Skew-Symmetric\r\n3 3 2\r\n2 1 4\r\n3 2 -5\r\n",
     "no_entries": "%%MatrixMarket matrix coordinate real general\n5 7 0\n",
+    "no_rows": "%%MatrixMarket matrix coordinate real general\n0 0 0\n",
     "rectangular_pattern": "%%MatrixMarket matrix coordinate pattern general\n2 9 3\n2 9\n1 1\n2 1\n",
 }
 
