@@ -118,11 +118,16 @@ def test_argument_errors_are_codes_not_crashes(pspmm_lib):
                                     ctypes.byref(cfg), null, null, 0, null) == _lib.PSPMM_E_RANGE
     # legacy hints keep the reference's domain
     for bad in (_lib.make_cfg(CF=9, blkWarpNum=4), _lib.make_cfg(CF=1, blkWarpNum=5),
-                _lib.make_cfg(lanes_per_row=3), _lib.make_cfg(vec_width=3), _lib.make_cfg(cta_threads=100)):
+                _lib.make_cfg(lanes_per_row=3), _lib.make_cfg(vec_width=3), _lib.make_cfg(cta_threads=100),
+                _lib.make_cfg(accumulate=2), _lib.make_cfg(accumulate=-1), _lib.make_cfg(col_tile=6)):
         assert pspmm_lib.pspmm_spmm_csr(one, one, one, one, one, 4, 4, 4, 16, 16, 16, ctypes.byref(bad),
                                         null, null, 0, null) == _lib.PSPMM_E_CONFIG
     assert pspmm_lib.pspmm_sddmm_csr(one, one, one, one, one, 4, 4, 16, 16, 16,
                                      ctypes.byref(_lib.make_cfg(CF=5, blkWarpNum=4)), null, null, 0,
+                                     null) == _lib.PSPMM_E_CONFIG
+    # SDDMM has nothing to add into
+    assert pspmm_lib.pspmm_sddmm_csr(one, one, one, one, one, 4, 4, 16, 16, 16,
+                                     ctypes.byref(_lib.make_cfg(accumulate=1)), null, null, 0,
                                      null) == _lib.PSPMM_E_CONFIG
     assert pspmm_lib.pspmm_spmm_bcsr(one, one, one, 4, one, one, 4, 4, 4, 16, 16, 16, ctypes.byref(cfg),
                                      null, null, 0, null) == _lib.PSPMM_E_UNSUPPORTED
