@@ -29,6 +29,10 @@ arrived, while chunk k+1 is still on the wire; the first product overwrites C, t
 it (``pspmm_cfg.accumulate``).  Unlike slicing the dense columns, this reads every entry of A
 once and keeps full-width row gathers.
 
+``exchange="needed_pipelined"`` combines the two: the rows a shard references are requested chunk
+by chunk (the same cut of every owner's block into ``row_chunks`` runs of rows), one all-to-all
+per chunk, and the product of column block k runs while the rows of chunk k+1 are on the wire.
+
 ``dim_chunks > 1`` splits the dense columns into slices and gathers slice s+1 on a side
 stream while the SpMM of slice s runs (the kernels take explicit leading dimensions, so a
 slice of C is written in place).
@@ -80,8 +84,8 @@ class ShardedSpMM:
     def __init__(self, rowPtr, colIdx, val, n_cols, rank, world, row_bounds=None, col_bounds=None,
                  device="cuda", group=None, local_spmm=None, dim_chunks=1, exchange="allgather",
                  row_chunks=4):
-        if exchange not in ("allgather", "needed", "pipelined"):
-            raise ValueError("exchange must be 'allgather', 'needed' or 'pipelined'")
+        if exchange not in ("allgather", "needed", "pipelined", "needed_pipelined"):
+            raise ValueError("exchange must be 'allgather', 'needed', 'pipelined' or 'needed_pipelined'")
         if row_chunks < 1:
             raise ValueError("row_chunks must be at least 1")
         self.rank, self.world, self.group, self.dim_chunks = rank, world, group, dim_chunks
@@ -102,14 +106,16 @@ class ShardedSpMM:
             self._plan_needed_rows(ci.to(device))
         elif exchange == "pipelined":
             self._plan_row_chunks(ci.to(device))
+        elif exchange == "needed_pipelined":
+            self._plan_needed_row_chunks(ci.to(device))
         else:
             self.colIdx = remap_columns(ci.to(device), self.col_bounds, self.max_rows)
-        if exchange == "pipelined":
+        if exchange in ("pipelined", "needed_pipelined"):
             self.block_spmm = [local_spmm if local_spmm is not None else self._planned_spmm(rp_k)
                                for rp_k, _, _ in self.blocks]
         else:
             self.local_spmm = local_spmm if local_spmm is not None else self._planned_spmm()
-        overlap = dim_chunks > 1 or exchange == "pipelined"
+        overlap = dim_chunks > 1 or exchange in ("pipelined", "needed_pipelined")
         self._side = torch.cuda.Stream() if (self.device.type == "cuda" and overlap) else None
 
     def _plan_row_chunks(self, cols_global):
@@ -144,6 +150,96 @@ class ShardedSpMM:
             self.blocks.append((rp, pos[a: a + sizes[kk]].contiguous(), val[a: a + sizes[kk]].contiguous()))
             a += sizes[kk]
         self.val = self.colIdx = None  # held per block from here on
+
+    def _plan_needed_row_chunks(self, cols_global):
+        """Set-up of the chunked sparse exchange.  Chunk k covers rows [k, k+1) * chunk_rows of every
+        owner's block; for each chunk: the distinct referenced columns (sorted, hence grouped by
+        owner), the row ids every owner has to send, and the column block of A renumbered to
+        positions in one receive buffer that holds the chunks one after the other."""
+        import torch.distributed as dist
+
+        dev = cols_global.device
+        K, W, n_loc = self.row_chunks, self.world, self.hi - self.lo
+        cr = max(1, -(-self.max_rows // K))
+        self.chunk_rows = cr
+        cb = self.col_bounds.to(dev)
+        c = cols_global.long()
+        owner = torch.searchsorted(cb, c, right=True) - 1
+        k = torch.div(c - cb[owner], cr, rounding_mode="floor")
+        rows = torch.repeat_interleave(torch.arange(n_loc, device=dev),
+                                       (self.rowPtr[1:] - self.rowPtr[:-1]).long())
+        key = k * n_loc + rows
+        order = torch.argsort(key, stable=True)
+        counts = torch.bincount(key, minlength=K * n_loc).view(K, n_loc)
+        del key, rows, owner
+        c, val = c[order], self.val[order]
+        del order
+        sizes = [int(x) for x in counts.sum(1).cpu()]
+        self.blocks, self.chunk_plan, a, base = [], [], 0, 0
+        for kk in range(K):
+            ck = c[a: a + sizes[kk]]
+            need = torch.unique(ck)  # sorted distinct global column ids of this chunk
+            cuts = torch.searchsorted(need, cb)
+            recv_counts = (cuts[1:] - cuts[:-1]).cpu()
+            own = torch.repeat_interleave(torch.arange(W, device=dev), recv_counts.to(dev))
+            wanted = (need - cb[own]).to(torch.int64)
+            recv_splits = [int(x) for x in recv_counts]
+            if W == 1:
+                send_splits, send_rows = list(recv_splits), wanted
+            else:
+                counts_out = torch.empty(W, dtype=torch.int64, device=dev)
+                dist.all_to_all_single(counts_out, recv_counts.to(dev), group=self.group)
+                send_splits = [int(x) for x in counts_out.cpu()]
+                send_rows = torch.empty(sum(send_splits), dtype=torch.int64, device=dev)
+                dist.all_to_all_single(send_rows, wanted, output_split_sizes=send_splits,
+                                       input_split_sizes=recv_splits, group=self.group)
+            rp = torch.zeros(n_loc + 1, dtype=torch.int32, device=dev)
+            rp[1:] = counts[kk].cumsum(0)
+            pos = (base + torch.searchsorted(need, ck)).to(torch.int32)
+            self.blocks.append((rp, pos, val[a: a + sizes[kk]].contiguous()))
+            self.chunk_plan.append((base, int(need.numel()), recv_splits, send_splits, send_rows))
+            base += int(need.numel())
+            a += sizes[kk]
+        self.n_needed = base
+        self.val = self.colIdx = None
+
+    def _forward_needed_pipelined(self, B_shard, out):
+        import torch.distributed as dist
+
+        dim = B_shard.shape[1]
+        recv = torch.empty(max(1, self.n_needed), dim, dtype=B_shard.dtype, device=B_shard.device)
+        cuda = self._side is not None
+        main = torch.cuda.current_stream() if cuda else None
+        events = []
+
+        def exchange(kk):
+            base, cnt, recv_splits, send_splits, send_rows = self.chunk_plan[kk]
+            send = B_shard.index_select(0, send_rows)
+            dst = recv[base: base + cnt]
+            if self.world == 1:
+                dst.copy_(send)
+            else:
+                dist.all_to_all_single(dst, send, output_split_sizes=recv_splits,
+                                       input_split_sizes=send_splits, group=self.group)
+
+        if cuda:
+            self._side.wait_stream(main)
+            with torch.cuda.stream(self._side):
+                for kk in range(self.row_chunks):
+                    exchange(kk)
+                    ev = torch.cuda.Event()
+                    ev.record(self._side)
+                    events.append(ev)
+            B_shard.record_stream(self._side)
+            recv.record_stream(self._side)
+        for kk in range(self.row_chunks):
+            if cuda:
+                main.wait_event(events[kk])
+            else:
+                exchange(kk)
+            rp, ci, v = self.blocks[kk]
+            self.block_spmm[kk](out, recv, rp, ci, v, accumulate=kk > 0)
+        return out
 
     def _forward_pipelined(self, B_shard, out):
         import torch.distributed as dist
@@ -283,10 +379,12 @@ class ShardedSpMM:
         if self.exchange == "needed":
             self.local_spmm(out, self._exchange_needed(B_shard), self.rowPtr, self.colIdx, self.val)
             return out
-        if self.exchange == "pipelined":
+        if self.exchange in ("pipelined", "needed_pipelined"):
             if dim % 4 != 0:
                 raise ValueError("the pipelined exchange adds into C with 128-bit accesses: dim must be a multiple of 4")
-            return self._forward_pipelined(B_shard, out)
+            if self.exchange == "pipelined":
+                return self._forward_pipelined(B_shard, out)
+            return self._forward_needed_pipelined(B_shard, out)
         k = max(1, min(self.dim_chunks, dim // 4)) if self.dim_chunks > 1 else 1
         if k == 1:
             self.local_spmm(out, self._gather(B_shard), self.rowPtr, self.colIdx, self.val)

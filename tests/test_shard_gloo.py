@@ -75,7 +75,7 @@ def _worker(rank, world, port, dim_chunks, q, exchange="allgather"):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("exchange", ["allgather", "needed", "pipelined"])
+@pytest.mark.parametrize("exchange", ["allgather", "needed", "pipelined", "needed_pipelined"])
 @pytest.mark.parametrize("world", [2, 3])
 def test_sharded_spmm_two_layers_gloo(world, exchange):
     ctx = mp.get_context("spawn")
@@ -110,6 +110,36 @@ def test_needed_rows_exchange_single_rank():
     assert op.n_needed == used.numel() < m.n_cols
     assert torch.equal(op.send_rows, used)
     got = op.forward(B)
+    want = orc.spmm_csr(*m.numpy(), B.numpy())
+    assert np.allclose(got.numpy(), want, rtol=1e-5, atol=1e-5)
+
+
+@pytest.mark.parametrize("row_chunks", [1, 3, 1000])
+def test_needed_pipelined_exchange_single_rank(row_chunks):
+    """world = 1: the chunks' receive regions tile the compact buffer, together they hold exactly the
+    referenced rows, and the block products sum to the full product."""
+    from oracle import oracle as orc
+    m = synth.with_empty_rows(synth.powerlaw_graph(801, 3000, seed=9), every=3)
+    B = synth.dense_uniform(m.n_cols, 12, 4)
+
+    def local_spmm(out, Bc, rowPtr, colIdx, val, accumulate=False):
+        prod = torch.from_numpy(orc.spmm_csr(rowPtr.numpy(), colIdx.numpy(), val.numpy(),
+                                             np.ascontiguousarray(Bc.numpy())))
+        out.add_(prod) if accumulate else out.copy_(prod)
+        return out
+
+    op = shard.ShardedSpMM(m.rowPtr, m.colIdx, m.val, m.n_cols, 0, 1, device="cpu", local_spmm=local_spmm,
+                           exchange="needed_pipelined", row_chunks=row_chunks)
+    used = torch.unique(m.colIdx.long())
+    assert op.n_needed == used.numel() < m.n_cols
+    assert torch.equal(torch.cat([p[4] for p in op.chunk_plan]), used)  # chunks are runs of rows: order is kept
+    end = 0
+    for (base, cnt, _, _, _), (rp, ci, v) in zip(op.chunk_plan, op.blocks):
+        assert base == end
+        end += cnt
+        if ci.numel():
+            assert base <= int(ci.min()) and int(ci.max()) < end
+    got = op.forward(B, torch.full((m.n_rows, 12), float("nan")))
     want = orc.spmm_csr(*m.numpy(), B.numpy())
     assert np.allclose(got.numpy(), want, rtol=1e-5, atol=1e-5)
 
