@@ -218,7 +218,7 @@ def main():
             print(json.dumps({"metric": "row-sharded SpMM GFLOP/s (2*nnz*dim/t), exchange of B included",
                               "value": max(r["allgather_overlapped_gflops"], r["allgather_spmm_gflops"],
                                            r["needed_rows_exchange_spmm_gflops"], r["allgather_pipelined_gflops"],
-                                           r["needed_rows_pipelined_gflops"]),
+                                           r["needed_rows_pipelined_gflops"], r["copy_engine_pipelined_gflops"]),
                               "unit": "GFLOP/s", "n_gpus": world,
                               "higher_is_better": True, "scaling": "strong", "dtype": "f32", "data": "synthetic",
                               "config": {"workload": "c5_scaleout", "scale": args.c5_scale, "nnz": r["nnz"],

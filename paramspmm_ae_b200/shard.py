@@ -29,6 +29,15 @@ arrived, while chunk k+1 is still on the wire; the first product overwrites C, t
 it (``pspmm_cfg.accumulate``).  Unlike slicing the dense columns, this reads every entry of A
 once and keeps full-width row gathers.
 
+``transport="copy_engine"`` (pipelined exchange only) moves the chunks without NCCL kernels:
+every rank keeps its block of the dense operand in a buffer that its peers have mapped
+(``torch.distributed._symmetric_memory``), and each rank pulls the chunks it needs with plain
+device-to-device copies, which the GPU's copy engines execute over NVLink.  No SM is taken from the
+SpMM and none of its memory instructions queue behind the transfer, so the overlap is the
+arithmetic one expects; two one-element all-reduces per product fence the peers' reads (blocks
+ready before the first pull, pulls finished before a block may be overwritten).  A producer can
+write straight into ``symmetric_input(dim)`` and pass that to ``forward`` to skip the staging copy.
+
 ``exchange="needed_pipelined"`` combines the two: the rows a shard references are requested chunk
 by chunk (the same cut of every owner's block into ``row_chunks`` runs of rows), one all-to-all
 per chunk, and the product of column block k runs while the rows of chunk k+1 are on the wire.
@@ -83,11 +92,16 @@ class ShardedSpMM:
 
     def __init__(self, rowPtr, colIdx, val, n_cols, rank, world, row_bounds=None, col_bounds=None,
                  device="cuda", group=None, local_spmm=None, dim_chunks=1, exchange="allgather",
-                 row_chunks=4):
+                 row_chunks=4, transport="nccl"):
         if exchange not in ("allgather", "needed", "pipelined", "needed_pipelined"):
             raise ValueError("exchange must be 'allgather', 'needed', 'pipelined' or 'needed_pipelined'")
         if row_chunks < 1:
             raise ValueError("row_chunks must be at least 1")
+        if transport not in ("nccl", "copy_engine"):
+            raise ValueError("transport must be 'nccl' or 'copy_engine'")
+        if transport == "copy_engine" and exchange != "pipelined":
+            raise ValueError("the copy-engine transport moves whole row chunks: use exchange='pipelined'")
+        self.transport, self._peer = transport, None
         self.rank, self.world, self.group, self.dim_chunks = rank, world, group, dim_chunks
         self.exchange, self.row_chunks = exchange, row_chunks
         self.row_bounds = partition_rows_by_nnz(rowPtr, world) if row_bounds is None else torch.as_tensor(row_bounds).long()
@@ -207,7 +221,7 @@ class ShardedSpMM:
         import torch.distributed as dist
 
         dim = B_shard.shape[1]
-        recv = torch.empty(max(1, self.n_needed), dim, dtype=B_shard.dtype, device=B_shard.device)
+        recv = self._receive_buffer(max(1, self.n_needed), dim, B_shard)
         cuda = self._side is not None
         main = torch.cuda.current_stream() if cuda else None
         events = []
@@ -231,7 +245,6 @@ class ShardedSpMM:
                     ev.record(self._side)
                     events.append(ev)
             B_shard.record_stream(self._side)
-            recv.record_stream(self._side)
         for kk in range(self.row_chunks):
             if cuda:
                 main.wait_event(events[kk])
@@ -241,12 +254,80 @@ class ShardedSpMM:
             self.block_spmm[kk](out, recv, rp, ci, v, accumulate=kk > 0)
         return out
 
-    def _forward_pipelined(self, B_shard, out):
+    def _receive_buffer(self, rows, dim, like):
+        """The receive buffer of the pipelined exchanges, kept between calls: both streams use it,
+        and the side stream waits for the main one before it writes, so one buffer is enough and
+        the allocator is not asked for gigabytes per product."""
+        buf = getattr(self, "_recv", None)
+        if buf is None or buf.shape != (rows, dim) or buf.dtype != like.dtype or buf.device != like.device:
+            buf = self._recv = torch.empty(rows, dim, dtype=like.dtype, device=like.device)
+        return buf
+
+    def _peer_blocks(self, dim, like):
+        """This rank's block of the dense operand in peer-mapped memory, padded to whole chunks,
+        plus the peers' blocks as local tensors.  Created once per width (a collective call)."""
+        if self._peer is None or self._peer[0].shape[1] != dim or self._peer[0].dtype != like.dtype:
+            import torch.distributed as dist
+            import torch.distributed._symmetric_memory as symm
+
+            rows = self.row_chunks * self.chunk_rows
+            src = symm.empty((rows, dim), dtype=like.dtype, device=like.device)
+            src.zero_()
+            group = self.group if self.group is not None else dist.group.WORLD
+            hdl = symm.rendezvous(src, group.group_name)
+            peers = [hdl.get_buffer(q, (rows, dim), like.dtype) for q in range(self.world)]
+            fence = torch.zeros(1, dtype=torch.int32, device=like.device)
+            self._peer = (src, peers, fence)
+        return self._peer
+
+    def symmetric_input(self, dim, dtype=torch.float32):
+        """The peer-mapped buffer for this rank's block of the dense operand (copy-engine transport):
+        rows [0, my block's row count) of it, for a producer to write into and hand to ``forward``."""
+        like = torch.empty(0, dtype=dtype, device=self.device)
+        return self._peer_blocks(dim, like)[0][: self.my_cols[1] - self.my_cols[0]]
+
+    def _forward_copy_engine(self, B_shard, out):
         import torch.distributed as dist
 
         K, W, cr = self.row_chunks, self.world, self.chunk_rows
         rows, dim = B_shard.shape
-        full = torch.empty(K * W * cr, dim, dtype=B_shard.dtype, device=B_shard.device)
+        src, peers, fence = self._peer_blocks(dim, B_shard)
+        full = self._receive_buffer(K * W * cr, dim, B_shard)
+        main = torch.cuda.current_stream()
+        events = []
+        self._side.wait_stream(main)
+        with torch.cuda.stream(self._side):
+            if B_shard.data_ptr() != src.data_ptr():
+                src[:rows].copy_(B_shard)
+            dist.all_reduce(fence, group=self.group)  # every block is in place
+            for kk in range(K):
+                for i in range(W):
+                    q = (self.rank + i) % W  # own chunk first, then the peers round-robin
+                    full[(kk * W + q) * cr: (kk * W + q + 1) * cr].copy_(peers[q][kk * cr: (kk + 1) * cr])
+                ev = torch.cuda.Event()
+                ev.record(self._side)
+                events.append(ev)
+            dist.all_reduce(fence, group=self.group)  # every peer has finished reading this block
+        B_shard.record_stream(self._side)
+        for kk in range(K):
+            main.wait_event(events[kk])
+            rp, ci, v = self.blocks[kk]
+            self.block_spmm[kk](out, full, rp, ci, v, accumulate=kk > 0)
+        # a producer on the main stream may overwrite the block only after the closing fence
+        main.wait_stream(self._side)
+        return out
+
+    def _forward_pipelined(self, B_shard, out):
+        import torch.distributed as dist
+
+        if self.transport == "copy_engine":
+            if self._side is None or self.world == 1:
+                raise ValueError("the copy-engine transport needs CUDA devices and at least two ranks")
+            return self._forward_copy_engine(B_shard, out)
+
+        K, W, cr = self.row_chunks, self.world, self.chunk_rows
+        rows, dim = B_shard.shape
+        full = self._receive_buffer(K * W * cr, dim, B_shard)
         cuda = self._side is not None
         main = torch.cuda.current_stream() if cuda else None
         events = []
@@ -273,7 +354,6 @@ class ShardedSpMM:
                     ev.record(self._side)
                     events.append(ev)
             B_shard.record_stream(self._side)
-            full.record_stream(self._side)
         for kk in range(K):
             if cuda:
                 main.wait_event(events[kk])

@@ -189,7 +189,8 @@ def scaleout_spmm(scale=24, nnz=512_000_000, dim=128, seed=51, iters=5, warmup=2
     row blocks followed by the SpMM, the exchange of only the rows each shard references (one
     all-to-all) followed by the SpMM on the compact operand, the all-gather in `row_chunks` row
     chunks with the product of column block k running while chunk k+1 is on the wire (for all rows
-    and for the referenced rows only), and the
+    over NCCL, for all rows pulled by the copy engines from peer-mapped memory, and for the referenced
+    rows only), and the
     all-gather with the dense columns cut into `dim_chunks` slices so that the gather of slice s+1
     overlaps the SpMM of slice s.
     Every rank generates the same global matrix from the seed and keeps only its rows.
@@ -208,6 +209,10 @@ def scaleout_spmm(scale=24, nnz=512_000_000, dim=128, seed=51, iters=5, warmup=2
     sh_needed = ShardedSpMM(m.rowPtr, m.colIdx, m.val, n, rank, world, device=dev, exchange="needed")
     sh_pipe = ShardedSpMM(m.rowPtr, m.colIdx, m.val, n, rank, world, device=dev, exchange="pipelined",
                           row_chunks=row_chunks)
+    sh_ce = None
+    if world > 1:
+        sh_ce = ShardedSpMM(m.rowPtr, m.colIdx, m.val, n, rank, world, device=dev, exchange="pipelined",
+                            row_chunks=row_chunks, transport="copy_engine")
     sh_np = ShardedSpMM(m.rowPtr, m.colIdx, m.val, n, rank, world, device=dev, exchange="needed_pipelined",
                         row_chunks=row_chunks)
     nnz_total, nnz_local = m.nnz, b - a
@@ -258,6 +263,13 @@ def scaleout_spmm(scale=24, nnz=512_000_000, dim=128, seed=51, iters=5, warmup=2
     out_ag.fill_(float("nan"))
     ms_np = timed(lambda: sh_np.forward(B_shard, out_ag), "needed rows in pipelined row chunks")
     torch.testing.assert_close(out_ag, out_rep, **tol)
+    ms_ce = None
+    if sh_ce is not None:
+        B_sym = sh_ce.symmetric_input(dim)  # the dense block lives in peer-mapped memory, as a producer would leave it
+        B_sym.copy_(B_shard)
+        out_ag.fill_(float("nan"))
+        ms_ce = timed(lambda: sh_ce.forward(B_sym, out_ag), "pipelined row chunks, copy engines")
+        torch.testing.assert_close(out_ag, out_rep, **tol)
     gf = lambda ms: 2.0 * nnz_total * dim / ms / 1e6
     by = 4 * (n + 1) + 8 * nnz_total + 4 * dim * n * 2
     return {"n": n, "nnz": nnz_total, "nnz_local": nnz_local, "rows_local": sh.local_rows, "dim": dim,
@@ -266,6 +278,8 @@ def scaleout_spmm(scale=24, nnz=512_000_000, dim=128, seed=51, iters=5, warmup=2
             "allgather_overlapped_ms": round(ms_ov, 4), "dim_chunks": dim_chunks,
             "allgather_pipelined_ms": round(ms_pipe, 4), "row_chunks": row_chunks,
             "allgather_pipelined_gflops": round(gf(ms_pipe), 1),
+            "copy_engine_pipelined_ms": None if ms_ce is None else round(ms_ce, 4),
+            "copy_engine_pipelined_gflops": 0.0 if ms_ce is None else round(gf(ms_ce), 1),
             "needed_rows_pipelined_ms": round(ms_np, 4), "needed_rows_pipelined_gflops": round(gf(ms_np), 1),
             "needed_rows_exchange_spmm_ms": round(ms_needed, 4),
             "needed_rows_exchange_spmm_gflops": round(gf(ms_needed), 1),
