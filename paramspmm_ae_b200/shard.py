@@ -131,6 +131,8 @@ class ShardedSpMM:
             self.local_spmm = local_spmm if local_spmm is not None else self._planned_spmm()
         overlap = dim_chunks > 1 or exchange in ("pipelined", "needed_pipelined")
         self._side = torch.cuda.Stream() if (self.device.type == "cuda" and overlap) else None
+        self._pull_streams = ([torch.cuda.Stream() for _ in range(min(3, world - 1))]
+                              if (self._side is not None and transport == "copy_engine") else [])
 
     def _plan_row_chunks(self, cols_global):
         """Set-up of the pipelined exchange: the receive buffer is [row_chunks][world][chunk_rows]
@@ -300,10 +302,18 @@ class ShardedSpMM:
             if B_shard.data_ptr() != src.data_ptr():
                 src[:rows].copy_(B_shard)
             dist.all_reduce(fence, group=self.group)  # every block is in place
+            # Pulls from different peers go to different streams, so several copy engines (and
+            # NVLink paths) are busy at once; a chunk is complete when all of them are.
+            lanes = [self._side] + self._pull_streams
+            for st in self._pull_streams:
+                st.wait_stream(self._side)
             for kk in range(K):
                 for i in range(W):
                     q = (self.rank + i) % W  # own chunk first, then the peers round-robin
-                    full[(kk * W + q) * cr: (kk * W + q + 1) * cr].copy_(peers[q][kk * cr: (kk + 1) * cr])
+                    with torch.cuda.stream(lanes[i % len(lanes)]):
+                        full[(kk * W + q) * cr: (kk * W + q + 1) * cr].copy_(peers[q][kk * cr: (kk + 1) * cr])
+                for st in self._pull_streams:
+                    self._side.wait_stream(st)
                 ev = torch.cuda.Event()
                 ev.record(self._side)
                 events.append(ev)
