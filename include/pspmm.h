@@ -123,11 +123,15 @@ PSPMM_API int pspmm_sddmm_csr(const int32_t *rowPtr, const int32_t *colIdx, cons
  * Block form: out[k*V+u] = <A[V*row(k)+u, :], B[colIdx[k], :]> where val[k*V+u] != 0, and 0
  * elsewhere (the stored values act as the mask).  Stands in for bcsr_sddmm /
  * bcsr_split_sddmm (SDDMM/sddmm.cpp:119-219 -> sddmm_kernel.cu:248-351, 1059-1287) with
- * V = 2 and vec_sddmm / vec_split_sddmm (sddmm.cpp:221-336) with V = 3.
+ * V = 2 and vec_sddmm / vec_split_sddmm (sddmm.cpp:221-336) with V = 3.  n_rows_A is the
+ * number of rows A really has, at least V*(n_blk_rows-1)+1 (PSPMM_E_ARG below that): when the row
+ * count of the matrix is not a multiple of V the last block-row has lanes without a row of A,
+ * their (masked) results are zero and nothing is read past row n_rows_A-1.  (The reference's
+ * kernels read those rows; its own callers pad A, PCSR.py:322-325.)
  */
 PSPMM_API int pspmm_sddmm_bcsr(const int32_t *rowPtr_b, const int32_t *colIdx, const float *val, int32_t V,
-                     const float *A, const float *B, float *out, int64_t n_blk_rows, int64_t nblk,
-                     int32_t dim, int64_t ldA, int64_t ldB, const pspmm_cfg *cfg,
+                     const float *A, const float *B, float *out, int64_t n_blk_rows, int64_t n_rows_A,
+                     int64_t nblk, int32_t dim, int64_t ldA, int64_t ldB, const pspmm_cfg *cfg,
                      const int32_t *rowPtr_b_split, const int32_t *target_row, int64_t n_seg,
                      void *stream);
 
@@ -156,7 +160,10 @@ PSPMM_API int pspmm_split_csr(const int32_t *rowPtr, int64_t n_rows, int32_t gra
  * need scratch memory for per-tile offsets: pspmm_split_device_scratch_bytes() tells how much
  * for a row count, the caller provides it (8-byte aligned device memory).
  * pspmm_split_count_device copies the piece count back and therefore synchronises `stream`;
- * pspmm_split_csr_device only enqueues work.
+ * pspmm_split_csr_device only enqueues work, so it cannot return an error for an n_seg that is
+ * not the piece count of this rowPtr and granularity: in that case nothing is written outside
+ * the arrays and rowPtr_split[0] becomes -1 instead of 0, which the caller can test once the
+ * stream has drained (the _static variant below behaves the same).
  */
 PSPMM_API int pspmm_split_device_scratch_bytes(int64_t n_rows, size_t *bytes);
 PSPMM_API int pspmm_split_count_device(const int32_t *rowPtr, int64_t n_rows, int32_t granularity,
@@ -208,6 +215,30 @@ PSPMM_API int pspmm_agnn_fused_csr(const int32_t *rowPtr, const int32_t *colIdx,
                                    int32_t vec_width, int32_t lanes_per_row, int32_t batch,
                                    const int32_t *rowPtr_split, const int32_t *target_row, int64_t n_seg,
                                    void *scratch, size_t scratch_bytes, void *stream);
+
+/*
+ * Exchange step of a row-sharded SpMM across GPUs (it has no counterpart in the reference, which
+ * runs on one GPU): copy n rows of a dense operand that is spread over several blocks of memory
+ * into the compact buffer dst[n, dim].  Row j of dst is row rows[j] of block s, where s is the
+ * source with first[s] <= j < first[s+1] (the list is grouped by source; first[0] = 0,
+ * first[n_src] = n).  The blocks are device pointers valid in this process: memory of the current
+ * GPU, or another GPU's memory mapped here (peer access over NVLink), read with plain 16-byte
+ * loads.  The kernel waits on nothing: the caller orders it after the producers of the blocks and
+ * keeps the blocks unchanged until it has finished (one barrier across the ranks on each side).
+ * `rotate` (0 <= rotate < n) is the list position the copy starts from, wrapping round: give every
+ * rank a different owner's first[] so that the ranks do not read one owner all at once.  `ctas`
+ * bounds the thread blocks used (0 = 64), so the copy can run beside a compute kernel.
+ * dim, ld_src and ld_dst must be multiples of 4, every base and dst 16-byte aligned.
+ */
+#define PSPMM_MAX_ROW_SOURCES 16
+typedef struct pspmm_row_sources {
+    const float *base[PSPMM_MAX_ROW_SOURCES];
+    int64_t first[PSPMM_MAX_ROW_SOURCES + 1];
+    int32_t n_src;
+} pspmm_row_sources;
+PSPMM_API int pspmm_pull_rows(const pspmm_row_sources *sources, const int32_t *rows, int64_t n, float *dst,
+                              int32_t dim, int64_t ld_src, int64_t ld_dst, int64_t rotate, int32_t ctas,
+                              void *stream);
 
 /*
  * Host-side CSR -> V x 1 block CSR, laid out exactly as scipy's tobsr((V,1)) (which the
@@ -275,7 +306,9 @@ PSPMM_API int pspmm_csr_file_read(const char *path, int32_t *rowPtr, int32_t *co
  * Timing loops.  Stand in for the *_spmm_profile / *_sddmm_profile functions
  * (SpMM/SpMM.cpp:482-889 -> SpMM_kernel.cu:564-1155; SDDMM/sddmm.cpp:338-661): `warmup`
  * untimed launches, then `iters` back-to-back launches between two CUDA events on `stream`;
- * *ms_per_iter receives the mean.  V = 1 selects the CSR kernels, V = 2 / 3 the block ones.
+ * *ms_per_iter receives the mean.  V = 1 selects the CSR kernels, V = 2 / 3 the block ones
+ * (n_rows then counts block-rows; n_rows_A of pspmm_profile_sddmm is the row count of A as in
+ * pspmm_sddmm_bcsr and is ignored for V = 1).
  */
 PSPMM_API int pspmm_profile_spmm(const int32_t *rowPtr, const int32_t *colIdx, const float *val, int32_t V,
                        const float *B, float *C, int64_t n_rows, int64_t n_cols, int64_t nnz,
@@ -283,8 +316,8 @@ PSPMM_API int pspmm_profile_spmm(const int32_t *rowPtr, const int32_t *colIdx, c
                        const int32_t *rowPtr_split, const int32_t *target_row, int64_t n_seg,
                        int32_t warmup, int32_t iters, float *ms_per_iter, void *stream);
 PSPMM_API int pspmm_profile_sddmm(const int32_t *rowPtr, const int32_t *colIdx, const float *val, int32_t V,
-                        const float *A, const float *B, float *out, int64_t n_rows, int64_t nnz,
-                        int32_t dim, int64_t ldA, int64_t ldB, const pspmm_cfg *cfg,
+                        const float *A, const float *B, float *out, int64_t n_rows, int64_t n_rows_A,
+                        int64_t nnz, int32_t dim, int64_t ldA, int64_t ldB, const pspmm_cfg *cfg,
                         const int32_t *rowPtr_split, const int32_t *target_row, int64_t n_seg,
                         int32_t warmup, int32_t iters, float *ms_per_iter, void *stream);
 

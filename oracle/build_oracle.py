@@ -43,7 +43,9 @@ import sys
 import sysconfig
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF_ROOT = os.environ.get("PSPMM_REFERENCE_ROOT", os.path.join(os.sep, "root", "reference"))
+# The reference checkout: PSPMM_REFERENCE_ROOT, else a directory named "reference" beside this
+# repository's own directory.  Where neither exists everything built from it is skipped.
+REF_ROOT = os.environ.get("PSPMM_REFERENCE_ROOT") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
 REF_OUT = os.path.join(HERE, "_ref")
 
 
@@ -205,7 +207,41 @@ def load_ref():
     return mod
 
 
+# The reference's Python layers, run unmodified on top of the drop-in extension modules by
+# tests/test_gpu_reference_python.py.  They cannot be imported from the reference checkout on a
+# machine that does not have it, so they are staged (copied as they are, never edited, never
+# committed: the directory is git-ignored like oracle/_ref) next to the other reference-derived
+# artefacts; the staging directory travels with the tree.
+PY_STAGE = os.path.join(os.path.dirname(HERE), "baseline", "_ref")
+# (GNN.py parses the command line when imported, so it cannot be used as a module and is not staged)
+_PY_FILES = ("PCSR.py", "SDDMM.py", "gnn_conv.py", "graph_input.py", "verification.py", "decider.py")
+_PY_DATA = (os.path.join("toy_dataset", "pubmed.mtx"),)
+
+
+def stage_reference_python(force=False):
+    """Copy the reference's Python layers and its toy matrix into baseline/_ref (returns the
+    directory, or None when the reference checkout is absent)."""
+    if not ref_available():
+        return None
+    import shutil
+
+    for rel in _PY_FILES + _PY_DATA:
+        src, dst = os.path.join(REF_ROOT, rel), os.path.join(PY_STAGE, rel)
+        if not os.path.isfile(src):
+            continue
+        if force or not os.path.exists(dst) or os.path.getmtime(dst) < os.path.getmtime(src):
+            os.makedirs(os.path.dirname(dst), exist_ok=True)
+            shutil.copyfile(src, dst)
+    return PY_STAGE
+
+
+def staged_reference_python():
+    """The staging directory when it holds the reference's layers, else None."""
+    return PY_STAGE if os.path.isfile(os.path.join(PY_STAGE, "PCSR.py")) else None
+
+
 if __name__ == "__main__":
+    print(stage_reference_python(force="--force" in sys.argv))
     print(build_oracle(force="--force" in sys.argv))
     print(build_ref(force="--force" in sys.argv))
     print(build_ref_sddmm(force="--force" in sys.argv))

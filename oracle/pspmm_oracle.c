@@ -11,7 +11,7 @@
  * Every function names the reference location (path within the reference
  * project : lines) whose behaviour it follows.
  *
- * Build: see oracle/Makefile (gcc -O2 -fopenmp -shared -fPIC).
+ * Build: oracle/build_oracle.py::build_oracle (gcc -O2 -fopenmp -shared -fPIC).
  */
 #include <stdint.h>
 #include <stdlib.h>

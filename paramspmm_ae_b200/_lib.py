@@ -49,6 +49,15 @@ class CsrFileInfo(ctypes.Structure):
                 ("source_mtime_ns", _i64)]
 
 
+MAX_ROW_SOURCES = 16
+
+
+class RowSources(ctypes.Structure):
+    """Mirror of ``pspmm_row_sources``."""
+
+    _fields_ = [("base", _vp * MAX_ROW_SOURCES), ("first", _i64 * (MAX_ROW_SOURCES + 1)), ("n_src", _i32)]
+
+
 class PspmmError(RuntimeError):
     def __init__(self, code, text):
         super().__init__("libpspmm: %s (code %d)" % (text, code))
@@ -66,7 +75,7 @@ _SIGNATURES = {
                         _vp, _vp, _i64, _vp],
     "pspmm_sddmm_csr": [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i32, _i64, _i64, _cfgp, _vp, _vp, _i64,
                         _vp],
-    "pspmm_sddmm_bcsr": [_vp, _vp, _vp, _i32, _vp, _vp, _vp, _i64, _i64, _i32, _i64, _i64, _cfgp,
+    "pspmm_sddmm_bcsr": [_vp, _vp, _vp, _i32, _vp, _vp, _vp, _i64, _i64, _i64, _i32, _i64, _i64, _cfgp,
                          _vp, _vp, _i64, _vp],
     "pspmm_genmask": [_vp, _vp, _vp, _i64, _i64, _i64, _vp, _vp],
     "pspmm_split_count": [_vp, _i64, _i32, ctypes.POINTER(_i64)],
@@ -78,6 +87,7 @@ _SIGNATURES = {
     "pspmm_agnn_scratch_bytes": [_i64, _i32, ctypes.POINTER(ctypes.c_size_t)],
     "pspmm_agnn_fused_csr": [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i32, _i64, _i64, _i64, ctypes.c_float, _i32,
                              _i32, _i32, _i32, _vp, _vp, _i64, _vp, ctypes.c_size_t, _vp],
+    "pspmm_pull_rows": [ctypes.POINTER(RowSources), _vp, _i64, _vp, _i32, _i64, _i64, _i64, _i32, _vp],
     "pspmm_bcsr_count": [_vp, _vp, _i64, _i64, _i32, _vp, ctypes.POINTER(_i64)],
     "pspmm_bcsr_fill": [_vp, _vp, _vp, _i64, _i64, _i32, _vp, _vp, _vp],
     "pspmm_mtx_info_read": [ctypes.c_char_p, ctypes.POINTER(MtxInfo)],
@@ -87,7 +97,7 @@ _SIGNATURES = {
     "pspmm_csr_file_read": [ctypes.c_char_p, _vp, _vp, _vp, _i64, _i64, _i32],
     "pspmm_profile_spmm": [_vp, _vp, _vp, _i32, _vp, _vp, _i64, _i64, _i64, _i32, _i64, _i64, _cfgp,
                            _vp, _vp, _i64, _i32, _i32, ctypes.POINTER(ctypes.c_float), _vp],
-    "pspmm_profile_sddmm": [_vp, _vp, _vp, _i32, _vp, _vp, _vp, _i64, _i64, _i32, _i64, _i64, _cfgp,
+    "pspmm_profile_sddmm": [_vp, _vp, _vp, _i32, _vp, _vp, _vp, _i64, _i64, _i64, _i32, _i64, _i64, _cfgp,
                             _vp, _vp, _i64, _i32, _i32, ctypes.POINTER(ctypes.c_float), _vp],
 }
 EXPORTED = ["pspmm_version", "pspmm_strerror", "pspmm_last_cuda_error"] + list(_SIGNATURES)

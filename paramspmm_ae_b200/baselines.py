@@ -192,3 +192,30 @@ def gespmm_time_ms(X, rowPtr, colIdx, val, warmup=PROFILE_WARMUP, iters=PROFILE_
 
 def gespmm_profile(X, rowPtr, colIdx, val):
     return _gflops(val.shape[0], X.shape[1], gespmm_time_ms(X, rowPtr, colIdx, val))
+
+
+def gather_ceiling_ms(colIdx, B, run=64, warmup=3, iters=10):
+    """Milliseconds the GPU needs just to fetch B[colIdx[k]] for every k (8 row loads in flight per
+    lane, nothing else): the floor of any row-major-gather SpMM over this column stream and dense
+    operand (see csrc/baselines.cu).  dim must be 16, 32, 64, 128 or 256."""
+    _check_cuda(colIdx, "colIdx", torch.int32, 1)
+    _check_cuda(B, "B", torch.float32, 2)
+    nnz, dim = colIdx.shape[0], B.shape[1]
+    h = _bl()
+    h.pspmm_baselines_gather_sink_bytes.restype = ctypes.c_int64
+    nbytes = h.pspmm_baselines_gather_sink_bytes(ctypes.c_int64(nnz), ctypes.c_int32(dim), ctypes.c_int32(run))
+    sink = torch.empty(nbytes // 4, dtype=torch.float32, device=B.device)
+
+    def go():
+        _ok(h.pspmm_baselines_gather_ceiling(_ptr(colIdx), ctypes.c_int64(nnz), _ptr(B), ctypes.c_int32(dim),
+                                             ctypes.c_int64(B.stride(0)), ctypes.c_int32(run), _ptr(sink), _stream()))
+
+    for _ in range(warmup):
+        go()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        go()
+    e1.record()
+    e1.synchronize()
+    return e0.elapsed_time(e1) / iters

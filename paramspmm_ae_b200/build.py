@@ -26,9 +26,8 @@ NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC,-fopenmp,-f
               "-cudart", "shared", "-I", os.path.join(ROOT, "include"), "-I", CSRC]
 
 CORE_SOURCES = ["pspmm_api.cu", "spmm_vw4.cu", "spmm_vw4_acc.cu", "spmm_vw2.cu", "spmm_vw1.cu", "sddmm_vw4.cu",
-                "sddmm_vw2.cu", "sddmm_vw1.cu", "host_builders.cpp", "mtx_io.cpp", "device_builders.cu", "agnn_fused.cu"]
+                "sddmm_vw2.cu", "sddmm_vw1.cu", "host_builders.cpp", "mtx_io.cpp", "device_builders.cu", "agnn_fused.cu", "exchange.cu"]
 BASELINE_SOURCES = ["baselines.cu"]
-PROBE = os.path.join(PKG, "gather_probe")  # stand-alone microbenchmark, see csrc/gather_probe.cu
 
 
 def _deps(src):
@@ -81,12 +80,6 @@ def build(force=False, verbose=False, baselines=True):
         _link(core_objs, LIB, [])
     if base_objs and (force or _stale(BASELINES_LIB, base_objs)):
         _link(base_objs, BASELINES_LIB, ["-lcusparse"])
-    probe_src = os.path.join(CSRC, "gather_probe.cu")
-    if os.path.exists(probe_src) and (force or _stale(PROBE, [probe_src])):
-        p = subprocess.run([NVCC] + ARCH + ["-O3", "-std=c++17", "-lineinfo", probe_src, "-o", PROBE],
-                           stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
-        if p.returncode != 0:
-            raise RuntimeError("nvcc failed on gather_probe.cu:\n%s" % p.stdout)
     if verbose:
         print("\n".join(logs))
     return LIB

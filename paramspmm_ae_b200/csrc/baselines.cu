@@ -208,10 +208,96 @@ PB_API int pspmm_baselines_gespmm(const int32_t *rowPtr, const int32_t *colIdx, 
     cudaStream_t st = (cudaStream_t)stream;
     const dim3 block(32, 8);
     const unsigned gx = (unsigned)((n_rows + 7) / 8);
-    if (dim <= 32)
+    // Coarsening as the reference's wrapper picks it (SpMM/Baseline_kernel.cu:763): 1 below 128
+    // dense columns, 2 from 128, 4 from 512.
+    if (dim < 128)
         gespmm_like_kernel<1><<<dim3(gx, (dim + 31) / 32), block, 0, st>>>(rowPtr, colIdx, val, B, C, n_rows, dim, ldB, ldC);
-    else
+    else if (dim < 512)
         gespmm_like_kernel<2><<<dim3(gx, (dim + 63) / 64), block, 0, st>>>(rowPtr, colIdx, val, B, C, n_rows, dim, ldB, ldC);
+    else
+        gespmm_like_kernel<4><<<dim3(gx, (dim + 127) / 128), block, 0, st>>>(rowPtr, colIdx, val, B, C, n_rows, dim, ldB, ldC);
+    PB_CUDA(cudaGetLastError());
+    return 0;
+}
+
+// ----------------------------------------------------------------------------- gather ceiling
+// How fast can ANY kernel on this GPU fetch the rows B[colIdx[k]] for the whole column stream of
+// a matrix?  This measures it: lane groups of dim/4 lanes (one 16-byte slice of a row per lane)
+// walk contiguous runs of the stream with 8 independent row loads in flight per lane and fold
+// what they load into one float4 per lane, written once at the end so that the loads cannot be
+// dropped.  No values, no row pointers, no output rows: the time of this kernel is a lower bound
+// for a row-major-gather SpMM over the same stream and the same dense operand, and
+// 4 * dim * nnz / time is the gather rate the memory system delivers for it (L2 hits included).
+// It is a measuring stick: nothing in libpspmm uses it.
+template <int LPR>
+__global__ void __launch_bounds__(256) gather_ceiling_kernel(const int32_t *__restrict__ colIdx, int64_t nnz,
+                                                             const float *__restrict__ B, int64_t ldB,
+                                                             int run, float4 *__restrict__ sink)
+{
+    const int gl = threadIdx.x % LPR;
+    const int64_t group = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) / LPR;
+    const int64_t k0 = group * run;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    const float *base = B + gl * 4;
+    int64_t k = k0;
+    const int64_t kend = k0 + run < nnz ? k0 + run : nnz;
+    for (; k + 8 <= kend; k += 8) {
+        // one 32-byte sector of column ids per 8 entries, read by every lane of the group (broadcast)
+        const int4 c0 = __ldg(reinterpret_cast<const int4 *>(colIdx + k));
+        const int4 c1 = __ldg(reinterpret_cast<const int4 *>(colIdx + k + 4));
+        const int c[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+        float4 x[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+            x[u] = __ldg(reinterpret_cast<const float4 *>(base + (int64_t)c[u] * ldB));
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            acc.x += x[u].x; acc.y += x[u].y; acc.z += x[u].z; acc.w += x[u].w;
+        }
+    }
+    for (; k < kend; ++k) {
+        const float4 x = __ldg(reinterpret_cast<const float4 *>(base + (int64_t)__ldg(colIdx + k) * ldB));
+        acc.x += x.x; acc.y += x.y; acc.z += x.z; acc.w += x.w;
+    }
+    if (k0 < nnz)
+        sink[(int64_t)blockIdx.x * blockDim.x + threadIdx.x] = acc;
+}
+
+// dim: a multiple of 4 with dim/4 in {4, 8, 16, 32, 64} (64: two passes of 32 lanes over the two
+// halves of a row).  run: entries per lane group (a multiple of 8, e.g. 64).  sink: device buffer of
+// pspmm_baselines_gather_sink_bytes(nnz, dim, run) bytes.  colIdx must be 16-byte aligned.
+PB_API int64_t pspmm_baselines_gather_sink_bytes(int64_t nnz, int32_t dim, int32_t run)
+{
+    const int lpr = dim / 4 > 32 ? 32 : dim / 4;
+    const int64_t groups = (nnz + run - 1) / run;
+    const int64_t threads = (groups * lpr + 255) / 256 * 256;
+    return threads * 16;
+}
+
+PB_API int pspmm_baselines_gather_ceiling(const int32_t *colIdx, int64_t nnz, const float *B, int32_t dim,
+                                          int64_t ldB, int32_t run, void *sink, void *stream)
+{
+    if (!colIdx || !B || !sink || nnz <= 0 || dim % 4 != 0 || run <= 0 || run % 8 != 0 ||
+        ((uintptr_t)colIdx) % 16 != 0 || ((uintptr_t)B) % 16 != 0 || ldB % 4 != 0)
+        return -1;
+    const int nvec = dim / 4;
+    if (nvec != 4 && nvec != 8 && nvec != 16 && nvec != 32 && nvec != 64)
+        return -1;
+    cudaStream_t st = (cudaStream_t)stream;
+    const int lpr = nvec > 32 ? 32 : nvec;
+    const int64_t groups = (nnz + run - 1) / run;
+    const unsigned grid = (unsigned)((groups * lpr + 255) / 256);
+    for (int half = 0; half < (nvec > 32 ? 2 : 1); ++half) {
+        const float *b = B + half * 128;
+        if (lpr == 4)
+            gather_ceiling_kernel<4><<<grid, 256, 0, st>>>(colIdx, nnz, b, ldB, run, (float4 *)sink);
+        else if (lpr == 8)
+            gather_ceiling_kernel<8><<<grid, 256, 0, st>>>(colIdx, nnz, b, ldB, run, (float4 *)sink);
+        else if (lpr == 16)
+            gather_ceiling_kernel<16><<<grid, 256, 0, st>>>(colIdx, nnz, b, ldB, run, (float4 *)sink);
+        else
+            gather_ceiling_kernel<32><<<grid, 256, 0, st>>>(colIdx, nnz, b, ldB, run, (float4 *)sink);
+    }
     PB_CUDA(cudaGetLastError());
     return 0;
 }

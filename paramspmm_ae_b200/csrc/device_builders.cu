@@ -19,7 +19,8 @@ __device__ __forceinline__ int pieces_of(const int32_t *rowPtr, int64_t r, int64
     if (r >= n_rows)
         return 0;
     const int len = rowPtr[r + 1] - rowPtr[r];
-    return len > 0 ? (len + gran - 1) / gran : 0;
+    // 64-bit: len + gran overflows int32 for a granularity near INT32_MAX
+    return len > 0 ? (int)(((int64_t)len + gran - 1) / gran) : 0;
 }
 
 // CTA-wide inclusive scan of one int per thread (blockDim.x == TILE); returns the inclusive sum.
@@ -118,14 +119,14 @@ __global__ void __launch_bounds__(TILE) fill_split(const int32_t *__restrict__ r
     const int mine = pieces_of(rowPtr, r, n_rows, gran);
     const int incl = block_inclusive_scan(mine, warp_sums);
     int64_t s = tile_off[blockIdx.x] + (incl - mine);
-    if (r == 0)
-        rowPtr_split[0] = 0;
+    if (r == 0)  // 0, or -1 when the caller's n_seg is not this partition's piece count
+        rowPtr_split[0] = (tile_off[gridDim.x] == n_seg) ? 0 : -1;
     if (mine > 0) {
-        const int end = rowPtr[r + 1];
-        for (int at = rowPtr[r]; at < end; at += gran, ++s) {
+        const int64_t end = rowPtr[r + 1];
+        for (int64_t at = rowPtr[r]; at < end; at += gran, ++s) {
             if (s < n_seg) {  // a wrong n_seg from the caller must not write out of bounds
                 target_row[s] = (int32_t)r;
-                rowPtr_split[s + 1] = at + gran < end ? at + gran : end;
+                rowPtr_split[s + 1] = (int32_t)(at + gran < end ? at + gran : end);
             }
         }
     }

@@ -3,6 +3,7 @@
 #include <stdint.h>
 
 #include <algorithm>
+#include <new>
 #include <vector>
 
 #ifdef _OPENMP
@@ -86,10 +87,14 @@ extern "C" int pspmm_split_csr(const int32_t *rowPtr, int64_t n_rows, int32_t gr
         return PSPMM_E_RANGE;
     const int64_t gran = granularity;
     std::vector<int64_t> off;
-    prefix_counts(n_rows, off, [&](int64_t r) {
-        const int64_t len = (int64_t)rowPtr[r + 1] - rowPtr[r];
-        return len > 0 ? (len + gran - 1) / gran : (int64_t)0;
-    });
+    try {
+        prefix_counts(n_rows, off, [&](int64_t r) {
+            const int64_t len = (int64_t)rowPtr[r + 1] - rowPtr[r];
+            return len > 0 ? (len + gran - 1) / gran : (int64_t)0;
+        });
+    } catch (const std::bad_alloc &) {
+        return PSPMM_E_NOMEM;
+    }
     if (off[(size_t)n_rows] != n_seg)
         return PSPMM_E_ARG;  // caller's piece count does not match this rowPtr / granularity
     rowPtr_split[0] = 0;
@@ -107,27 +112,35 @@ extern "C" int pspmm_split_csr(const int32_t *rowPtr, int64_t n_rows, int32_t gr
 
 // Blocks of one block-row in first-encounter order.  `slot` is a per-thread array of n_cols
 // entries, all -1 on entry and restored to -1 on exit.  With cols/vals null it only counts.
+// `room` bounds the blocks that may be written (the caller's rowPtr_b says how many the
+// block-row has); the return value is the number of blocks met, which exceeds `room` when the
+// inputs disagree, or -1 when a column id lies outside [0, n_cols).
 static int64_t walk_block_row(const int32_t *rowPtr, const int32_t *colIdx, const float *val,
-                              int64_t n_rows, int32_t V, int64_t br, int32_t *slot,
-                              int32_t *cols, float *vals)
+                              int64_t n_rows, int64_t n_cols, int32_t V, int64_t br, int32_t *slot,
+                              int32_t *cols, float *vals, int64_t room)
 {
     int64_t made = 0;
-    for (int32_t v = 0; v < V; ++v) {
+    bool bad_col = false;
+    for (int32_t v = 0; v < V && !bad_col; ++v) {
         const int64_t r = br * V + v;
         if (r >= n_rows)
             break;
         for (int32_t k = rowPtr[r]; k < rowPtr[r + 1]; ++k) {
             const int32_t c = colIdx[k];
+            if (c < 0 || c >= n_cols) {
+                bad_col = true;
+                break;
+            }
             if (slot[c] < 0) {
                 slot[c] = (int32_t)made;
-                if (cols) {
+                if (cols && made < room) {
                     cols[made] = c;
                     for (int32_t u = 0; u < V; ++u)
                         vals[made * V + u] = 0.0f;
                 }
                 ++made;
             }
-            if (cols)
+            if (cols && slot[c] < room)
                 vals[(int64_t)slot[c] * V + v] += val[k];
         }
     }
@@ -135,10 +148,32 @@ static int64_t walk_block_row(const int32_t *rowPtr, const int32_t *colIdx, cons
         const int64_t r = br * V + v;
         if (r >= n_rows)
             break;
-        for (int32_t k = rowPtr[r]; k < rowPtr[r + 1]; ++k)
-            slot[colIdx[k]] = -1;
+        for (int32_t k = rowPtr[r]; k < rowPtr[r + 1]; ++k) {
+            const int32_t c = colIdx[k];
+            if (c >= 0 && c < n_cols)
+                slot[c] = -1;
+        }
     }
-    return made;
+    return bad_col ? -1 : made;
+}
+
+// One column -> slot array per worker thread, allocated before the parallel region so that an
+// allocation failure surfaces as an exception in the calling thread.
+static std::vector<std::vector<int32_t>> make_slots(int64_t n_cols)
+{
+    std::vector<std::vector<int32_t>> slots((size_t)max_threads());
+    for (auto &s : slots)
+        s.assign((size_t)std::max<int64_t>(n_cols, 1), -1);
+    return slots;
+}
+
+static int this_thread()
+{
+#ifdef _OPENMP
+    return omp_get_thread_num();
+#else
+    return 0;
+#endif
 }
 
 extern "C" int pspmm_bcsr_count(const int32_t *rowPtr, const int32_t *colIdx, int64_t n_rows,
@@ -148,25 +183,29 @@ extern "C" int pspmm_bcsr_count(const int32_t *rowPtr, const int32_t *colIdx, in
         return PSPMM_E_ARG;
     if (n_rows > 0 && rowPtr[n_rows] > 0 && !colIdx)
         return PSPMM_E_ARG;
-    const int64_t nbr = (n_rows + V - 1) / V;
-    std::vector<int64_t> cnt((size_t)nbr, 0);
-#pragma omp parallel
-    {
-        std::vector<int32_t> slot((size_t)std::max<int64_t>(n_cols, 1), -1);
-#pragma omp for schedule(dynamic, 1024)
+    try {
+        const int64_t nbr = (n_rows + V - 1) / V;
+        std::vector<int64_t> cnt((size_t)nbr, 0);
+        auto slots = make_slots(n_cols);
+        const int T = (int)slots.size();
+#pragma omp parallel for schedule(dynamic, 1024) num_threads(T)
         for (int64_t br = 0; br < nbr; ++br)
-            cnt[(size_t)br] = walk_block_row(rowPtr, colIdx, nullptr, n_rows, V, br, slot.data(),
-                                             nullptr, nullptr);
+            cnt[(size_t)br] = walk_block_row(rowPtr, colIdx, nullptr, n_rows, n_cols, V, br,
+                                             slots[(size_t)this_thread()].data(), nullptr, nullptr, 0);
+        int64_t run = 0;
+        rowPtr_b[0] = 0;
+        for (int64_t br = 0; br < nbr; ++br) {
+            if (cnt[(size_t)br] < 0)
+                return PSPMM_E_ARG;  // a column id outside [0, n_cols)
+            run += cnt[(size_t)br];
+            if (run > INT32_MAX)
+                return PSPMM_E_RANGE;
+            rowPtr_b[br + 1] = (int32_t)run;
+        }
+        *nblk = run;
+    } catch (const std::bad_alloc &) {
+        return PSPMM_E_NOMEM;
     }
-    int64_t run = 0;
-    rowPtr_b[0] = 0;
-    for (int64_t br = 0; br < nbr; ++br) {
-        run += cnt[(size_t)br];
-        if (run > INT32_MAX)
-            return PSPMM_E_RANGE;
-        rowPtr_b[br + 1] = (int32_t)run;
-    }
-    *nblk = run;
     return PSPMM_OK;
 }
 
@@ -180,19 +219,24 @@ extern "C" int pspmm_bcsr_fill(const int32_t *rowPtr, const int32_t *colIdx, con
     if (nbr > 0 && rowPtr_b[nbr] > 0 && (!colIdx || !val || !colIdx_b || !val_b))
         return PSPMM_E_ARG;
     int bad = 0;
-#pragma omp parallel
-    {
-        std::vector<int32_t> slot((size_t)std::max<int64_t>(n_cols, 1), -1);
-#pragma omp for schedule(dynamic, 1024)
+    try {
+        auto slots = make_slots(n_cols);
+        const int T = (int)slots.size();
+#pragma omp parallel for schedule(dynamic, 1024) num_threads(T)
         for (int64_t br = 0; br < nbr; ++br) {
             const int64_t at = rowPtr_b[br];
-            const int64_t made = walk_block_row(rowPtr, colIdx, val, n_rows, V, br, slot.data(),
-                                                colIdx_b + at, val_b + at * V);
-            if (made != (int64_t)rowPtr_b[br + 1] - at) {
+            const int64_t room = (int64_t)rowPtr_b[br + 1] - at;
+            // never more than `room` blocks are written, whatever the row pointers claim
+            const int64_t made = walk_block_row(rowPtr, colIdx, val, n_rows, n_cols, V, br,
+                                                slots[(size_t)this_thread()].data(), colIdx_b + at,
+                                                val_b + at * V, room < 0 ? 0 : room);
+            if (made != room) {
 #pragma omp atomic write
                 bad = 1;
             }
         }
+    } catch (const std::bad_alloc &) {
+        return PSPMM_E_NOMEM;
     }
     return bad ? PSPMM_E_ARG : PSPMM_OK;
 }

@@ -416,7 +416,7 @@ extern "C" int pspmm_spmm_bcsr(const int32_t *rowPtr_b, const int32_t *colIdx, c
 // ----------------------------------------------------------------------------- SDDMM
 static int sddmm_launch(const int32_t *segPtr, const int32_t *target_row, int64_t n_seg,
                         const int32_t *colIdx, const float *val, int V, const float *A,
-                        const float *B, float *out, int32_t dim, int64_t ldA, int64_t ldB,
+                        const float *B, float *out, int64_t n_rows_A, int32_t dim, int64_t ldA, int64_t ldB,
                         const pspmm_cfg *cfg, cudaStream_t st)
 {
     int rc = pspmm_validate_cfg(cfg, true);
@@ -437,6 +437,7 @@ static int sddmm_launch(const int32_t *segPtr, const int32_t *target_row, int64_
     a.B = B;
     a.out = out;
     a.n_seg = n_seg;
+    a.n_rows_A = n_rows_A;
     a.ldA = ldA;
     a.ldB = ldB;
     a.nvec = dim / s.vw;
@@ -481,12 +482,12 @@ extern "C" int pspmm_sddmm_csr(const int32_t *rowPtr, const int32_t *colIdx, con
     if (!colIdx || !out)
         return PSPMM_E_ARG;
     return sddmm_launch(split ? rowPtr_split : rowPtr, target_row, split ? n_seg : n_rows, colIdx,
-                        nullptr, 1, A, B, out, dim, ldA, ldB, cfg, (cudaStream_t)stream);
+                        nullptr, 1, A, B, out, n_rows, dim, ldA, ldB, cfg, (cudaStream_t)stream);
 }
 
 extern "C" int pspmm_sddmm_bcsr(const int32_t *rowPtr_b, const int32_t *colIdx, const float *val,
                                 int32_t V, const float *A, const float *B, float *out,
-                                int64_t n_blk_rows, int64_t nblk, int32_t dim, int64_t ldA,
+                                int64_t n_blk_rows, int64_t n_rows_A, int64_t nblk, int32_t dim, int64_t ldA,
                                 int64_t ldB, const pspmm_cfg *cfg, const int32_t *rowPtr_b_split,
                                 const int32_t *target_row, int64_t n_seg, void *stream)
 {
@@ -495,6 +496,9 @@ extern "C" int pspmm_sddmm_bcsr(const int32_t *rowPtr_b, const int32_t *colIdx, 
     int rc = check_sizes(n_blk_rows * V, 0, nblk * V, dim);
     if (rc)
         return rc;
+    // A may stop inside the last block-row (a row count that is not a multiple of V), not before it.
+    if (n_rows_A < 0 || (n_blk_rows > 0 && n_rows_A <= (n_blk_rows - 1) * V))
+        return PSPMM_E_ARG;
     const bool split = target_row != nullptr || rowPtr_b_split != nullptr;
     if (split && (!rowPtr_b_split || n_seg < 0 || (n_seg > 0 && !target_row)))
         return PSPMM_E_ARG;
@@ -507,7 +511,7 @@ extern "C" int pspmm_sddmm_bcsr(const int32_t *rowPtr_b, const int32_t *colIdx, 
     if (!colIdx || !val || !out)
         return PSPMM_E_ARG;
     return sddmm_launch(split ? rowPtr_b_split : rowPtr_b, target_row,
-                        split ? n_seg : n_blk_rows, colIdx, val, V, A, B, out, dim, ldA, ldB, cfg,
+                        split ? n_seg : n_blk_rows, colIdx, val, V, A, B, out, n_rows_A, dim, ldA, ldB, cfg,
                         (cudaStream_t)stream);
 }
 
@@ -626,7 +630,7 @@ extern "C" int pspmm_profile_spmm(const int32_t *rowPtr, const int32_t *colIdx, 
 
 extern "C" int pspmm_profile_sddmm(const int32_t *rowPtr, const int32_t *colIdx, const float *val,
                                    int32_t V, const float *A, const float *B, float *out,
-                                   int64_t n_rows, int64_t nnz, int32_t dim, int64_t ldA,
+                                   int64_t n_rows, int64_t n_rows_A, int64_t nnz, int32_t dim, int64_t ldA,
                                    int64_t ldB, const pspmm_cfg *cfg, const int32_t *rowPtr_split,
                                    const int32_t *target_row, int64_t n_seg, int32_t warmup,
                                    int32_t iters, float *ms_per_iter, void *stream)
@@ -635,7 +639,7 @@ extern "C" int pspmm_profile_sddmm(const int32_t *rowPtr, const int32_t *colIdx,
         if (V == 1)
             return pspmm_sddmm_csr(rowPtr, colIdx, A, B, out, n_rows, nnz, dim, ldA, ldB, cfg,
                                    rowPtr_split, target_row, n_seg, stream);
-        return pspmm_sddmm_bcsr(rowPtr, colIdx, val, V, A, B, out, n_rows, nnz, dim, ldA, ldB, cfg,
+        return pspmm_sddmm_bcsr(rowPtr, colIdx, val, V, A, B, out, n_rows, n_rows_A, nnz, dim, ldA, ldB, cfg,
                                 rowPtr_split, target_row, n_seg, stream);
     };
     return time_loop(launch, warmup, iters, ms_per_iter, (cudaStream_t)stream);

@@ -47,6 +47,7 @@ struct SddmmArgs {
     const float *B;
     float *out;
     int64_t n_seg;
+    int64_t n_rows_A;  // rows of A that exist: block forms read rows arow*V + w only below this
     int64_t ldA, ldB;
     int32_t nvec;
     int32_t rows_per_group;

@@ -96,7 +96,8 @@ __global__ void __launch_bounds__(512) sddmm_seg_kernel(const SddmmArgs a)
                     voff[cf] = vi * VW;
 #pragma unroll
                     for (int w = 0; w < V; ++w)
-                        av[w][cf] = (live && act[cf])
+                        // (the last block-row of an odd row count has lanes without a row of A)
+                        av[w][cf] = (live && act[cf] && arow * V + w < a.n_rows_A)
                                         ? ldg_vec<VW>(a.A + (arow * V + w) * a.ldA + voff[cf])
                                         : zero_vec<VW>();
                 }

@@ -4,8 +4,8 @@ Same module and autograd-function names, constructor arguments and forward signa
 (gnn_conv.py:13-238 of the reference).  The layer semantics are the reference's:
 
 * GCN   forward  A (H W); backward AG = A G (A itself: the normalised adjacency is symmetric),
-        dH = AG W^T, dW = H^T AG.  Layers that widen their input aggregate first instead,
-        (A H) W, see REORDER_NARROW_FIRST.
+        dH = AG W^T, dW = H^T AG.  With REORDER_NARROW_FIRST (off by default) layers that widen
+        their input aggregate first instead, (A H) W.
 * GIN   forward  (A X) W; backward dW = (A X)^T G, dX = A (G W^T).
 * AGNN  forward  X' = X W, e = SDDMM(X', X') * beta, out = SpMM(e, X'); no edge softmax and no
         row normalisation (the reference has none); the gradient w.r.t. beta follows the
@@ -22,9 +22,13 @@ n_heads = 1
 
 # When a GCN layer widens its input (fan-in < fan-out) the aggregation is cheaper before the
 # projection: A (H W) = (A H) W, and the SpMM then runs at the narrower width.  The reference always
-# aggregates after the projection (SpCONV/SpCONV.h:43-72); results agree to fp32 rounding.  Set to
-# False to keep the reference's order everywhere.
-REORDER_NARROW_FIRST = True
+# aggregates after the projection (SpCONV/SpCONV.h:43-72), and so does this module by default, so
+# that layer outputs and gradients are the reference's up to the summation order inside the SpMM.
+# Setting this to True is an opt-in: results then differ from the reference's by fp32
+# re-association of the two products (both orders are tested against fp64 algebra), the backward
+# keeps A H instead of H, and the operator is looked up under the input width when the caller's
+# dictionary has one for it.
+REORDER_NARROW_FIRST = False
 
 
 def _aggregate(P, X):
@@ -131,7 +135,10 @@ class _Conv(torch.nn.Module):
 
 class GCNConv(_Conv):
     def forward(self, H, spmm_dict):
-        return GCNFunction.apply(H, self.weights, self._operator(spmm_dict))
+        P = self._operator(spmm_dict)
+        if REORDER_NARROW_FIRST and self.weights.size(0) < self.weights.size(1):
+            P = spmm_dict.get(self.weights.size(0), P)  # the aggregation runs at the input width
+        return GCNFunction.apply(H, self.weights, P)
 
 
 class GINConv(_Conv):
@@ -143,6 +150,16 @@ class AGNNConv(_Conv):
     def __init__(self, input_dim, output_dim):
         super().__init__(input_dim, output_dim)
         self.attention_w = torch.nn.Parameter(torch.randn(1, n_heads))
+        self._beta_cache = (None, 0.0)
+
+    def _beta(self):
+        """attention_w as a host float for the fused kernel's by-value argument, read back from the
+        device only when the parameter has changed since the last call (in-place updates bump the
+        tensor's version counter)."""
+        key = (self.attention_w.data_ptr(), self.attention_w._version)
+        if self._beta_cache[0] != key:
+            self._beta_cache = (key, float(self.attention_w.detach().reshape(())))
+        return self._beta_cache[1]
 
     def forward(self, X, spmm_dict, colIdx):
         P = self._operator(spmm_dict)
@@ -152,6 +169,6 @@ class AGNNConv(_Conv):
             from . import ops
             Xp = torch.mm(X, self.weights)
             split = P.target_row is not None
-            return ops.agnn_fused(Xp, Xp, P.rowPtr, P.colIdx, float(self.attention_w.reshape(())), softmax=False,
+            return ops.agnn_fused(Xp, Xp, P.rowPtr, P.colIdx, self._beta(), softmax=False,
                                   target_row=P.target_row, n_out_rows=P.mtx_nodes if split else None)
         return AGNNFunction.apply(X, self.weights, self.attention_w, P, colIdx)

@@ -288,18 +288,21 @@ def _spmm(X, rowPtr, colIdx, val, target_row, V, CF, W):
     _check_legacy(CF, W)
     _spmm_inputs(X, rowPtr, colIdx, val, target_row, V)
     n, dim = X.shape
-    if V == 1:
-        # The reference returns zeros_like(input): one output row per input row.
-        n_out = n
-        out = torch.empty((n, dim), dtype=torch.float32, device=X.device)
-        if target_row is None and rowPtr.shape[0] - 1 != n:
-            raise RuntimeError("rowPtr must have input.size(0)+1 entries")
-    else:
-        padded = (n + V - 1) // V * V  # SpMM/SpMM_kernel.cu:281-282, 427-428
-        n_out = padded // V
-        if target_row is None and rowPtr.shape[0] - 1 != n_out:
-            raise RuntimeError("rowPtr must describe ceil(input.size(0)/%d) block rows" % V)
-        out = torch.empty((padded, dim), dtype=torch.float32, device=X.device)
+    # The reference sizes the output from the dense input, zeros_like(input) for CSR
+    # (SpMM/SpMM_kernel.cu:136) and the input's row count rounded up to a multiple of V for the
+    # block layouts (:281-282, 427-428), and walks as many (block-)rows as the row pointer has.
+    # Its own callers hand in inputs with more rows than the matrix (GNN.py:226-240 pads the
+    # features to an even row count): those extra output rows stay zero.
+    padded = (n + V - 1) // V * V
+    n_out = padded // V
+    out = torch.empty((padded, dim), dtype=torch.float32, device=X.device)
+    if target_row is None:
+        n_seg = rowPtr.shape[0] - 1
+        if n_seg > n_out:
+            raise RuntimeError("rowPtr describes %d (block-)rows, the input only allows %d" % (n_seg, n_out))
+        if n_seg < n_out:
+            out[n_seg * V:].zero_()
+            n_out = n_seg
     return spmm_into(out, X, rowPtr, colIdx, val, target_row, V, n_out, CF, W)
 
 
@@ -420,13 +423,17 @@ def _sddmm(A, B, rowPtr, colIdx, val, target_row, V, CF, W, time_only=False):
     out = torch.empty_like(val)
     cfg = _cfg("sddmm", CF, W, dim, nent, n_seg, V, split)
     null = ctypes.c_void_p(0)
-    n_rows = n_seg if not split else (A.shape[0] // V)
+    # (block-)rows of the pattern; A may stop inside the last block-row when the node count is
+    # not a multiple of V, and the kernel then reads nothing past A's last row
+    n_rows = n_seg if not split else (A.shape[0] + V - 1) // V
+    if A.shape[0] <= (n_rows - 1) * V:
+        raise RuntimeError("A has %d rows, the pattern needs more than %d" % (A.shape[0], (n_rows - 1) * V))
     args_tail = (ctypes.byref(cfg), _ptr(rowPtr) if split else null,
                  _ptr(target_row) if split else null, n_seg if split else 0)
     if time_only:
         ms = ctypes.c_float(0.0)
         check(lib().pspmm_profile_sddmm(null if split else _ptr(rowPtr), _ptr(colIdx), _ptr(val), V,
-                                        _ptr(A), _ptr(B), _ptr(out), n_rows, nent, dim, A.stride(0),
+                                        _ptr(A), _ptr(B), _ptr(out), n_rows, A.shape[0], nent, dim, A.stride(0),
                                         B.stride(0), *args_tail, PROFILE_WARMUP, PROFILE_ITERS,
                                         ctypes.byref(ms), _stream()))
         return ms.value
@@ -436,7 +443,7 @@ def _sddmm(A, B, rowPtr, colIdx, val, target_row, V, CF, W, time_only=False):
                                     *args_tail, _stream()))
     else:
         check(lib().pspmm_sddmm_bcsr(null if split else _ptr(rowPtr), _ptr(colIdx), _ptr(val), V,
-                                     _ptr(A), _ptr(B), _ptr(out), n_rows, nent, dim, A.stride(0),
+                                     _ptr(A), _ptr(B), _ptr(out), n_rows, A.shape[0], nent, dim, A.stride(0),
                                      B.stride(0), *args_tail, _stream()))
     return out
 
@@ -538,6 +545,38 @@ def agnn_fused(A, B, rowPtr, colIdx, beta=1.0, softmax=True, target_row=None, n_
                                      seg_ptr if split else null, _ptr(target_row) if split else null,
                                      n_seg if split else 0, _ptr(scratch) if split else null, sbytes, _stream()))
     return out
+
+
+def pull_rows(dst, sources, first, rows, rotate=0, ctas=0):
+    """dst[j] = sources[s][rows[j]] for first[s] <= j < first[s+1]: gathers rows of a dense operand
+    that lives in several blocks (this GPU's memory or peer-mapped memory of other GPUs) into one
+    compact buffer with a copy kernel that reads the blocks directly (``pspmm_pull_rows``).
+    ``sources``: 2-D float32 CUDA tensors with one row stride; ``first``: len(sources)+1
+    non-decreasing list positions; ``rows``: int32 CUDA tensor of row ids inside the owning block."""
+    if not sources or len(sources) > _lib.MAX_ROW_SOURCES or len(first) != len(sources) + 1:
+        raise RuntimeError("between 1 and %d sources with len(sources)+1 list positions" % _lib.MAX_ROW_SOURCES)
+    _check_cuda(rows, "rows", torch.int32, 1)
+    if dst.dtype != torch.float32 or not dst.is_cuda or dst.dim() != 2 or dst.stride(1) != 1:
+        raise RuntimeError("dst must be a 2-D float32 CUDA tensor with unit column stride")
+    n, dim = dst.shape
+    if rows.shape[0] != n or int(first[-1]) != n:
+        raise RuntimeError("rows and first must describe exactly dst.shape[0] rows")
+    src = _lib.RowSources()
+    ld = None
+    for s, t in enumerate(sources):
+        if t.dtype != torch.float32 or not t.is_cuda or t.dim() != 2 or t.stride(1) != 1 or t.shape[1] != dim:
+            raise RuntimeError("every source must be a float32 CUDA tensor [rows, %d] with unit column stride" % dim)
+        if ld is None:
+            ld = t.stride(0)
+        elif t.stride(0) != ld:
+            raise RuntimeError("all sources must share one row stride")
+        src.base[s] = t.data_ptr()
+    for s, f in enumerate(first):
+        src.first[s] = int(f)
+    src.n_src = len(sources)
+    check(lib().pspmm_pull_rows(ctypes.byref(src), _ptr(rows), n, _ptr(dst), dim, ld, dst.stride(0), int(rotate),
+                                int(ctas), _stream()))
+    return dst
 
 
 def genmask(rowPtr_bcsr, rowPtr, blkval, nnz):

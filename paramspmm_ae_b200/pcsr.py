@@ -32,6 +32,68 @@ _CONV_BWD = {("csr", False): ops.csr_spmm_backward, ("csr", True): ops.csr_split
              ("bcsr", False): ops.bcsr_spmm_backward, ("bcsr", True): ops.bcsr_split_spmm_backward}
 
 
+class _format_spmm(object):
+    """Shared body of the COO and CSC comparator objects (PCSR.py:45-124): device copies of one
+    storage format of the graph's matrix, a result and a timing method over cuSPARSE."""
+
+    label = ""
+
+    def _arrays(self):
+        raise NotImplementedError
+
+    def _input(self, dim, x):
+        if x is None and dim is None:
+            raise ValueError("at least one of x and dim should be given")
+        return torch.ones(self.mtx_nodes, dim, device="cuda") if dim is not None else x.to("cuda")
+
+    def get_spmm_result(self, dim=None, x=None):
+        return self._compute(self._input(dim, x), *self._arrays()).to("cpu")
+
+    def profiling(self, dim=None, x=None):
+        tp = self._profile(self._input(dim, x), *self._arrays())
+        print("{}-> dim: {} gflops: {:.0f}".format(self.label, dim, tp))
+        return tp
+
+
+class coo_spmm(_format_spmm):
+    """cuSPARSE COO (ALG4) comparator built from a ``graph_input`` (PCSR.py:45-84)."""
+
+    label = "coo"
+    _compute = staticmethod(baselines.cusparse_compute_coo_alg4)
+    _profile = staticmethod(baselines.cusparse_profile_coo_alg4)
+
+    def __init__(self, graph, device="cuda"):
+        c = graph.csr_data
+        lens = (c.rowPtr[1:] - c.rowPtr[:-1]).long()
+        self.row = torch.repeat_interleave(torch.arange(graph.mtx_nodes, dtype=torch.int32), lens).to(device)
+        self.col, self.val = c.colIdx.to(device), c.val.to(device)
+        self.mtx_nodes = graph.mtx_nodes
+
+    def _arrays(self):
+        return self.row, self.col, self.val
+
+
+class csc_spmm(_format_spmm):
+    """cuSPARSE CSC comparator built from a ``graph_input`` (PCSR.py:87-124)."""
+
+    label = "csc"
+    _compute = staticmethod(baselines.cusparse_compute_csc)
+    _profile = staticmethod(baselines.cusparse_profile_csc)
+
+    def __init__(self, graph, device="cuda"):
+        from scipy.sparse import csr_array
+        c = graph.csr_data
+        csc = csr_array((c.val.numpy(), c.colIdx.numpy(), c.rowPtr.numpy()),
+                        shape=(graph.mtx_nodes, graph.mtx_nodes)).tocsc()
+        self.colPtr = torch.from_numpy(csc.indptr.astype("int32")).to(device)
+        self.rowIdx = torch.from_numpy(csc.indices.astype("int32")).to(device)
+        self.val = torch.from_numpy(csc.data).to(device)
+        self.mtx_nodes = graph.mtx_nodes
+
+    def _arrays(self):
+        return self.colPtr, self.rowIdx, self.val
+
+
 def _kind(vec_size):
     return "csr" if vec_size == 1 else ("bcsr" if vec_size == 2 else "vec")
 

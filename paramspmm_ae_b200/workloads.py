@@ -33,6 +33,38 @@ def _time_ms(fn, warmup=3, iters=10):
     return a.elapsed_time(b) / iters
 
 
+def sample_rows(rowPtr, count=32, seed=0):
+    """Row ids worth checking: the longest rows (hubs), the last rows that hold entries (largest
+    output offsets), the first row, and a seeded random draw."""
+    rp = rowPtr.long()
+    ln = rp[1:] - rp[:-1]
+    n = ln.numel()
+    k = max(1, count // 4)
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    nonempty = torch.nonzero(ln > 0).flatten()
+    picks = [torch.topk(ln, min(k, n)).indices.cpu(), nonempty[-k:].cpu(), torch.tensor([0, n - 1]),
+             torch.randint(0, n, (count - 2 * k,), generator=g)]
+    return torch.unique(torch.cat(picks))
+
+
+def check_rows_fp64(rowPtr, colIdx, val, B, out, rows, what="spmm"):
+    """Compare the sampled rows of out = A B with dense fp64 algebra (one gather and one matrix-vector
+    product per row, 64-bit indices throughout, nothing shared with the kernels).  Tolerance: 1e-5
+    relative plus an absolute floor of 1e-4 that grows with the row's length beyond 256 entries
+    (fp32 re-association over L terms).  Returns the largest error in units of the bound."""
+    worst = 0.0
+    for r in rows.tolist():
+        a, b = int(rowPtr[r]), int(rowPtr[r + 1])
+        want = (val[a:b].double()[None, :] @ B[colIdx[a:b].long()].double())[0]
+        got = out[r].double()
+        bound = 1e-5 * want.abs() + 1e-4 * max(1.0, (b - a) / 256.0)
+        ratio = float(((got - want).abs() / bound).max()) if b > a else float(got.abs().max())
+        if not ratio <= 1.0:
+            raise AssertionError("%s: row %d (%d entries) is off by %.3g times the bound" % (what, r, b - a, ratio))
+        worst = max(worst, ratio)
+    return worst
+
+
 def agnn_layer(n=232_965, pairs=57_180_000, dim=64, seed=41, iters=10, grans=(0, 128, 512, 1024, 2048, 4096), device="cuda:0"):
     dev = torch.device(device)
     t0 = time.time()
@@ -172,11 +204,36 @@ def gcn_forward_backward(n=2_449_029, pairs=61_900_000, feats=100, hidden=256, c
         loss.backward()
         return loss
 
-    ms = _time_ms(step, warmup=1, iters=iters)
+    # Independent check before timing: sampled rows (hub rows, the last rows, random ones) of the
+    # aggregation at every width the step uses, and of the first layer's output A (X W1), against
+    # dense fp64 algebra.
+    rows = sample_rows(g.rowPtr, 32, seed)
+    checked = {}
+    for d in sorted(set(dims)):
+        Z = synth.dense_normal(n, d, seed + 7 + d, dev)
+        checked["spmm_dim%d" % d] = round(check_rows_fp64(g.rowPtr, g.colIdx, g.val, Z, ops_by_dim[d].GIN_spmm(Z)[:n],
+                                                          rows, "aggregation at width %d" % d), 3)
+    with torch.no_grad():
+        out1 = layers[0](X, ops_by_dim)
+        XW = (X.double() @ layers[0].weights.detach().double())
+        checked["layer1"] = round(check_rows_fp64(g.rowPtr, g.colIdx, g.val, XW, out1, rows, "first GCN layer"), 3)
+        del XW, out1
+
+    def timed(reorder):
+        old = gnn_conv.REORDER_NARROW_FIRST
+        gnn_conv.REORDER_NARROW_FIRST = reorder
+        try:
+            return _time_ms(step, warmup=1, iters=iters), float(step())
+        finally:
+            gnn_conv.REORDER_NARROW_FIRST = old
+
+    ms, loss = timed(False)            # the reference's operation order, A (H W) in every layer
+    ms_reorder, loss_reorder = timed(True)   # widening layers aggregate first, (A H) W
     spmm_flops = 2.0 * g.nnz * (sum(dims) * 2)  # one SpMM per layer forward, one backward
     return {"n": n, "nnz": g.nnz, "generate_s": round(gen_s, 1), "ms_per_step": round(ms, 2),
-            "loss": float(step()), "spmm_gflop_per_step": round(spmm_flops / 1e9, 1),
-            "regime": decider.regime(stats)}
+            "ms_per_step_narrow_first": round(ms_reorder, 2), "loss": loss, "loss_narrow_first": loss_reorder,
+            "spmm_gflop_per_step": round(spmm_flops / 1e9, 1), "regime": decider.regime(stats),
+            "fp64_row_checks_worst_error_over_bound": checked, "rows_checked": int(rows.numel())}
 
 
 def scaleout_spmm(scale=24, nnz=512_000_000, dim=128, seed=51, iters=5, warmup=2, rank=0, world=1,
@@ -244,6 +301,14 @@ def scaleout_spmm(scale=24, nnz=512_000_000, dim=128, seed=51, iters=5, warmup=2
         return float(t.item())
 
     ms_rep = timed(lambda: sh.forward_replicated(B_full, out_rep), "replicated")
+    # Independent check of the product every other form is compared with: sampled local rows (the
+    # shard's hub rows, its last rows, whose output offsets are the largest, random ones) against
+    # dense fp64 algebra with 64-bit indexing.  At 2^24 rows and dim 128 the output holds 2^31
+    # elements: the last rows sit at byte offsets beyond 2^32 and at element offsets up to 2^31 - 1.
+    rows = sample_rows(sh.rowPtr, 40, seed)
+    fp64_worst = check_rows_fp64(sh.rowPtr, sh._colIdx_global, sh.val, B_full, out_rep, rows,
+                                 "row shard %d of %d" % (rank, world))
+    fp64_max_offset = int(rows.max()) * dim
     ms_ag = timed(lambda: sh.forward(B_shard, out_ag), "allgather")
     # Hub rows of this matrix sum 10^5 and more terms, and the pieces of a split row arrive in a
     # different order on every launch (REDs): the comparison allows for fp32 re-association.
@@ -286,4 +351,6 @@ def scaleout_spmm(scale=24, nnz=512_000_000, dim=128, seed=51, iters=5, warmup=2
             "needed_rows_fraction": round(sh_needed.n_needed / n, 4),
             "spmm_replicated_gflops": round(gf(ms_rep), 1), "allgather_spmm_gflops": round(gf(ms_ag), 1),
             "allgather_overlapped_gflops": round(gf(ms_ov), 1),
-            "compulsory_bytes_global": by, "spmm_replicated_gbs_global": round(by / ms_rep / 1e6, 1)}
+            "compulsory_bytes_global": by, "spmm_replicated_gbs_global": round(by / ms_rep / 1e6, 1),
+            "fp64_rows_checked": int(rows.numel()), "fp64_worst_error_over_bound": round(fp64_worst, 3),
+            "fp64_largest_checked_element_offset": fp64_max_offset}

@@ -352,14 +352,92 @@ def test_device_split_builder_bit_exact(dev, oracle, mats, gran):
     assert torch.equal(rps.cpu(), h_rps) and torch.equal(tr.cpu(), h_tr)
 
 
+def test_device_split_builder_extreme_granularity_and_wrong_count(dev, mats):
+    """A partition length near INT32_MAX (length + granularity overflows 32 bits) still gives the
+    host builder's arrays, and a piece count that is not the partition's is flagged in
+    rowPtr_split[0] (-1) without writing outside the arrays."""
+    from paramspmm_ae_b200 import _lib, ops
+    lib = _lib.lib()
+    rp = mats["hub"].rowPtr
+    big = 2**31 - 1
+    h_rps, h_tr = ops.split_csr(rp, big)
+    rps, tr = ops.split_csr_device(rp.to(dev), big)
+    assert torch.equal(rps.cpu(), h_rps) and torch.equal(tr.cpu(), h_tr)
+    assert int(rps[0]) == 0
+    # wrong count: one piece fewer than the partition has
+    n = rp.shape[0] - 1
+    S = h_tr.shape[0] - 1
+    need = ctypes.c_size_t(0)
+    _lib.check(lib.pspmm_split_device_scratch_bytes(n, ctypes.byref(need)))
+    scratch = torch.empty((need.value + 7) // 8, dtype=torch.int64, device=dev)
+    out_rps = torch.full((S + 2,), -5, dtype=torch.int32, device=dev)
+    out_tr = torch.full((S + 1,), -5, dtype=torch.int32, device=dev)
+    p = lambda t: ctypes.c_void_p(t.data_ptr())
+    rp_d = rp.to(dev)
+    _lib.check(lib.pspmm_split_csr_device(p(rp_d), n, big, p(out_rps), p(out_tr), S, p(scratch), need.value,
+                                          ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
+    torch.cuda.synchronize()
+    assert int(out_rps[0]) == -1                       # flagged
+    assert int(out_rps[S + 1]) == -5 and int(out_tr[S]) == -5   # nothing past the caller's sizes
+
+
 def test_profile_entry_points_return_gflops(dev, mats):
+    """All twelve *_profile functions (SpMM/SpMM.cpp:482-889, SDDMM/sddmm.cpp:338-661): an integer
+    GFLOP/s figure; the block forms take the CSR entry count before CF."""
     from paramspmm_ae_b200 import ops
-    m = mats["uniform16"].to(dev)
-    X = torch.ones(m.n_rows, 64, device=dev)
-    g = ops.csr_spmm_profile(X, m.rowPtr, m.colIdx, m.val, 2, 8)
-    assert isinstance(g, int) and g > 0
-    g = ops.csr_sddmm_profile(X, X, m.rowPtr, m.colIdx, m.val, 2, 8)
-    assert isinstance(g, int) and g > 0
+    m = mats["powerlaw"]  # odd row count: the block forms pad
+    d = m.to(dev)
+    n, nnz = m.n_rows, m.nnz
+    X = torch.ones(n, 64, device=dev)
+    rps, tr = ops.split_csr(m.rowPtr, 32)
+    rps, tr = rps.to(dev), tr.to(dev)
+    got = [ops.csr_spmm_profile(X, d.rowPtr, d.colIdx, d.val, 2, 8),
+           ops.csr_split_spmm_profile(X, rps, d.colIdx, d.val, tr, 2, 8),
+           ops.csr_sddmm_profile(X, X, d.rowPtr, d.colIdx, d.val, 2, 8),
+           ops.csr_split_sddmm_profile(X, X, rps, d.colIdx, d.val, tr, 2, 8)]
+    for V, sp, sps, sd, sds in ((2, ops.bcsr_spmm_profile, ops.bcsr_split_spmm_profile, ops.bcsr_sddmm_profile,
+                                 ops.bcsr_split_sddmm_profile),
+                                (3, ops.vec_spmm_profile, ops.vec_split_spmm_profile, ops.vec_sddmm_profile,
+                                 ops.vec_split_sddmm_profile)):
+        rpb, cb, vb = ops.bcsr_from_csr(m.rowPtr, m.colIdx, m.val, m.n_cols, V)
+        b_rps, b_tr = ops.split_csr(rpb, 32)
+        rpb, cb, vb, b_rps, b_tr = (t.to(dev) for t in (rpb, cb, vb, b_rps, b_tr))
+        A = torch.ones((n + V - 1) // V * V, 64, device=dev)
+        got += [sp(X, rpb, cb, vb, nnz, 2, 8), sps(X, b_rps, cb, vb, b_tr, nnz, 2, 8),
+                sd(A, X, rpb, cb, vb, nnz, 2, 8), sds(A, X, b_rps, cb, vb, b_tr, nnz, 2, 8)]
+    assert len(got) == 12 and all(isinstance(g, int) and g > 0 for g in got), got
+    with pytest.raises(RuntimeError):
+        ops.csr_spmm_profile(X, d.rowPtr, d.colIdx, d.val, 9, 8)      # CF outside 1..8
+    with pytest.raises(RuntimeError):
+        ops.csr_sddmm_profile(X, X, d.rowPtr, d.colIdx, d.val, 5, 8)  # CF outside 1..4
+
+
+def test_spmm_output_rows_follow_the_dense_input(dev, oracle, mats):
+    """The reference sizes the output from the dense input (zeros_like(input), padded to a multiple
+    of the block height) and its own callers pass inputs with more rows than the matrix (features
+    padded to an even row count): the extra output rows are zero, fewer rows than the matrix raise."""
+    from paramspmm_ae_b200 import ops
+    m = mats["powerlaw"]
+    rp, ci, v = m.numpy()
+    d = m.to(dev)
+    n = m.n_rows
+    X = dense(n + 1, 32, 5)
+    want = oracle.spmm_csr(rp, ci, v, X[:n].numpy())
+    Xd = X.to(dev)
+    out = ops.csr_spmm(Xd, d.rowPtr, d.colIdx, d.val, 1, 8)
+    assert out.shape == (n + 1, 32) and float(out[n].abs().max()) == 0.0
+    close(out[:n], want)
+    rps, tr = ops.split_csr(m.rowPtr, 32)
+    out = ops.csr_split_spmm(Xd, rps.to(dev), d.colIdx, d.val, tr.to(dev), 1, 8)
+    assert out.shape == (n + 1, 32) and float(out[n].abs().max()) == 0.0
+    close(out[:n], want)
+    rpb, cb, vb = ops.bcsr_from_csr(m.rowPtr, m.colIdx, m.val, m.n_cols, 2)
+    X3 = dense(n + 3, 32, 5)
+    out = ops.bcsr_spmm(X3.to(dev), rpb.to(dev), cb.to(dev), vb.to(dev), 1, 8)
+    assert out.shape == (n + 3, 32) and float(out[n:].abs().max()) == 0.0
+    close(out[:n], oracle.spmm_csr(rp, ci, v, X3[:n].numpy()))
+    with pytest.raises(RuntimeError):
+        ops.csr_spmm(Xd[: n - 1].contiguous(), d.rowPtr, d.colIdx, d.val, 1, 8)
 
 
 def test_spconv_forward_backward(dev, oracle, mats):
@@ -395,6 +473,18 @@ def test_cusparse_comparators_agree(dev, oracle, mats):
     want = oracle.spmm_csr(rp, ci, v, B.numpy())
     close(baselines.cusparse_compute(B.to(dev), d.rowPtr, d.colIdx, d.val), want)
     close(baselines.cusparse_compute_csr_alg2(B.to(dev), d.rowPtr, d.colIdx, d.val), want)
+    # COO (ALG4) and CSC forms, fed the way the reference's coo_spmm / csc_spmm objects feed them
+    # (PCSR.py:45-124); the CSC arrays come from scipy, as there
+    from scipy.sparse import csr_array
+    rows = torch.repeat_interleave(torch.arange(m.n_rows, dtype=torch.int32), (m.rowPtr[1:] - m.rowPtr[:-1]).long())
+    close(baselines.cusparse_compute_coo_alg4(B.to(dev), rows.to(dev), d.colIdx, d.val), want)
+    csc = csr_array((v, ci, rp), shape=(m.n_rows, m.n_cols)).tocsc()
+    t = lambda a, dt: torch.from_numpy(a.astype(dt)).to(dev)
+    close(baselines.cusparse_compute_csc(B.to(dev), t(csc.indptr, "int32"), t(csc.indices, "int32"),
+                                         t(csc.data, "float32")), want)
+    assert baselines.cusparse_profile_coo_alg4(B.to(dev), rows.to(dev), d.colIdx, d.val) > 0
+    assert baselines.cusparse_profile_csc(B.to(dev), t(csc.indptr, "int32"), t(csc.indices, "int32"),
+                                          t(csc.data, "float32")) > 0
     close(baselines.gespmm_compute(B.to(dev), d.rowPtr, d.colIdx, d.val), want)
     for dim in (20, 100):  # the row-caching comparator on ragged widths
         B2 = dense(m.n_cols, dim, 8)

@@ -1,4 +1,4 @@
-"""GPU parity against the reference's OWN CUDA kernels for SDDMM and genmask.
+"""GPU parity against the reference's OWN CUDA kernels for SpMM, SDDMM and genmask.
 
 oracle/build_oracle.py::build_ref_sddmm compiles the reference's SDDMM extension (sddmm.cpp,
 sddmm_kernel.cu, sddmm_baseline_kernel.cu) unmodified for sm_100a into oracle/_ref/; these tests
@@ -133,3 +133,72 @@ def test_spmm_against_reference_cuda(ref_spmm, graphs, name, dim):
     ours_b = ops.bcsr_spmm(X, rpb_d, cb_d, vb_d, CF, 8)
     assert ours_b.shape == theirs_b.shape
     _close(ours_b, theirs_b.cpu().numpy())
+
+
+@pytest.mark.parametrize("name", ["powerlaw", "rmat"])
+@pytest.mark.parametrize("dim", [16, 47, 64, 100, 128, 256])
+def test_split_block_and_vec_spmm_against_reference_cuda(ref_spmm, graphs, name, dim):
+    """bcsr_split_spmm (2 x 1 blocks, row-split), vec_spmm and vec_split_spmm (3 x 1 blocks) of the
+    reference (SpMM/SpMM.cpp:273-480) next to the restatement and to this library's kernels.
+    The block-rows are split at 32 blocks, the reference's own partition length for short rows
+    (graph_input.py:101), so each piece is one staging window of its kernels."""
+    from oracle import oracle as orc
+    from paramspmm_ae_b200 import ops, synth
+    dev = torch.device("cuda:0")
+    m = graphs[name]
+    X = synth.dense_uniform(m.n_cols, dim, 300 + dim).to(dev)
+    CF = min(8, (dim + 31) // 32)
+    want = orc.spmm_csr(*m.numpy(), X.cpu().numpy())
+    for V, plain, split in ((2, None, ref_spmm.bcsr_split_spmm), (3, ref_spmm.vec_spmm, ref_spmm.vec_split_spmm)):
+        rpb, cb, vb = ops.bcsr_from_csr(m.rowPtr, m.colIdx, m.val, m.n_cols, V)
+        rps, tr = ops.split_csr(rpb, 32)
+        rpb_d, cb_d, vb_d, rps_d, tr_d = (t.to(dev) for t in (rpb, cb, vb, rps, tr))
+        ours_plain = ops.bcsr_spmm if V == 2 else ops.vec_spmm
+        ours_split = ops.bcsr_split_spmm if V == 2 else ops.vec_split_spmm
+        if plain is not None:
+            theirs = plain(X, rpb_d, cb_d, vb_d, CF, 8)
+            torch.cuda.synchronize()
+            _close(theirs[: m.n_rows], want)                               # pins the restatement
+            ours = ours_plain(X, rpb_d, cb_d, vb_d, CF, 8)
+            assert ours.shape == theirs.shape
+            _close(ours, theirs.cpu().numpy())
+        theirs_s = split(X, rps_d, cb_d, vb_d, tr_d, CF, 8)
+        torch.cuda.synchronize()
+        _close(theirs_s[: m.n_rows], want)
+        ours_s = ours_split(X, rps_d, cb_d, vb_d, tr_d, CF, 8)
+        assert ours_s.shape == theirs_s.shape
+        _close(ours_s, theirs_s.cpu().numpy())
+
+
+@pytest.mark.parametrize("name", ["powerlaw", "rmat"])
+def test_split_block_sddmm_against_reference_cuda(ref, graphs, name):
+    """bcsr_split_sddmm of the reference (SDDMM/sddmm.cpp:169-219) inside the domain its launcher
+    supports (one column tile: CF = ceil(dim / 32) <= 4; A padded to an even row count, as the
+    reference's own callers pad it).  The 3 x 1 SDDMM kernels of the reference are not run: read as
+    text they index shared memory with a hard-coded factor 2 and guard the wrong loop variable
+    (sddmm_kernel.cu:1303, 1339), so they stay checked against the restatement only."""
+    from oracle import oracle as orc
+    from paramspmm_ae_b200 import ops, synth
+    dev = torch.device("cuda:0")
+    m = graphs[name]
+    rpb, cb, vb = ops.bcsr_from_csr(m.rowPtr, m.colIdx, m.val, m.n_cols, 2)
+    rps, tr = ops.split_csr(rpb, 32)
+    cb_d, vb_d, rps_d, tr_d = (t.to(dev) for t in (cb, vb, rps, tr))
+    nbr = rpb.shape[0] - 1
+    for dim in (32, 64, 100, 128):
+        A = synth.dense_uniform(nbr * 2, dim, 500 + dim).to(dev)
+        B = synth.dense_uniform(m.n_cols, dim, 600 + dim).to(dev)
+        CF = (dim + 31) // 32
+        theirs = ref.bcsr_split_sddmm(A, B, rps_d, cb_d, vb_d, tr_d, CF, 8)
+        torch.cuda.synchronize()
+        want = orc.sddmm_bcsr(rpb.numpy(), cb.numpy(), vb.numpy(), A.cpu().numpy(), B.cpu().numpy())
+        _close(theirs, want)
+        _close(ops.bcsr_split_sddmm(A, B, rps_d, cb_d, vb_d, tr_d, CF, 8), theirs.cpu().numpy())
+    # an A that stops inside the last block-row (odd row count, not padded): nothing is read past it
+    if m.n_rows % 2 == 1:
+        A = synth.dense_uniform(m.n_rows, 64, 9).to(dev)
+        B = synth.dense_uniform(m.n_cols, 64, 10).to(dev)
+        Apad = torch.cat([A, torch.zeros(1, 64, device=dev)])
+        want = orc.sddmm_bcsr(rpb.numpy(), cb.numpy(), vb.numpy(), Apad.cpu().numpy(), B.cpu().numpy())
+        _close(ops.bcsr_sddmm(A, B, rpb.to(dev), cb_d, vb_d, 2, 8), want)
+        _close(ops.bcsr_split_sddmm(A, B, rps_d, cb_d, vb_d, tr_d, 2, 8), want)
