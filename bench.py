@@ -13,9 +13,14 @@ step time is the sum of the launch times.  With N > 1 (torchrun, one rank per GP
 runs the same pass on its own row block of an N-times taller matrix with the dense operand
 replicated (no data-path collective); the step time is the maximum over ranks.
 
-`--impl reference` times the reference's CPU path for the same product,
-torch.sparse.mm on a CSR tensor on the host (verification.py:44-77 of the reference), on a
-bounded sample of the workload with all host threads.
+Beside `value` the line carries `scaleout`: the strong-scaling times of the row-sharded SpMM of
+ONE global R-MAT matrix (2^24 nodes, 5.12e8 entries, dim 128) at this GPU count, with the dense
+operand replicated, all-gathered, and exchanged row by row through the pull kernel; the speed-up at
+N GPUs is the N = 1 run's figure divided by this one.
+
+`--impl reference` times the reference's CPU path for the same products, torch.sparse.mm on CSR
+tensors on the host (verification.py:44-77 of the reference): one step is the same pass over all
+48 (matrix, dim) SpMMs, with all the host threads the process may use.
 """
 import argparse
 import json
@@ -33,12 +38,13 @@ NNZ_PER_ROW = 16
 DIMS = list(range(16, 257, 16))
 MATRICES = ("uniform", "banded", "rmat")
 FALLBACK_HBM_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum per launch from `ncu --set full` captures of these
-# launches at 1,000,000 rows (summaries with the commands: profiles/spmm_seg_kernel_c2_*.md).
+# DRAM bytes of one launch (dram__bytes_read.sum + dram__bytes_write.sum of an `ncu` capture of that
+# launch at 1,000,000 rows) and the source revision the captured library was built from.  A launch
+# whose kernel configuration has changed since its capture reports no traffic.
 NCU_DRAM_BYTES = {
-    ("uniform", 64): 3.172e9, ("banded", 64): 0.602e9, ("rmat", 64): 0.715e9,
-    ("uniform", 128): 7.447e9, ("banded", 128): 1.116e9, ("rmat", 128): 2.014e9,
-    ("uniform", 256): 16.086e9, ("banded", 256): 2.149e9, ("rmat", 256): 5.775e9,
+    ("uniform", 64): (3.172e9, "fcf53ef"), ("banded", 64): (0.602e9, "fcf53ef"), ("rmat", 64): (0.715e9, "fcf53ef"),
+    ("uniform", 128): (7.447e9, "fcf53ef"), ("banded", 128): (1.116e9, "fcf53ef"), ("rmat", 128): (2.014e9, "fcf53ef"),
+    ("uniform", 256): (16.086e9, "fcf53ef"), ("banded", 256): (2.149e9, "fcf53ef"), ("rmat", 256): (5.775e9, "fcf53ef"),
 }
 
 
@@ -59,6 +65,8 @@ def parse():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-comparators", action="store_true", help="skip the cuSPARSE timing rows")
+    ap.add_argument("--no-scaleout", action="store_true", help="skip the strong-scaling leg (the `scaleout` key)")
+    ap.add_argument("--scaleout-iters", type=int, default=5)
     return ap.parse_args()
 
 
@@ -77,7 +85,9 @@ def bench_config(n, dims):
     return {"workload": "c2_dim_sweep", "rows_per_gpu": n, "nnz_per_row": NNZ_PER_ROW,
             "matrices": list(MATRICES), "dims": list(dims), "launches_per_step": 3 * len(dims),
             "l2": "flushed before every launch (256 MiB memset outside the timed events)",
-            "sharding": "row blocks, dense operand replicated, no collective"}
+            "sharding": "`value`: every rank runs the pass on its own row block with the dense operand replicated, "
+                        "no collective (weak scaling); `scaleout`: one global matrix row-sharded over the ranks "
+                        "(strong scaling), dense operand replicated / all-gathered / exchanged"}
 
 
 def spmm_bytes(n_rows, n_cols, nnz, dim, n_seg=None):
@@ -140,6 +150,19 @@ class ClockSampler(threading.Thread):
 
 
 # ----------------------------------------------------------------------------- CPU arms
+def use_all_host_threads():
+    """torch's intra-op thread count = the cores this process may run on.  Under
+    torch.distributed.run the environment carries OMP_NUM_THREADS=1; the CPU arms are timed on one
+    rank only, so they take every core of the affinity mask back."""
+    import torch
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    torch.set_num_threads(max(1, n))
+    return torch.get_num_threads()
+
+
 def cpu_spmm_gflops(mats_cpu, dim, seconds, max_iters=50):
     """torch.sparse.mm on CSR tensors on the host, all threads: GFLOP/s over one SpMM per matrix."""
     import torch
@@ -160,34 +183,43 @@ def cpu_spmm_gflops(mats_cpu, dim, seconds, max_iters=50):
 
 
 def run_reference(args):
-    """The reference's CPU implementation of the product, same metric and unit."""
+    """The reference's CPU implementation of the product on the same workload: one step = the same
+    48 SpMMs as the native arm (3 matrices x 16 dims), torch.sparse.mm on CSR tensors."""
     import torch
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    dim = 64
-    mats = build_matrices(args.rows, "cpu")
-    flops = sum(2.0 * m.nnz * dim for m in mats.values())
+    cores = use_all_host_threads()
     from paramspmm_ae_b200 import synth
-    B = synth.dense_uniform(args.rows, dim, 11)
-    sps = [torch.sparse_csr_tensor(m.rowPtr, m.colIdx, m.val, size=(m.n_rows, m.n_cols)) for m in mats.values()]
-    for _ in range(max(1, args.warmup)):
-        for s in sps:
-            torch.sparse.mm(s, B)
+    mats = build_matrices(args.rows, "cpu")
+    sps = {k: torch.sparse_csr_tensor(m.rowPtr, m.colIdx, m.val, size=(m.n_rows, m.n_cols)) for k, m in mats.items()}
+    Bs = {dim: synth.dense_uniform(args.rows, dim, 1000 + dim) for dim in args.dims}
+    flops = sum(2.0 * m.nnz * dim for m in mats.values() for dim in args.dims)
+
+    def one_pass():
+        for dim in args.dims:
+            for name in MATRICES:
+                torch.sparse.mm(sps[name], Bs[dim])
+
+    # One full pass takes seconds on the host: one untimed pass warms caches and thread pools, however
+    # many warm-up steps the native arm is asked for.
+    warm = 1 if args.warmup > 0 else 0
+    for _ in range(warm):
+        one_pass()
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        for s in sps:
-            torch.sparse.mm(s, B)
+        one_pass()
     dt = time.perf_counter() - t0
     val = flops * args.steps / dt / 1e9
-    sample = "one SpMM per matrix (uniform, banded, rmat; %d rows, 16 nnz/row) at dim %d" % (args.rows, dim)
+    sample = ("%d passes over all %d SpMMs of the workload (3 matrices x dims %s, %d rows, 16 nnz/row), "
+              "%d untimed pass before them" % (args.steps, 3 * len(args.dims), list(args.dims), args.rows, warm))
     print(json.dumps({
         "impl": "reference", "metric": "SpMM GFLOP/s (2*nnz*dim/t)", "value": val, "unit": "GFLOP/s",
-        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "warmup_passes_run": warm,
         "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": bench_config(args.rows, args.dims),
-        "cpu_baseline": {"value": val, "unit": "GFLOP/s", "cores": torch.get_num_threads(), "kind": "reference",
+        "cpu_baseline": {"value": val, "unit": "GFLOP/s", "cores": cores, "kind": "reference",
                          "sample": sample + "; torch.sparse.mm(CSR) on the host, the reference's CPU path"},
         "e2e": {"value": val, "unit": "GFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
@@ -326,22 +358,54 @@ def main():
         sweep.append({"matrix": name, "dim": dim, "ms": round(ms, 5),
                       "gflops": round(2.0 * mats[name].nnz * dim / ms / 1e6, 1),
                       "gbs": round(by / ms / 1e6, 1), "frac": round(by / ms / 1e6 / peak, 4),
-                      "split": int(p["if_split"])})
+                      "split": int(p["if_split"]), "path": p.get("path", "gather")})
+
+    def roofline_of(i):
+        r = {"bound": "hbm", "achieved": sweep[i]["gbs"], "peak": peak, "unit": "GB/s", "frac": sweep[i]["frac"],
+             "traffic": None, "peak_source": peak_kind,
+             "kernel": "%s %s dim=%d" % ("spmm_window_kernel" if sweep[i]["path"] == "window" else "spmm_seg_kernel",
+                                         sweep[i]["matrix"], sweep[i]["dim"]),
+             "ms": sweep[i]["ms"],
+             "bytes_model": "4(n+1)+8nnz+4*dim*n_cols+4*dim*n_rows (+8S for a split layout)"}
+        key = (sweep[i]["matrix"], sweep[i]["dim"])
+        if n == N_ROWS and key in NCU_DRAM_BYTES and sweep[i]["path"] == "gather":
+            tb, rev = NCU_DRAM_BYTES[key]
+            algo = sweep[i]["gbs"] * sweep[i]["ms"] * 1e6
+            r["traffic"] = tb
+            r["traffic_source"] = ("ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch of this case, "
+                                   "library built from revision %s" % rev)
+            r["traffic_over_algorithmic"] = round(tb / algo, 2)
+            # the same launch measured on the bytes it actually moves
+            r["traffic_gbs"] = round(tb / mean_ms[i] / 1e6, 1)
+            r["traffic_frac"] = round(tb / mean_ms[i] / 1e6 / peak, 4)
+        return r
+
     top = max(range(len(cases)), key=lambda i: mean_ms[i])
-    roofline = {"bound": "hbm", "achieved": sweep[top]["gbs"], "peak": peak, "unit": "GB/s",
-                "frac": sweep[top]["frac"], "traffic": None, "peak_source": peak_kind,
-                "kernel": "spmm_seg_kernel %s dim=%d" % (sweep[top]["matrix"], sweep[top]["dim"]),
-                "bytes_model": "4(n+1)+8nnz+4*dim*n_cols+4*dim*n_rows (+8S for a split layout)",
-                "best_frac": max(s["frac"] for s in sweep),
-                "rmat_dim_ge_64_frac": [s["frac"] for s in sweep if s["matrix"] == "rmat" and s["dim"] >= 64]}
-    key = (sweep[top]["matrix"], sweep[top]["dim"])
-    if n == N_ROWS and key in NCU_DRAM_BYTES:
-        roofline["traffic"] = NCU_DRAM_BYTES[key]
-        roofline["traffic_source"] = "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch of this case"
-        # the same launch measured on the bytes it actually moves: with uniformly random columns and
-        # B several times the L2, nnz * dim * 4 gathered bytes are DRAM transactions by construction
-        roofline["traffic_gbs"] = round(NCU_DRAM_BYTES[key] / mean_ms[top] / 1e6, 1)
-        roofline["traffic_frac"] = round(NCU_DRAM_BYTES[key] / mean_ms[top] / 1e6 / peak, 4)
+    roofline = roofline_of(top)
+    roofline["best_frac"] = max(s["frac"] for s in sweep)
+    roofline["rmat_dim_ge_64_frac"] = [s["frac"] for s in sweep if s["matrix"] == "rmat" and s["dim"] >= 64]
+    # the power-law case at dim 128, and how close the two gather-bound launches come to the rate at
+    # which this GPU can fetch their rows at all (the bare gather of the same column stream, timed here)
+    roofline_rmat, gather = None, None
+    if ("rmat", 128) in cases:
+        roofline_rmat = roofline_of(cases.index(("rmat", 128)))
+    if rank == 0 and not args.no_comparators:
+        try:
+            from paramspmm_ae_b200 import baselines
+            gather = []
+            for key in sorted({("rmat", 128), (sweep[top]["matrix"], sweep[top]["dim"])}):
+                if key not in cases or key[1] not in (16, 32, 64, 128, 256):
+                    continue
+                m, ms = mats[key[0]], mean_ms[cases.index(key)]
+                flush.zero_()
+                floor_ms = baselines.gather_ceiling_ms(m.colIdx, Bs[key[1]], warmup=2, iters=5)
+                gb = 4.0 * key[1] * m.nnz
+                gather.append({"matrix": key[0], "dim": key[1], "gathered_bytes": gb,
+                               "spmm_gather_gbs": round(gb / ms / 1e6, 1),
+                               "bare_gather_gbs": round(gb / floor_ms / 1e6, 1), "bare_gather_ms": round(floor_ms, 5),
+                               "frac_of_bare_gather": round(floor_ms / ms, 4)})
+        except Exception as e:
+            gather = {"unavailable": "%s: %s" % (type(e).__name__, e)}
 
     # ---- end to end: host buffers in, host buffer out, copies inside the timed region
     e2e = None
@@ -457,11 +521,36 @@ def main():
     # ---- CPU baseline on the host cores (rank 0, N = 1 only)
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        cores = use_all_host_threads()
         mats_cpu = {k: m.to("cpu") for k, m in mats.items()}
         g, it = cpu_spmm_gflops(mats_cpu, 64, args.cpu_seconds)
-        cpu = {"value": g, "unit": "GFLOP/s", "cores": torch.get_num_threads(), "kind": "reference",
+        cpu = {"value": g, "unit": "GFLOP/s", "cores": cores, "kind": "reference",
                "sample": "%d passes of one SpMM per matrix (3 matrices, %d rows, 16 nnz/row) at dim 64 with "
                          "torch.sparse.mm(CSR) on the host, the reference's CPU path (verification.py:44-77)" % (it, n)}
+
+    # ---- strong scaling of one global matrix over the ranks (BASELINE's scale-out configuration)
+    scaleout = None
+    if not args.no_scaleout:
+        from paramspmm_ae_b200 import workloads
+        del Bs, Cs, mats, layouts, flush
+        torch.cuda.empty_cache()
+        try:
+            r = workloads.scaleout_brief(scale=args.c5_scale, nnz=args.c5_nnz, iters=args.scaleout_iters, rank=rank,
+                                         world=world, device="cuda:%d" % local)
+            gf = lambda ms: round(2.0 * r["nnz"] * r["dim"] / ms / 1e6, 1)
+            scaleout = {"workload": "c5_scaleout: R-MAT 2^%d nodes, %d entries, dim %d, rows of A in contiguous blocks "
+                                    "balanced by nnz, one block per GPU" % (args.c5_scale, r["nnz"], r["dim"]),
+                        "scaling": "strong", "n_gpus": world,
+                        "replicated_ms": r["replicated_ms"], "allgather_ms": r["allgather_ms"],
+                        "exchange_ms": r["exchange_ms"],
+                        "replicated_gflops": gf(r["replicated_ms"]), "allgather_gflops": gf(r["allgather_ms"]),
+                        "exchange_gflops": gf(r["exchange_ms"]),
+                        "exchange_form": "rows referenced by the shard only, fetched from the owners' peer-mapped blocks "
+                                         "by the pull kernel in %d chunks, products overlapped (transport %s)"
+                                         % (r["row_chunks"], r["transport"]),
+                        "detail": r}
+        except Exception as e:  # the headline number must not depend on this leg
+            scaleout = {"unavailable": "%s: %s" % (type(e).__name__, e)}
 
     if rank == 0:
         print(json.dumps({
@@ -471,6 +560,7 @@ def main():
             "data": "synthetic",
             "config": bench_config(n, dims),
             "e2e": e2e, "gpu_launches": launches, "clocks": clocks, "roofline": roofline,
+            "roofline_rmat": roofline_rmat, "gather": gather, "scaleout": scaleout,
             "cpu_baseline": cpu, "comparators": comparators, "wall_ms_per_step_incl_flush": wall / args.steps * 1e3, "sweep": sweep,
         }))
     if world > 1:

@@ -42,6 +42,15 @@ write straight into ``symmetric_input(dim)`` and pass that to ``forward`` to ski
 by chunk (the same cut of every owner's block into ``row_chunks`` runs of rows), one all-to-all
 per chunk, and the product of column block k runs while the rows of chunk k+1 are on the wire.
 
+``transport="pull"`` (the two "needed" exchanges) does away with the pack, the all-to-all and the
+request lists: every rank keeps its block of the dense operand in peer-mapped memory and each rank
+fetches the rows it references with ONE copy kernel that reads the owners' blocks directly
+(``pspmm_pull_rows``: plain 16-byte loads over NVLink, a bounded number of thread blocks, every
+rank starting at a different owner), straight into its compact operand.  With
+``exchange="needed_pipelined"`` the fetch of chunk k+1 runs beside the product of column block k.
+The kernel waits on nothing; a one-element all-reduce before the fetches (every block is in place)
+and one after them (every peer has finished reading) order it against the producers.
+
 ``dim_chunks > 1`` splits the dense columns into slices and gathers slice s+1 on a side
 stream while the SpMM of slice s runs (the kernels take explicit leading dimensions, so a
 slice of C is written in place).
@@ -70,8 +79,8 @@ def extract_rows(rowPtr, colIdx, val, lo, hi):
     """Rows [lo, hi) of a CSR matrix with re-based row pointers and global column ids."""
     rp = torch.as_tensor(rowPtr)
     a, b = int(rp[lo]), int(rp[hi])
-    return ((rp[lo: hi + 1] - rp[lo]).to(torch.int32).contiguous(), colIdx[a:b].contiguous(),
-            val[a:b].contiguous())
+    part = lambda t: t[a:b].clone() if (b - a) < t.shape[0] else t  # a slice would keep the whole array alive
+    return ((rp[lo: hi + 1] - rp[lo]).to(torch.int32).contiguous(), part(colIdx), part(val))
 
 
 def remap_columns(colIdx, col_bounds, max_rows):
@@ -92,15 +101,18 @@ class ShardedSpMM:
 
     def __init__(self, rowPtr, colIdx, val, n_cols, rank, world, row_bounds=None, col_bounds=None,
                  device="cuda", group=None, local_spmm=None, dim_chunks=1, exchange="allgather",
-                 row_chunks=4, transport="nccl"):
+                 row_chunks=4, transport="nccl", local_block=None):
         if exchange not in ("allgather", "needed", "pipelined", "needed_pipelined"):
             raise ValueError("exchange must be 'allgather', 'needed', 'pipelined' or 'needed_pipelined'")
         if row_chunks < 1:
             raise ValueError("row_chunks must be at least 1")
-        if transport not in ("nccl", "copy_engine"):
-            raise ValueError("transport must be 'nccl' or 'copy_engine'")
+        if transport not in ("nccl", "copy_engine", "pull"):
+            raise ValueError("transport must be 'nccl', 'copy_engine' or 'pull'")
         if transport == "copy_engine" and exchange != "pipelined":
             raise ValueError("the copy-engine transport moves whole row chunks: use exchange='pipelined'")
+        if transport == "pull" and exchange not in ("needed", "needed_pipelined"):
+            raise ValueError("the pull transport fetches referenced rows: use exchange='needed' or 'needed_pipelined'")
+        self.pull_ctas = 64
         self.transport, self._peer = transport, None
         self.rank, self.world, self.group, self.dim_chunks = rank, world, group, dim_chunks
         self.exchange, self.row_chunks = exchange, row_chunks
@@ -111,7 +123,9 @@ class ShardedSpMM:
         self.max_rows = int((self.col_bounds[1:] - self.col_bounds[:-1]).max())
         lo, hi = int(self.row_bounds[rank]), int(self.row_bounds[rank + 1])
         self.lo, self.hi = lo, hi
-        rp, ci, v = extract_rows(rowPtr, colIdx, val, lo, hi)
+        # local_block = (rowPtr, colIdx with global ids, val) of this rank's rows when the caller has
+        # extracted them already (several operators over one shard then share these arrays)
+        rp, ci, v = local_block if local_block is not None else extract_rows(rowPtr, colIdx, val, lo, hi)
         self.rowPtr = rp.to(device)
         self.val = v.to(device)
         self.device = torch.device(device)
@@ -129,7 +143,7 @@ class ShardedSpMM:
                                for rp_k, _, _ in self.blocks]
         else:
             self.local_spmm = local_spmm if local_spmm is not None else self._planned_spmm()
-        overlap = dim_chunks > 1 or exchange in ("pipelined", "needed_pipelined")
+        overlap = dim_chunks > 1 or exchange in ("pipelined", "needed_pipelined") or transport == "pull"
         self._side = torch.cuda.Stream() if (self.device.type == "cuda" and overlap) else None
         self._pull_streams = ([torch.cuda.Stream() for _ in range(min(3, world - 1))]
                               if (self._side is not None and transport == "copy_engine") else [])
@@ -200,7 +214,9 @@ class ShardedSpMM:
             own = torch.repeat_interleave(torch.arange(W, device=dev), recv_counts.to(dev))
             wanted = (need - cb[own]).to(torch.int64)
             recv_splits = [int(x) for x in recv_counts]
-            if W == 1:
+            if self.transport == "pull":  # the reader addresses the owners' blocks itself: nothing to request
+                send_splits, send_rows = None, wanted.to(torch.int32)
+            elif W == 1:
                 send_splits, send_rows = list(recv_splits), wanted
             else:
                 counts_out = torch.empty(W, dtype=torch.int64, device=dev)
@@ -272,7 +288,11 @@ class ShardedSpMM:
             import torch.distributed as dist
             import torch.distributed._symmetric_memory as symm
 
-            rows = self.row_chunks * self.chunk_rows
+            rows = self.max_rows if self.transport == "pull" else self.row_chunks * self.chunk_rows
+            if self.world == 1:  # no peers: an ordinary buffer stands in for the mapped one
+                src = torch.zeros((rows, dim), dtype=like.dtype, device=like.device)
+                self._peer = (src, [src], None)
+                return self._peer
             src = symm.empty((rows, dim), dtype=like.dtype, device=like.device)
             src.zero_()
             group = self.group if self.group is not None else dist.group.WORLD
@@ -283,10 +303,55 @@ class ShardedSpMM:
         return self._peer
 
     def symmetric_input(self, dim, dtype=torch.float32):
-        """The peer-mapped buffer for this rank's block of the dense operand (copy-engine transport):
+        """The peer-mapped buffer for this rank's block of the dense operand (copy-engine and pull transports):
         rows [0, my block's row count) of it, for a producer to write into and hand to ``forward``."""
         like = torch.empty(0, dtype=dtype, device=self.device)
         return self._peer_blocks(dim, like)[0][: self.my_cols[1] - self.my_cols[0]]
+
+    def _forward_pull(self, B_shard, out):
+        """Both "needed" exchanges over the pull transport: fetch kernels on the side stream, one per
+        chunk, each followed by an event; the products on the main stream wait for their chunk."""
+        import torch.distributed as dist
+
+        from . import ops
+
+        rows, dim = B_shard.shape
+        src, peers, fence = self._peer_blocks(dim, B_shard)
+        recv = self._receive_buffer(max(1, self.n_needed), dim, B_shard)
+        main = torch.cuda.current_stream()
+        side = self._side
+        events = []
+        side.wait_stream(main)
+        with torch.cuda.stream(side):
+            if B_shard.data_ptr() != src.data_ptr():
+                src[:rows].copy_(B_shard)
+            if fence is not None:
+                dist.all_reduce(fence, group=self.group)  # every block is in place
+            for base, cnt, recv_splits, _, want_rows in self.chunk_plan:
+                first = [0]
+                for c in recv_splits:
+                    first.append(first[-1] + c)
+                if cnt:
+                    # start at the next rank's rows so that the ranks read different owners at a time
+                    rotate = first[(self.rank + 1) % self.world] % cnt
+                    ops.pull_rows(recv[base: base + cnt], peers, first, want_rows, rotate=rotate, ctas=self.pull_ctas)
+                ev = torch.cuda.Event()
+                ev.record(side)
+                events.append(ev)
+            if fence is not None:
+                dist.all_reduce(fence, group=self.group)  # every peer has finished reading this block
+        B_shard.record_stream(side)
+        if self.exchange == "needed":
+            main.wait_event(events[0])
+            self.local_spmm(out, recv, self.rowPtr, self.colIdx, self.val)
+        else:
+            for kk in range(self.row_chunks):
+                main.wait_event(events[kk])
+                rp, ci, v = self.blocks[kk]
+                self.block_spmm[kk](out, recv, rp, ci, v, accumulate=kk > 0)
+        # a producer on the main stream may overwrite the block only after the closing fence
+        main.wait_stream(side)
+        return out
 
     def _forward_copy_engine(self, B_shard, out):
         import torch.distributed as dist
@@ -390,6 +455,10 @@ class ShardedSpMM:
         self.colIdx = torch.searchsorted(need, cols_global.long()).to(torch.int32)
         self.n_needed = int(need.numel())
         self.recv_splits = [int(x) for x in recv_counts]
+        if self.transport == "pull":  # the reader addresses the owners' blocks itself: nothing to request
+            self.chunk_rows = self.max_rows
+            self.chunk_plan = [(0, self.n_needed, self.recv_splits, None, wanted.to(torch.int32))]
+            return
         if self.world == 1:
             self.send_splits, self.send_rows = list(self.recv_splits), wanted
             return
@@ -411,6 +480,22 @@ class ShardedSpMM:
         dist.all_to_all_single(recv, send, output_split_sizes=self.recv_splits,
                                input_split_sizes=self.send_splits, group=self.group)
         return recv
+
+    def local_block(self):
+        """(rowPtr, global column ids, values) of this rank's rows, for building further operators
+        over the same shard without extracting it again (needs keep_global_columns())."""
+        return self.rowPtr, self._colIdx_global, self.val
+
+    def pull_lists(self):
+        """Per chunk of the pull transport: (position of the chunk in the compact operand, list
+        positions where each owner's rows start, row ids inside the owners' blocks)."""
+        out = []
+        for base, cnt, recv_splits, _, want_rows in self.chunk_plan:
+            first = [0]
+            for c in recv_splits:
+                first.append(first[-1] + c)
+            out.append((base, first, want_rows))
+        return out
 
     def _planned_spmm(self, rowPtr=None):
         """The CUDA operator with the configuration the decider picks for the row-length statistics
@@ -466,6 +551,10 @@ class ShardedSpMM:
         dim = B_shard.shape[1]
         if out is None:
             out = torch.empty(self.local_rows, dim, dtype=B_shard.dtype, device=B_shard.device)
+        if self.transport == "pull":
+            if dim % 4 != 0 or self._side is None:
+                raise ValueError("the pull transport needs CUDA devices and a dim that is a multiple of 4")
+            return self._forward_pull(B_shard, out)
         if self.exchange == "needed":
             self.local_spmm(out, self._exchange_needed(B_shard), self.rowPtr, self.colIdx, self.val)
             return out

@@ -354,3 +354,109 @@ def scaleout_spmm(scale=24, nnz=512_000_000, dim=128, seed=51, iters=5, warmup=2
             "compulsory_bytes_global": by, "spmm_replicated_gbs_global": round(by / ms_rep / 1e6, 1),
             "fp64_rows_checked": int(rows.numel()), "fp64_worst_error_over_bound": round(fp64_worst, 3),
             "fp64_largest_checked_element_offset": fp64_max_offset}
+
+
+def scaleout_brief(scale=24, nnz=512_000_000, dim=128, seed=51, iters=5, warmup=2, rank=0, world=1,
+                   device="cuda:0", row_chunks=4):
+    """The three strong-scaling curves of the row-sharded SpMM that the benchmark line carries at
+    every GPU count (same global R-MAT matrix and dense operand as :func:`scaleout_spmm`):
+
+    * ``replicated``  every rank already holds the whole dense operand: the local SpMM alone;
+    * ``allgather``   one NCCL all-gather of the dense row blocks, then the SpMM;
+    * ``exchange``    only the rows a shard references, fetched by the pull kernel from the owners'
+                      peer-mapped blocks in ``row_chunks`` chunks, the product of a chunk running
+                      beside the fetch of the next (``needed_pipelined`` / ``pull``); the same in one
+                      piece (``needed`` / ``pull``) and its two legs alone are reported beside it.
+
+    Times are CUDA-event times on the launching stream, maximum over ranks.  The replicated product
+    is checked on sampled rows against fp64 dense algebra, the other forms against it.
+    """
+    import torch.distributed as dist
+    from .shard import ShardedSpMM
+
+    dev = torch.device(device)
+    m = synth.rmat(scale, nnz, seed=seed, device=dev)
+    n = m.n_rows
+    sh = ShardedSpMM(m.rowPtr, m.colIdx, m.val, n, rank, world, device=dev)
+    a, b = int(m.rowPtr[sh.lo]), int(m.rowPtr[sh.hi])
+    cols_global = m.colIdx[a:b].clone()
+    sh.keep_global_columns(cols_global)
+    common = dict(row_bounds=sh.row_bounds, device=dev, local_block=(sh.rowPtr, cols_global, sh.val))
+    notes = {}
+    try:
+        sh_pull = ShardedSpMM(m.rowPtr, m.colIdx, m.val, n, rank, world, exchange="needed", transport="pull", **common)
+        sh_pipe = ShardedSpMM(m.rowPtr, m.colIdx, m.val, n, rank, world, exchange="needed_pipelined",
+                              transport="pull", row_chunks=row_chunks, **common)
+        src = sh_pull.symmetric_input(dim)  # peer-mapped blocks, where a producer would leave its rows
+        src_pipe = sh_pipe.symmetric_input(dim)
+        transport = "pull"
+    except Exception as ex:  # peer-mapped memory unavailable: the NCCL all-to-all forms stand in
+        notes["pull_unavailable"] = "%s: %s" % (type(ex).__name__, ex)
+        sh_pull = ShardedSpMM(m.rowPtr, m.colIdx, m.val, n, rank, world, exchange="needed", **common)
+        sh_pipe = ShardedSpMM(m.rowPtr, m.colIdx, m.val, n, rank, world, exchange="needed_pipelined",
+                              row_chunks=row_chunks, **common)
+        transport = "nccl"
+    nnz_total = m.nnz
+    del m
+    torch.cuda.empty_cache()
+    B_full = synth.dense_uniform(n, dim, seed + 1, dev)
+    c0, c1 = sh.my_cols
+    B_shard = B_full[c0:c1].clone()
+    out_rep = torch.empty(sh.local_rows, dim, device=dev)
+    out = torch.empty(sh.local_rows, dim, device=dev)
+
+    def timed(fn):
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / iters], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    res = {"world": world, "n": n, "nnz": nnz_total, "dim": dim, "row_chunks": row_chunks, "transport": transport}
+    res["replicated_ms"] = timed(lambda: sh.forward_replicated(B_full, out_rep))
+    rows = sample_rows(sh.rowPtr, 40, seed)
+    res["fp64_worst_error_over_bound"] = round(check_rows_fp64(sh.rowPtr, cols_global, sh.val, B_full, out_rep, rows,
+                                                               "row shard %d of %d" % (rank, world)), 3)
+    res["fp64_rows_checked"] = int(rows.numel())
+    res["fp64_largest_checked_element_offset"] = int(rows.max()) * dim
+    del B_full
+    tol = dict(rtol=1e-4, atol=2e-3)  # hub rows: 1e5 terms, pieces added in a different order per launch
+    res["allgather_ms"] = timed(lambda: sh.forward(B_shard, out))
+    torch.testing.assert_close(out, out_rep, **tol)
+    if transport == "pull":
+        src.copy_(B_shard)
+        src_pipe.copy_(B_shard)
+    else:
+        src = src_pipe = B_shard
+    out.fill_(float("nan"))
+    res["exchange_one_piece_ms"] = timed(lambda: sh_pull.forward(src, out))
+    torch.testing.assert_close(out, out_rep, **tol)
+    out.fill_(float("nan"))
+    res["exchange_ms"] = timed(lambda: sh_pipe.forward(src_pipe, out))
+    torch.testing.assert_close(out, out_rep, **tol)
+    res["needed_rows_fraction"] = round(sh_pull.n_needed / n, 4)
+    if transport == "pull":
+        # the two legs of the one-piece form alone: the fetch, and the product on the compact operand
+        base, first, want_rows = sh_pull.pull_lists()[0]
+        _, peers, _ = sh_pull._peer_blocks(dim, B_shard)
+        recv = sh_pull._receive_buffer(max(1, sh_pull.n_needed), dim, B_shard)
+        rot = first[(rank + 1) % world] % max(1, sh_pull.n_needed)
+        res["fetch_alone_ms"] = timed(lambda: ops.pull_rows(recv, peers, first, want_rows, rotate=rot, ctas=sh_pull.pull_ctas))
+        res["fetch_alone_all_sms_ms"] = timed(lambda: ops.pull_rows(recv, peers, first, want_rows, rotate=rot, ctas=1184))
+        res["fetched_bytes"] = int(sh_pull.n_needed) * dim * 4
+        res["spmm_on_fetched_rows_ms"] = timed(lambda: sh_pull.local_spmm(out, recv, sh_pull.rowPtr, sh_pull.colIdx, sh_pull.val))
+    res.update(notes)
+    for k in list(res):
+        if k.endswith("_ms"):
+            res[k] = round(res[k], 4)
+    return res

@@ -10,7 +10,8 @@ import torch
 pytestmark = pytest.mark.gpu
 
 MODES = [("allgather", "nccl", 1), ("allgather", "nccl", 4), ("needed", "nccl", 1), ("pipelined", "nccl", 1),
-         ("needed_pipelined", "nccl", 1), ("pipelined", "copy_engine", 1)]
+         ("needed_pipelined", "nccl", 1), ("pipelined", "copy_engine", 1), ("needed", "pull", 1),
+         ("needed_pipelined", "pull", 1)]
 
 
 def _worker(rank, world, port, q):
@@ -38,7 +39,7 @@ def _worker(rank, world, port, q):
             op = ShardedSpMM(m.rowPtr, m.colIdx, m.val, n, rank, world, device=dev, exchange=exchange,
                              transport=transport, dim_chunks=dim_chunks, row_chunks=3)
             src = shard_of_B
-            if transport == "copy_engine":
+            if transport in ("copy_engine", "pull"):
                 src = op.symmetric_input(dim)
                 src.copy_(shard_of_B)
             for _ in range(2):  # the second call reuses buffers, fences and streams of the first

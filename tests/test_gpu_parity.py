@@ -600,3 +600,56 @@ def test_agnn_fused_rejects_what_it_cannot_run(dev):
         ops.agnn_fused(X, X, rp, ci)
     with pytest.raises(RuntimeError):
         ops.agnn_fused(X.cpu(), X.cpu(), rp, ci)
+
+
+# ----------------------------------------------------------------------------- row pull (exchange step)
+@pytest.mark.parametrize("dim", [4, 64, 128, 132, 260])
+def test_pull_rows_copies_the_listed_rows(dev, dim):
+    """pspmm_pull_rows with several source blocks (all on this GPU here; on a node they are the
+    peers' mapped blocks): every listed row lands at its list position, for every rotation and CTA
+    budget, strided sources and destination included; bit-exact (a copy)."""
+    from paramspmm_ae_b200 import _lib, ops
+    g = torch.Generator().manual_seed(dim)
+    sizes = [700, 1, 0, 1300, 64]
+    wide = [torch.rand(s, dim + 4, generator=g).to(dev) for s in sizes]
+    blocks = [w[:, :dim] for w in wide]           # row stride dim + 4
+    counts = [333, 1, 0, 1300, 7]
+    rows, first = [], [0]
+    for s, c in zip(sizes, counts):
+        rows.append(torch.sort(torch.randperm(s, generator=g)[:c]).values if c else torch.empty(0, dtype=torch.long))
+        first.append(first[-1] + c)
+    rows_d = torch.cat(rows).int().to(dev)
+    want = torch.cat([b[r.to(dev)] for b, r in zip(blocks, rows)])
+    n = first[-1]
+    for rotate, ctas in ((0, 0), (5, 1), (first[3], 3), (n - 1, 1000)):
+        dst = torch.full((n, dim + 8), float("nan"), device=dev)[:, :dim]
+        ops.pull_rows(dst, blocks, first, rows_d, rotate=rotate, ctas=ctas)
+        assert torch.equal(dst, want)
+    # nothing to copy, and the argument checks
+    ops.pull_rows(torch.empty(0, dim, device=dev), blocks[:1], [0, 0], torch.empty(0, dtype=torch.int32, device=dev))
+    with pytest.raises(RuntimeError):
+        ops.pull_rows(torch.empty(n, dim, device=dev), blocks, first[:-1], rows_d)
+    with pytest.raises(_lib.PspmmError):
+        ops.pull_rows(torch.empty(n, dim, device=dev), blocks, first, rows_d, rotate=n)
+
+
+@pytest.mark.parametrize("exchange,row_chunks", [("needed", 1), ("needed_pipelined", 3)])
+def test_pull_transport_single_rank(dev, oracle, mats, exchange, row_chunks):
+    """The pull transport with one rank (the owner's block is this GPU's own buffer): same product
+    as the plain kernel, twice in a row (buffers, streams and events are reused)."""
+    from paramspmm_ae_b200.shard import ShardedSpMM
+    m = mats["rmat"]
+    rp, ci, v = m.numpy()
+    d = m.to(dev)
+    B = dense(m.n_cols, 64, 31)
+    want = oracle.spmm_csr(rp, ci, v, B.numpy())
+    op = ShardedSpMM(d.rowPtr, d.colIdx, d.val, m.n_cols, 0, 1, device=dev, exchange=exchange, transport="pull",
+                     row_chunks=row_chunks)
+    Bd = B.to(dev)
+    for _ in range(2):
+        out = op.forward(Bd, torch.full((m.n_rows, 64), float("nan"), device=dev))
+        torch.cuda.synchronize()
+        close(out, want)
+    src = op.symmetric_input(64)   # a producer writes the block in place: no staging copy
+    src.copy_(Bd)
+    close(op.forward(src), want)

@@ -173,3 +173,65 @@ def test_pipelined_exchange_single_rank(row_chunks):
     assert np.allclose(got.numpy(), want, rtol=1e-5, atol=1e-5)
     with pytest.raises(ValueError):
         op.forward(synth.dense_uniform(m.n_cols, 10, 4))
+
+
+def _pull_worker(rank, world, port, exchange, row_chunks, q):
+    """The row lists of the pull transport (the CUDA copy kernel consumes them as they are): every
+    rank gathers all blocks of the dense operand (what peer-mapped memory gives it on GPUs), fills its
+    compact operand from (owner, row) exactly as the lists say, and the block products must give the
+    global product."""
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from oracle import oracle as orc
+        m = synth.with_empty_rows(synth.powerlaw_graph(1201, 9000, seed=7), every=4)
+        B = synth.dense_uniform(m.n_cols, 8, 5)
+        op = shard.ShardedSpMM(m.rowPtr, m.colIdx, m.val, m.n_cols, rank, world, device="cpu",
+                               local_spmm=lambda *a, **k: None, exchange=exchange, transport="pull",
+                               row_chunks=row_chunks)
+        blocks = [B[int(op.col_bounds[q_]): int(op.col_bounds[q_ + 1])] for q_ in range(world)]
+        recv = torch.full((max(1, op.n_needed), 8), float("nan"))
+        lists = op.pull_lists()
+        end = 0
+        for base, first, rows in lists:
+            assert base == end and first[0] == 0 and len(first) == world + 1 and rows.dtype == torch.int32
+            assert all(a <= b for a, b in zip(first, first[1:])) and first[-1] == rows.numel()
+            for s in range(world):
+                r = rows[first[s]: first[s + 1]].long()
+                assert r.numel() == 0 or (int(r.min()) >= 0 and int(r.max()) < blocks[s].shape[0])
+                assert bool((r[1:] > r[:-1]).all())  # ascending and distinct inside an owner
+                recv[base + first[s]: base + first[s + 1]] = blocks[s][r]
+            end += first[-1]
+        assert end == op.n_needed and not bool(torch.isnan(recv[: op.n_needed]).any())
+        want = orc.spmm_csr(*m.numpy(), B.numpy())[op.lo: op.hi]
+        if exchange == "needed":
+            got = orc.spmm_csr(op.rowPtr.numpy(), op.colIdx.numpy(), op.val.numpy(), recv.numpy())
+        else:
+            got = sum(orc.spmm_csr(rp.numpy(), ci.numpy(), v.numpy(), recv.numpy()) for rp, ci, v in op.blocks)
+        q.put((rank, bool(np.allclose(got, want, rtol=1e-5, atol=1e-5)), op.n_needed))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("exchange,row_chunks", [("needed", 1), ("needed_pipelined", 3)])
+@pytest.mark.parametrize("world", [2, 3])
+def test_pull_transport_row_lists_gloo(world, exchange, row_chunks):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_pull_worker, args=(r, world, port, exchange, row_chunks, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=120) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert all(r[1] for r in res), res
+    assert all(0 < r[2] <= 1201 for r in res)
+
+
+def test_pull_transport_rejects_other_exchanges():
+    m = synth.uniform_rows(20, 3, seed=1)
+    with pytest.raises(ValueError):
+        shard.ShardedSpMM(m.rowPtr, m.colIdx, m.val, 20, 0, 1, device="cpu", exchange="allgather", transport="pull")
