@@ -1,51 +1,87 @@
 #!/usr/bin/env python3
 """Measured configuration sweep: the stand-in for the reference's ``profile_engine`` /
 ``training_data_gen`` (PCSR.py:672-823), which time every <representation, CF, blkWarpNum>
-on a matrix collection and label each (matrix, dim) with the fastest.
+on a matrix collection and label each (matrix, dim) with the fastest, and for the hold-out
+evaluation of its decider (models/rnd_tree.ipynb: accuracy and "normalised performance" of the
+predicted configuration against the best one on matrices the forests were not trained on).
 
-Here the swept space is that of the sm_100a kernels: PCSR split on/off and partition length,
-block height (vec_size 1 or 2), lanes per row (rows per warp), rows per lane group, CTA size.
-For every (row-length regime, dim) the fastest configuration is written to a JSON table that
-``paramspmm_ae_b200.decider`` loads; all raw timings are kept next to it.
+The swept space is that of the sm_100a kernels: PCSR split on/off and partition length, block
+height (vec_size 1 or 2), lanes per row (rows per warp), rows per lane group, gather depth, CTA
+size, column tiles; for banded matrices the window kernel's shape.
 
-    python -m paramspmm_ae_b200.sweep --out sweep_raw.json --table paramspmm_ae_b200/config_table.json
+    python -m paramspmm_ae_b200.sweep fit     --table paramspmm_ae_b200/config_table.json
+    python -m paramspmm_ae_b200.sweep window  --table paramspmm_ae_b200/config_table.json
+    python -m paramspmm_ae_b200.sweep holdout --out paramspmm_ae_b200/decider_holdout.json
 
-Each candidate is verified against the plain-CSR result of the default configuration before
-it is timed (the reference verifies each candidate against torch.sparse.mm, PCSR.py:759-770).
+``fit`` times every candidate on the fitting matrices of each row-length regime and writes, per
+(regime, dim), the configuration with the smallest summed time.  ``window`` does the same for the
+window kernel on a banded matrix and records the dims at which it beats the gather kernel.
+``holdout`` takes matrices that ``fit`` never sees (other generators' parameters, sizes and seeds),
+times for each (matrix, dim) the whole candidate space and the configuration the table gives, and
+records table-choice time / best time.  Each candidate is verified against the plain-CSR result of
+the default configuration before it is timed (the reference verifies each candidate against
+torch.sparse.mm, PCSR.py:759-770).
 """
 from __future__ import annotations
 
 import argparse
 import itertools
 import json
+import os
 import time
 
 import torch
 
 from . import _lib, decider, ops, synth
 
+ALL_REGIMES = ["short_even", "short_skewed", "medium_even", "medium_skewed", "long_even", "long_skewed"]
 
-def regime_matrices(n, device, which):
+
+def fitting_matrices(n, device, which):
+    """Matrices the table is fitted on.  Seeds and sizes differ from the benchmark's matrices
+    (bench.py: seeds 21-23 at 10^6 rows) and from the hold-out set below."""
     out = {}
     if "short_even" in which:
-        out["short_even"] = [("uniform", synth.uniform_rows(n, 16, seed=21, device=device)),
-                             ("banded", synth.banded_rows(n, 16, 32, seed=22, device=device))]
+        out["short_even"] = [("uniform16", synth.uniform_rows(n, 16, seed=121, device=device)),
+                             ("banded16", synth.banded_rows(n, 16, 32, seed=122, device=device))]
     if "short_skewed" in which:
-        out["short_skewed"] = [("rmat", synth.rmat(max(1, (n - 1).bit_length()), 16 * n, n=n, seed=23, device=device))]
+        out["short_skewed"] = [("rmat16", synth.rmat(max(1, (n - 1).bit_length()), 16 * n, n=n, seed=123, device=device)),
+                               ("powerlaw12", synth.powerlaw_graph(n // 2, (n // 2) * 6, seed=124, device=device))]
+    if "medium_even" in which:
+        out["medium_even"] = [("uniform64", synth.uniform_rows(n // 4, 64, seed=125, device=device))]
     if "medium_skewed" in which:
-        out["medium_skewed"] = [("powerlaw50", synth.powerlaw_graph(n // 4, (n // 4) * 25, seed=31, device=device))]
+        out["medium_skewed"] = [("powerlaw50", synth.powerlaw_graph(n // 4, (n // 4) * 25, seed=131, device=device))]
+    if "long_even" in which:
+        out["long_even"] = [("uniform256", synth.uniform_rows(n // 16, 256, seed=126, device=device))]
     if "long_skewed" in which:
-        out["long_skewed"] = [("powerlaw490", synth.powerlaw_graph(232965 if n >= 1_000_000 else n // 8,
-                                                                   (232965 if n >= 1_000_000 else n // 8) * 245,
-                                                                   seed=41, device=device))]
+        k = 232965 if n >= 1_000_000 else n // 8
+        out["long_skewed"] = [("powerlaw490", synth.powerlaw_graph(k, k * 245, seed=141, device=device))]
     return out
 
 
-VEC1_ONLY = False
-CTA_THREADS = (256,)
+def holdout_matrices(device, scale=1.0):
+    """Fourteen matrices no fit ever sees: other sizes, mean degrees 4..600, R-MAT and Chung-Lu
+    exponents, band widths inside and outside the window kernel's reach, all six regimes."""
+    s = lambda x: max(2048, int(x * scale))
+    return [
+        ("uniform_k8", synth.uniform_rows(s(500_000), 8, seed=201, device=device)),
+        ("uniform_k4", synth.uniform_rows(s(1_200_000), 4, seed=202, device=device)),
+        ("uniform_k40", synth.uniform_rows(s(300_000), 40, seed=203, device=device)),
+        ("uniform_k200", synth.uniform_rows(s(60_000), 200, seed=204, device=device)),
+        ("banded_k12_bw48", synth.banded_rows(s(700_000), 12, 48, seed=205, device=device)),
+        ("banded_k48_bw64", synth.banded_rows(s(200_000), 48, 64, seed=206, device=device)),
+        ("banded_k16_bw200", synth.banded_rows(s(800_000), 16, 200, seed=207, device=device)),
+        ("rmat_deg8", synth.rmat(19, s(4_000_000), seed=208, device=device)),
+        ("rmat_deg46", synth.rmat(18, s(12_000_000), seed=209, device=device)),
+        ("rmat_flat_deg23", synth.rmat(20, s(24_000_000), a=0.45, b=0.22, c=0.22, seed=210, device=device)),
+        ("chunglu_g2.1_deg11", synth.powerlaw_graph(s(400_000), s(2_000_000), gamma=2.1, seed=211, device=device)),
+        ("chunglu_g3.0_deg11", synth.powerlaw_graph(s(600_000), s(3_000_000), gamma=3.0, seed=212, device=device)),
+        ("chunglu_g2.5_deg61", synth.powerlaw_graph(s(150_000), s(4_500_000), gamma=2.5, seed=213, device=device)),
+        ("chunglu_g2.1_deg600", synth.powerlaw_graph(s(50_000), s(15_000_000), gamma=2.1, seed=214, device=device)),
+    ]
 
 
-def candidates(dim, regime, quick):
+def candidates(dim, regime, quick=False, vecs=(1, 2), cta_threads=(64, 128, 256)):
     vw = 4 if dim % 4 == 0 else (2 if dim % 2 == 0 else 1)
     nvec = dim // vw
     top = 1
@@ -60,13 +96,18 @@ def candidates(dim, regime, quick):
         grans = [0, 32, 64, 128] if not long_rows else [0, 64, 128, 256, 512]
     else:
         grans = [0]
-    vecs = (1,) if (quick or VEC1_ONLY) else (1, 2)
-    tiles = (0, 128) if dim > 128 else (0,)
-    for vec, gran, lpr, rpg, mlp, thr, tile in itertools.product(vecs, grans, lprs, rpgs, mlps, CTA_THREADS, tiles):
-        if vec != 1 and mlp != 8:
-            continue  # block kernels are built with one gather depth
-        if tile and (vec != 1 or lpr != 32):
-            continue  # column ranges of 128: one 16-byte slice per lane of a full warp
+    if quick:
+        vecs, cta_threads = (1,), (256,)
+    tiles = [0] + [t for t in (32, 64, 128) if t < dim and dim % 4 == 0]
+    for vec, gran, lpr, rpg, mlp, thr, tile in itertools.product(vecs, grans, lprs, rpgs, mlps, cta_threads, tiles):
+        if vec != 1 and (mlp != 8 or thr != 256 or tile):
+            continue  # block kernels are built with one gather depth; measured at one CTA size, untiled
+        if thr == 64 and lpr == 32 and rpg == 2:
+            continue
+        if tile and (lpr * vw > tile or thr != 256 or rpg != 4):
+            continue  # column ranges narrower than a lane group make no sense; tiles measured at one shape
+        if tile and tile < 128 and skew:
+            continue  # narrow column ranges re-read A for every range: only the even regimes try them
         yield {"vec_size": vec, "if_split": int(gran > 0), "granularity": gran or None,
                "lanes_per_row": lpr, "vec_width": vw, "rows_per_group": rpg, "cta_threads": thr,
                "gather_batch": mlp, "col_tile": tile}
@@ -93,87 +134,222 @@ class Layouts:
             rp, ci, v = self.cache["b", vec]
         tr = None
         if gran:
-            rps, tr = ops.split_csr(rp.cpu(), gran)
-            rp, tr = rps.to(self.dev), tr.to(self.dev)
+            rp, tr = ops.split_csr_device(rp, gran)
         self.cache[key] = (rp, ci, v, tr)
         return self.cache[key]
 
 
-def run(args):
-    global VEC1_ONLY, CTA_THREADS
-    VEC1_ONLY = bool(getattr(args, "vec1_only", False))
-    CTA_THREADS = tuple(getattr(args, "cta_threads", None) or (256,))
+class Timer:
+    """Times candidates on one (matrix, dim): verification against the default plain-CSR product
+    first, then back-to-back launches between CUDA events."""
+
+    def __init__(self, m, dim, dev, warmup, iters):
+        # matrices far larger than the benchmark's 1.6e7 entries get proportionally fewer timed launches
+        iters = max(5, int(iters * min(1.0, 2.0e7 / max(1, m.nnz))))
+        self.m, self.dim, self.dev, self.warmup, self.iters = m, dim, dev, warmup, iters
+        self.lay = Layouts(m, dev)
+        self.B = synth.dense_uniform(m.n_cols, dim, 1000 + dim, dev)
+        self.ref = ops.csr_spmm(self.B, m.rowPtr, m.colIdx, m.val, 1, 8)
+        # hub rows sum thousands of terms in a different order: the floor grows with the row's length
+        ln = (m.rowPtr[1:] - m.rowPtr[:-1]).double()
+        self.tol = (1e-5 * self.ref.abs() + 1e-4 * torch.clamp(ln / 256.0, min=1.0)[:, None]).float()
+        self.max_row = int(ln.max())
+
+    def ms(self, cand):
+        m, dim = self.m, self.dim
+        if not cand.get("if_split") and self.max_row > 4096 and not cand.get("window_rows"):
+            return None  # one lane group per hub row would take milliseconds
+        V = cand.get("vec_size", 1)
+        rp, ci, v, tr = self.lay.get(V, cand.get("granularity") if cand.get("if_split") else None)
+        nbr = (m.n_rows + V - 1) // V
+        out = torch.full((nbr * V, dim), float("nan"), device=self.dev)
+        cfg = _lib.make_cfg(**{k: int(cand.get(k, 0) or 0) for k in
+                               ("lanes_per_row", "vec_width", "cta_threads", "rows_per_group", "gather_batch",
+                                "col_tile", "window_rows", "cta_rows")})
+        ops.spmm_into(out, self.B, rp, ci, v, target_row=tr, V=V, n_out_rows=nbr, cfg=cfg)
+        bad = int(((out[: m.n_rows] - self.ref).abs() > self.tol).sum())
+        if bad or bool(torch.isnan(out[: m.n_rows]).any()):
+            raise RuntimeError("candidate %s disagrees with the default on dim %d (%d elements)" % (cand, dim, bad))
+        return ops.spmm_time_ms(self.B, rp, ci, v, tr, V, cfg=cfg, warmup=self.warmup, iters=self.iters, out=out)
+
+
+def _load_table(path):
+    if path and os.path.exists(path):
+        with open(path) as f:
+            return json.load(f)
+    return {"version": 2, "entries": {"spmm": {}}}
+
+
+def _save_table(path, table, note):
+    table["version"] = 2
+    table.setdefault("sources", {}).update(note)
+    with open(path, "w") as f:
+        json.dump(table, f, indent=1, sort_keys=True)
+
+
+def fit(args):
     dev = torch.device("cuda:0")
     _lib.lib()
-    which = args.regimes
-    mats = regime_matrices(args.rows, dev, which)
-    results = []
-    best = {}
-    t_start = time.time()
+    mats = fitting_matrices(args.rows, dev, args.regimes)
+    raw, best = [], {}
+    t0 = time.time()
     for regime, lst in mats.items():
         for dim in args.dims:
             agg = {}
             for mname, m in lst:
-                lay = Layouts(m, dev)
-                B = synth.dense_uniform(m.n_cols, dim, 1000 + dim, dev)
-                ref = ops.csr_spmm(B, m.rowPtr, m.colIdx, m.val, 1, 8)
-                tol = 1e-4 + 1e-5 * ref.abs()
-                max_row = int((m.rowPtr[1:] - m.rowPtr[:-1]).max())
+                tm = Timer(m, dim, dev, args.warmup, args.iters)
                 for cand in candidates(dim, regime, args.quick):
-                    if not cand["if_split"] and max_row > 4096:
-                        continue  # one lane group per hub row would take milliseconds
-                    rp, ci, v, tr = lay.get(cand["vec_size"], cand["granularity"])
-                    V = cand["vec_size"]
-                    nbr = (m.n_rows + V - 1) // V
-                    out = torch.empty(nbr * V, dim, device=dev)
-                    cfg = _lib.make_cfg(lanes_per_row=cand["lanes_per_row"], vec_width=cand["vec_width"],
-                                        cta_threads=cand["cta_threads"], rows_per_group=cand["rows_per_group"],
-                                        gather_batch=cand["gather_batch"], col_tile=cand.get("col_tile", 0))
-                    ops.spmm_into(out, B, rp, ci, v, target_row=tr, V=V, n_out_rows=nbr, cfg=cfg)
-                    # hub rows sum thousands of terms in a different order: scale the floor
-                    bad = ((out[: m.n_rows] - ref).abs() > tol * 50).sum().item()
-                    if bad:
-                        raise RuntimeError("candidate %s disagrees with the default on %s dim %d (%d elements)"
-                                           % (cand, mname, dim, bad))
-                    ms = ops.spmm_time_ms(B, rp, ci, v, tr, V, cfg=cfg, warmup=args.warmup, iters=args.iters,
-                                          out=out)
-                    rec = dict(cand, regime=regime, matrix=mname, dim=dim, ms=ms,
-                               gflops=2.0 * m.nnz * dim / ms / 1e6)
-                    results.append(rec)
-                    key = json.dumps(cand, sort_keys=True)
-                    agg.setdefault(key, []).append(ms)
-                del B, ref
-            # fastest candidate by summed time over the regime's matrices
-            k = min(agg, key=lambda kk: sum(agg[kk]))
+                    ms = tm.ms(cand)
+                    if ms is None:
+                        continue
+                    raw.append(dict(cand, regime=regime, matrix=mname, dim=dim, ms=ms))
+                    agg.setdefault(json.dumps(cand, sort_keys=True), []).append(ms)
+                del tm
+            full = {k: v for k, v in agg.items() if len(v) == len(lst)}  # timed on every matrix of the regime
+            k = min(full, key=lambda kk: sum(full[kk]))
             e = json.loads(k)
-            e["ms_sum"] = sum(agg[k])
+            e["ms_sum"] = sum(full[k])
             best.setdefault(regime, {})[str(dim)] = e
-            print("%-14s dim %3d best %s  (%.1f s elapsed)" % (regime, dim, e, time.time() - t_start), flush=True)
-    with open(args.out, "w") as f:
-        json.dump({"rows": args.rows, "iters": args.iters, "results": results}, f)
+            print("%-14s dim %3d best %s  (%.0f s)" % (regime, dim, e, time.time() - t0), flush=True)
+    if args.raw:
+        with open(args.raw, "w") as f:
+            json.dump({"rows": args.rows, "iters": args.iters, "results": raw}, f)
     if args.table:
-        table = {"version": 1,
-                 "source": "python -m paramspmm_ae_b200.sweep, rows=%d iters=%d, back-to-back launches, B200" % (args.rows, args.iters),
-                 "entries": {"spmm": best}}
-        # regimes that were not measured inherit from the nearest measured one
-        with open(args.table, "w") as f:
-            json.dump(table, f, indent=1, sort_keys=True)
+        table = _load_table(args.table)
+        table.setdefault("entries", {}).setdefault("spmm", {}).update(best)
+        _save_table(args.table, table, {"fit:" + ",".join(sorted(best)): "python -m paramspmm_ae_b200.sweep fit, rows=%d "
+                                        "iters=%d, back-to-back launches, B200; fitting matrices: %s"
+                                        % (args.rows, args.iters, {r: [n for n, _ in l] for r, l in mats.items()})})
     return best
 
 
+WINDOW_SHAPES = ((96, 32), (128, 64), (160, 96), (192, 128), (256, 160), (256, 192))
+
+
+def window(args):
+    """Window kernel vs the gather kernel on a banded fitting matrix, per dim: the fastest window
+    shape is recorded where it beats the table's gather configuration by at least 3 %."""
+    dev = torch.device("cuda:0")
+    _lib.lib()
+    m = synth.banded_rows(args.rows, 16, 32, seed=122, device=dev)
+    st = decider.row_stats(m.rowPtr, m.colIdx)
+    entries, raw = {}, []
+    for dim in args.dims:
+        if dim % 4:
+            continue
+        tm = Timer(m, dim, dev, args.warmup, args.iters)
+        gather = dict(decider.choose(dict(st, window_hit=0.0), dim))
+        g_ms = tm.ms(gather)
+        best = None
+        for (wr, cr), lpr in itertools.product(WINDOW_SHAPES, (16, 32)):
+            if lpr == 32 and dim < 128 and dim != 96:
+                continue
+            if wr * lpr * 16 > 200 * 1024:
+                continue
+            cand = {"window_rows": wr, "cta_rows": cr, "lanes_per_row": lpr, "vec_width": 4}
+            ms = tm.ms(cand)
+            raw.append(dict(cand, dim=dim, ms=ms, gather_ms=g_ms))
+            if best is None or ms < best[0]:
+                best = (ms, cand)
+        print("window dim %3d: gather %.4f ms, window %.4f ms %s" % (dim, g_ms, best[0], best[1]), flush=True)
+        if best[0] < 0.97 * g_ms:
+            entries[str(dim)] = dict(best[1], ms=best[0], gather_ms=g_ms)
+        del tm
+    if args.raw:
+        with open(args.raw, "w") as f:
+            json.dump({"rows": args.rows, "results": raw}, f)
+    if args.table:
+        table = _load_table(args.table)
+        table.setdefault("entries", {})["window"] = entries
+        _save_table(args.table, table, {"window": "python -m paramspmm_ae_b200.sweep window, rows=%d iters=%d, banded "
+                                                  "16 entries per row, half bandwidth 32, seed 122" % (args.rows, args.iters)})
+    return entries
+
+
+def holdout(args):
+    dev = torch.device("cuda:0")
+    _lib.lib()
+    decider.load_table(args.table)
+    rows_out = []
+    t0 = time.time()
+    for name, m in holdout_matrices(dev, args.scale):
+        st = decider.row_stats(m.rowPtr, m.colIdx)
+        reg = decider.regime(st)
+        for dim in args.dims:
+            tm = Timer(m, dim, dev, args.warmup, args.iters)
+            plan = decider.choose(st, dim)
+            t_ms = tm.ms(dict(plan))
+            best = (t_ms, "table")
+            n_c = 0
+            space = [c for c in candidates(dim, reg)]
+            if st["window_hit"] >= 0.5 and dim % 4 == 0 and dim >= 32:
+                space += [{"window_rows": wr, "cta_rows": cr, "lanes_per_row": 32 if dim >= 128 else 16, "vec_width": 4}
+                          for wr, cr in WINDOW_SHAPES]
+            for cand in space:
+                ms = tm.ms(cand)
+                if ms is None:
+                    continue
+                n_c += 1
+                if ms < best[0]:
+                    best = (ms, cand)
+            rec = {"matrix": name, "n_rows": m.n_rows, "nnz": m.nnz, "regime": reg, "window_hit": round(st["window_hit"], 3),
+                   "dim": dim, "table_ms": round(t_ms, 5), "best_ms": round(best[0], 5),
+                   "normalised_performance": round(best[0] / t_ms, 4), "candidates": n_c,
+                   "table_choice": {k: plan[k] for k in ("if_split", "vec_size", "granularity", "path") if k in plan},
+                   "table_kernel": plan.kernel_cfg(),
+                   "best": best[1]}
+            rows_out.append(rec)
+            print("%-20s %-14s dim %3d table %.4f best %.4f  ratio %.3f  (%.0f s)"
+                  % (name, reg, dim, t_ms, best[0], best[0] / t_ms, time.time() - t0), flush=True)
+            del tm
+    ratios = torch.tensor([r["normalised_performance"] for r in rows_out], dtype=torch.float64)
+    by_regime = {}
+    for r in rows_out:
+        by_regime.setdefault(r["regime"], []).append(r["normalised_performance"])
+    summary = {"pairs": len(rows_out), "mean_normalised_performance": round(float(ratios.mean()), 4),
+               "geomean_normalised_performance": round(float(ratios.log().mean().exp()), 4),
+               "worst": round(float(ratios.min()), 4),
+               "share_within_5_percent": round(float((ratios >= 0.95).double().mean()), 4),
+               "per_regime_mean": {k: round(sum(v) / len(v), 4) for k, v in sorted(by_regime.items())},
+               "vec_size_2_best_in": sum(1 for r in rows_out if isinstance(r["best"], dict) and r["best"].get("vec_size") == 2),
+               "window_best_in": sum(1 for r in rows_out if isinstance(r["best"], dict) and r["best"].get("window_rows"))}
+    out = {"what": "table-choice time vs the fastest of the whole candidate space, per (hold-out matrix, dim); "
+                   "normalised_performance = best_ms / table_ms (1 = the table picked the fastest); matrices, sizes "
+                   "and seeds are disjoint from the fitting set; back-to-back launches, %d iterations, B200" % args.iters,
+           "dims": list(args.dims), "summary": summary, "rows": rows_out}
+    with open(args.out, "w") as f:
+        json.dump(out, f, indent=1)
+    print(json.dumps(summary))
+    return out
+
+
 def main():
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--rows", type=int, default=1_000_000)
-    ap.add_argument("--dims", type=int, nargs="*", default=list(range(16, 257, 16)))
-    ap.add_argument("--regimes", nargs="*", default=["short_even", "short_skewed"])
-    ap.add_argument("--iters", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--quick", action="store_true")
-    ap.add_argument("--vec1-only", action="store_true", help="skip the 2 x 1 block layout")
-    ap.add_argument("--cta-threads", type=int, nargs="*", default=[256], help="CTA sizes to try (128, 256)")
-    ap.add_argument("--out", default="sweep_raw.json")
-    ap.add_argument("--table", default=None)
-    run(ap.parse_args())
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    sub = ap.add_subparsers(dest="cmd", required=True)
+    here = os.path.dirname(os.path.abspath(__file__))
+    table = os.path.join(here, "config_table.json")
+    p = sub.add_parser("fit")
+    p.add_argument("--rows", type=int, default=1_000_000)
+    p.add_argument("--dims", type=int, nargs="*", default=list(range(16, 257, 16)))
+    p.add_argument("--regimes", nargs="*", default=ALL_REGIMES)
+    p.add_argument("--quick", action="store_true")
+    p.add_argument("--raw", default=None, help="write every timing to this file")
+    p.add_argument("--table", default=table)
+    p = sub.add_parser("window")
+    p.add_argument("--rows", type=int, default=1_000_000)
+    p.add_argument("--dims", type=int, nargs="*", default=list(range(32, 257, 16)))
+    p.add_argument("--raw", default=None)
+    p.add_argument("--table", default=table)
+    p = sub.add_parser("holdout")
+    p.add_argument("--dims", type=int, nargs="*", default=[16, 32, 64, 128, 256])
+    p.add_argument("--scale", type=float, default=1.0, help="shrink the hold-out matrices (quick checks)")
+    p.add_argument("--table", default=table)
+    p.add_argument("--out", default=os.path.join(here, "decider_holdout.json"))
+    for q in sub.choices.values():
+        q.add_argument("--iters", type=int, default=20)
+        q.add_argument("--warmup", type=int, default=3)
+    args = ap.parse_args()
+    {"fit": fit, "window": window, "holdout": holdout}[args.cmd](args)
 
 
 if __name__ == "__main__":

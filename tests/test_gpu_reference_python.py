@@ -107,18 +107,23 @@ def test_reference_decider_loop_on_the_dropin(ref, graph, capsys):
 
 
 def test_reference_vec_size_3_operator(ref, graph, capsys):
-    """vec_size = 3 is reachable only by constructing the operator from raw tensors
-    (PCSR.py:150-169): the reference's loader builds 2 x 1 blocks only."""
+    """vec_size = 3: the reference's loader builds 2 x 1 blocks only and its raw-tensor constructor
+    rejects every 2-D value array (PCSR.py:165-166), so the branch of get_spmm_result that calls
+    vec_spmm / vec_split_spmm (:226-240) is reached here by handing 3 x 1 arrays to an operator
+    object built from the graph."""
     from paramspmm_ae_b200 import ops
     c = graph.csr_data
     rpb, cb, vb = ops.bcsr_from_csr(c.rowPtr, c.colIdx, c.val, graph.mtx_nodes, 3)
+    with pytest.raises(ValueError):
+        ref.pcsr.pcsr_spmm(None, 3, False, graph.mtx_nodes, graph.mtx_edges, rpb, cb, vb, None)
     veri = ref.veri.SpMM_verification(1, c.rowPtr, c.colIdx, c.val)
     rps, tr = ops.split_csr(rpb, 32)
     for dim in (32, 100):
         veri.reference(dim)
         for if_split, rp, t in ((False, rpb, None), (True, rps, tr)):
-            op = ref.pcsr.pcsr_spmm(None, 3, if_split, graph.mtx_nodes, graph.mtx_edges, rp, cb, vb,
-                                    t.cuda() if t is not None else None, CF=1, blkWarpNum=4)
+            op = ref.pcsr.pcsr_spmm(graph, vec_size=2, if_split=if_split, CF=1, blkWarpNum=4)
+            op.vec_size, op.rowPtr, op.colIdx, op.val = 3, rp.cuda(), cb.cuda(), vb.cuda()
+            op.target_row = t.cuda() if t is not None else None
             op.get_spmm_result(dim)
             veri.compare(op.result, "pubmed-vec3")
     capsys.readouterr()
@@ -156,9 +161,17 @@ def _dense_adjacency(g, dev):
     return A.to(dev)
 
 
-def _close(got, want, what):
+def _close_strict(got, want, what):
     # fp32 sums over a node's neighbours against fp64: 1e-5 relative, 1e-4 absolute
     torch.testing.assert_close(got.double(), want, rtol=1e-5, atol=1e-4, msg=lambda m: what + ": " + m)
+
+
+def _close_reduction(got, want, what):
+    # Weight gradients are dense fp32 products that sum over all 19,717 nodes, done by cuBLAS
+    # (torch.mm) in the reference's layers and in this package's alike: the absolute floor follows
+    # the size of the result (1e-5 of its largest element) instead of being fixed at 1e-4.
+    torch.testing.assert_close(got.double(), want, rtol=1e-5, atol=1e-5 * max(10.0, float(want.abs().max())),
+                               msg=lambda m: what + ": " + m)
 
 
 @pytest.mark.parametrize("vec_size,if_split", [(1, False), (1, True), (2, False), (2, True)])
@@ -209,14 +222,18 @@ def test_reference_gcn_and_gin_layers_forward_backward(ref, vec_size, if_split, 
             if i + 1 < len(Ws):
                 h = torch.relu(h)
         h.backward(G.double())
+        # GIN aggregates with unnormalised weights (1 per edge, 1 + epsilon on the diagonal): three
+        # layers grow the activations to the thousands and elements that cancel to small values carry
+        # the rounding of their large terms, so its floor follows the result's size as well
+        _close = _close_strict if net == "gcn" else _close_reduction
         _close(out, h.detach(), net + " forward")
         _close(gx, x64.grad, net + " input gradient")
         for a, b in zip(gw, Ws):
-            _close(a, b.grad, net + " weight gradient")
+            _close_reduction(a, b.grad, net + " weight gradient")
         _close(out2, h.detach(), net + " forward (package layer)")
         _close(gx2, x64.grad, net + " input gradient (package layer)")
         for a, b in zip(gw2, Ws):
-            _close(a, b.grad, net + " weight gradient (package layer)")
+            _close_reduction(a, b.grad, net + " weight gradient (package layer)")
     capsys.readouterr()
 
 
@@ -261,12 +278,13 @@ def test_reference_agnn_layer_forward_backward(ref, vec_size, if_split, capsys):
     W64 = layer.weights.detach().double()
     Xp = X[:n].double() @ W64
     E = (Xp @ Xp.t()) * mask * beta
+    _close = _close_strict
     _close(out, E @ Xp, "agnn forward")
     _close(out2, E @ Xp, "agnn forward (package layer)")
     # the layer's own backward treats the edge values as constants (gnn_conv.py:153-180)
     d_prime = E @ G[:n].double()
     _close(gx, d_prime @ W64.t(), "agnn input gradient")
-    _close(gw, X[:n].double().t() @ d_prime, "agnn weight gradient")
+    _close_reduction(gw, X[:n].double().t() @ d_prime, "agnn weight gradient")
     torch.testing.assert_close(gx2, gx, rtol=1e-5, atol=1e-4)
     torch.testing.assert_close(gw2, gw, rtol=1e-5, atol=1e-4)
     torch.testing.assert_close(ga2, ga, rtol=1e-4, atol=1e-2)  # a sum over all edges times column ids (~1e7)
