@@ -143,11 +143,11 @@ class Timer:
     """Times candidates on one (matrix, dim): verification against the default plain-CSR product
     first, then back-to-back launches between CUDA events."""
 
-    def __init__(self, m, dim, dev, warmup, iters):
+    def __init__(self, m, dim, dev, warmup, iters, layouts=None):
         # matrices far larger than the benchmark's 1.6e7 entries get proportionally fewer timed launches
         iters = max(5, int(iters * min(1.0, 2.0e7 / max(1, m.nnz))))
         self.m, self.dim, self.dev, self.warmup, self.iters = m, dim, dev, warmup, iters
-        self.lay = Layouts(m, dev)
+        self.lay = layouts if layouts is not None else Layouts(m, dev)  # PCSR arrays are per matrix, not per dim
         self.B = synth.dense_uniform(m.n_cols, dim, 1000 + dim, dev)
         self.ref = ops.csr_spmm(self.B, m.rowPtr, m.colIdx, m.val, 1, 8)
         # hub rows sum thousands of terms in a different order: the floor grows with the row's length
@@ -194,10 +194,11 @@ def fit(args):
     raw, best = [], {}
     t0 = time.time()
     for regime, lst in mats.items():
+        lays = {mname: Layouts(m, dev) for mname, m in lst}
         for dim in args.dims:
             agg = {}
             for mname, m in lst:
-                tm = Timer(m, dim, dev, args.warmup, args.iters)
+                tm = Timer(m, dim, dev, args.warmup, args.iters, lays[mname])
                 for cand in candidates(dim, regime, args.quick):
                     ms = tm.ms(cand)
                     if ms is None:
@@ -275,8 +276,9 @@ def holdout(args):
     for name, m in holdout_matrices(dev, args.scale):
         st = decider.row_stats(m.rowPtr, m.colIdx)
         reg = decider.regime(st)
+        lay = Layouts(m, dev)
         for dim in args.dims:
-            tm = Timer(m, dim, dev, args.warmup, args.iters)
+            tm = Timer(m, dim, dev, args.warmup, args.iters, lay)
             plan = decider.choose(st, dim)
             t_ms = tm.ms(dict(plan))
             best = (t_ms, "table")
