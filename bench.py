@@ -358,17 +358,16 @@ def main():
         sweep.append({"matrix": name, "dim": dim, "ms": round(ms, 5),
                       "gflops": round(2.0 * mats[name].nnz * dim / ms / 1e6, 1),
                       "gbs": round(by / ms / 1e6, 1), "frac": round(by / ms / 1e6 / peak, 4),
-                      "split": int(p["if_split"]), "path": p.get("path", "gather")})
+                      "split": int(p["if_split"])})
 
     def roofline_of(i):
         r = {"bound": "hbm", "achieved": sweep[i]["gbs"], "peak": peak, "unit": "GB/s", "frac": sweep[i]["frac"],
              "traffic": None, "peak_source": peak_kind,
-             "kernel": "%s %s dim=%d" % ("spmm_window_kernel" if sweep[i]["path"] == "window" else "spmm_seg_kernel",
-                                         sweep[i]["matrix"], sweep[i]["dim"]),
+             "kernel": "spmm_seg_kernel %s dim=%d" % (sweep[i]["matrix"], sweep[i]["dim"]),
              "ms": sweep[i]["ms"],
              "bytes_model": "4(n+1)+8nnz+4*dim*n_cols+4*dim*n_rows (+8S for a split layout)"}
         key = (sweep[i]["matrix"], sweep[i]["dim"])
-        if n == N_ROWS and key in NCU_DRAM_BYTES and sweep[i]["path"] == "gather":
+        if n == N_ROWS and key in NCU_DRAM_BYTES:
             tb, rev = NCU_DRAM_BYTES[key]
             algo = sweep[i]["gbs"] * sweep[i]["ms"] * 1e6
             r["traffic"] = tb

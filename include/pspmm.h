@@ -62,13 +62,6 @@ typedef struct pspmm_cfg {
                                 several launches over column ranges.  0 = one launch */
     int32_t hint_CF;         /* legacy coarsening factor, validated only */
     int32_t hint_blkWarpNum; /* legacy warps per block, validated only */
-    int32_t window_rows;     /* SpMM on plain CSR only: > 0 selects the window kernel for matrices whose rows reference
-                                nearby columns (banded, locality-ordered): every thread block copies this many
-                                consecutive rows of B (128 dense columns of them at most) into shared memory once and
-                                its entries read B from there; entries outside that range are fetched from global
-                                memory, so the result is right for any matrix.  0 = the gather kernel.  Ignored for
-                                split or block layouts, accumulate = 1, and operands without 16-byte alignment */
-    int32_t cta_rows;        /* window kernel: rows of A per thread block (0 = window_rows / 2) */
     int32_t accumulate;      /* SpMM only: 0 = C is overwritten (every row is written, empty rows with zeros);
                                 1 = the product is added to what C holds (reduction instructions; the order in
                                 which contributions reach a row is not fixed).  Lets a caller sum products over

@@ -25,7 +25,7 @@ ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC,-fopenmp,-fvisibility=hidden",
               "-cudart", "shared", "-I", os.path.join(ROOT, "include"), "-I", CSRC]
 
-CORE_SOURCES = ["pspmm_api.cu", "spmm_window.cu", "spmm_vw4.cu", "spmm_vw4_acc.cu", "spmm_vw2.cu", "spmm_vw1.cu", "sddmm_vw4.cu",
+CORE_SOURCES = ["pspmm_api.cu", "spmm_vw4.cu", "spmm_vw4_acc.cu", "spmm_vw2.cu", "spmm_vw1.cu", "sddmm_vw4.cu",
                 "sddmm_vw2.cu", "sddmm_vw1.cu", "host_builders.cpp", "mtx_io.cpp", "device_builders.cu", "agnn_fused.cu", "exchange.cu"]
 BASELINE_SOURCES = ["baselines.cu"]
 

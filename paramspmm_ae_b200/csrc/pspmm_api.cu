@@ -64,8 +64,6 @@ int pspmm_validate_cfg(const pspmm_cfg *cfg, bool sddmm)
         return PSPMM_E_CONFIG;
     if (cfg->col_tile < 0 || cfg->col_tile % 4 != 0)
         return PSPMM_E_CONFIG;
-    if (cfg->window_rows < 0 || cfg->cta_rows < 0 || (sddmm && cfg->window_rows != 0))
-        return PSPMM_E_CONFIG;
     return PSPMM_OK;
 }
 
@@ -387,15 +385,6 @@ extern "C" int pspmm_spmm_csr(const int32_t *rowPtr, const int32_t *colIdx, cons
         return PSPMM_E_ARG;
     if (split && n_seg >= INT32_MAX)
         return PSPMM_E_RANGE;
-    if (cfg && cfg->window_rows > 0 && !split && !cfg->accumulate && n_rows > 0 && nnz > 0) {
-        rc = pspmm_validate_cfg(cfg, false);
-        if (rc)
-            return rc;
-        rc = pspmm_launch_spmm_window(rowPtr, colIdx, val, B, C, n_rows, n_cols, dim, ldB, ldC, cfg->window_rows,
-                                      cfg->cta_rows, cfg->lanes_per_row, (cudaStream_t)stream);
-        if (rc != PSPMM_E_UNSUPPORTED)
-            return rc;  // done, or a real error; unsupported operands take the gather kernel below
-    }
     return spmm_launch(split ? rowPtr_split : rowPtr, target_row, split ? n_seg : n_rows, colIdx,
                        val, 1, B, C, n_rows, n_cols, dim, ldB, ldC, cfg, (cudaStream_t)stream);
 }

@@ -69,11 +69,6 @@ bool pspmm_launch_sddmm_vw4(const LaunchShape &s, int V, const SddmmArgs &a, dim
 bool pspmm_launch_sddmm_vw2(const LaunchShape &s, int V, const SddmmArgs &a, dim3 grid, cudaStream_t st);
 bool pspmm_launch_sddmm_vw1(const LaunchShape &s, int V, const SddmmArgs &a, dim3 grid, cudaStream_t st);
 
-// Window kernel (spmm_window.cu); PSPMM_E_UNSUPPORTED when the operands do not allow it.
-int pspmm_launch_spmm_window(const int32_t *rowPtr, const int32_t *colIdx, const float *val, const float *B,
-                             float *C, int64_t n_rows, int64_t n_cols, int32_t dim, int64_t ldB, int64_t ldC,
-                             int32_t window_rows, int32_t cta_rows, int32_t lanes_per_row, cudaStream_t st);
-
 // Smallest instantiated coarsening factor >= need (0 when none).
 static inline int pspmm_round_cf(int need)
 {

@@ -33,47 +33,22 @@ def dynamic_CF_prompter(dim, CF_set=None, warp_size=32):
     return [cf for cf in CF_set if gap_calculator(dim, cf, warp_size) < 32]
 
 
-WINDOW_ROWS, WINDOW_CTA_ROWS = 128, 64  # the window kernel's default shape: rows of B staged / rows of A per CTA
-
-
-def window_hit_rate(rowPtr, colIdx, cta_rows=WINDOW_CTA_ROWS, window_rows=WINDOW_ROWS):
-    """Share of the entries the window kernel would find in shared memory: rows are taken in blocks
-    of `cta_rows`, a block's window starts at the smallest column of its rows and spans
-    `window_rows` columns.  (The locality the reference summarises as max_bw / avg_bw,
-    graph_input.py:392-410, measured the way the kernel uses it.)"""
-    import torch
-
-    rp = torch.as_tensor(rowPtr).long()
-    ci = torch.as_tensor(colIdx).long()
-    n = rp.numel() - 1
-    if n <= 0 or ci.numel() == 0:
-        return 0.0
-    ln = rp[1:] - rp[:-1]
-    rows = torch.repeat_interleave(torch.arange(n, device=rp.device), ln)
-    blk = torch.div(rows, cta_rows, rounding_mode="floor")
-    nblk = (n + cta_rows - 1) // cta_rows
-    lo = torch.full((nblk,), 2**62, dtype=torch.long, device=rp.device).scatter_reduce(0, blk, ci, "amin")
-    return float(((ci - lo[blk]) < window_rows).double().mean())
-
-
-def row_stats(rowPtr, colIdx=None):
-    """nnz-per-row summary of a CSR row pointer (torch tensor or numpy array, any device); with the
-    column indices also `window_hit`, the share of entries within reach of the window kernel."""
+def row_stats(rowPtr):
+    """nnz-per-row summary of a CSR row pointer (torch tensor or numpy array, any device)."""
     import torch
 
     rp = torch.as_tensor(rowPtr).long()
     ln = (rp[1:] - rp[:-1]).double()
     n = ln.numel()
     if n == 0:
-        return {"n_rows": 0, "nnz": 0, "avg": 0.0, "cov": 0.0, "max": 0, "real_avg": 0.0, "window_hit": 0.0}
+        return {"n_rows": 0, "nnz": 0, "avg": 0.0, "cov": 0.0, "max": 0, "real_avg": 0.0}
     nnz = int(rp[-1] - rp[0])
     avg = nnz / n
     nonempty = int((ln > 0).sum())
     std = float(ln.std(unbiased=True)) if n > 1 else 0.0
     real_avg = nnz / nonempty if nonempty and nonempty / n < 0.98 else avg
     return {"n_rows": n, "nnz": nnz, "avg": avg, "cov": std / avg if avg else 0.0,
-            "max": int(ln.max()), "real_avg": real_avg,
-            "window_hit": window_hit_rate(rp, colIdx) if colIdx is not None else 0.0}
+            "max": int(ln.max()), "real_avg": real_avg}
 
 
 def regime(stats):
@@ -88,8 +63,6 @@ def auto_granularity(real_avg_degree):
     """The reference's partition length: ceil(avg / 32) * 32 (graph_input.py:101)."""
     return max(32, int(math.ceil(real_avg_degree / 32) * 32))
 
-
-WINDOW_MIN_HIT = 0.97  # below this share of in-window entries the gather kernel is kept
 
 _DEFAULT_TABLE = {"version": 1, "source": "built-in defaults (no measurements)", "entries": {}}
 _table = None
@@ -124,8 +97,7 @@ class Plan(dict):
 
     def kernel_cfg(self):
         return {k: int(self.get(k, 0) or 0)
-                for k in ("lanes_per_row", "vec_width", "cta_threads", "rows_per_group", "gather_batch", "col_tile",
-                          "window_rows", "cta_rows")}
+                for k in ("lanes_per_row", "vec_width", "cta_threads", "rows_per_group", "gather_batch", "col_tile")}
 
 
 def choose(stats, dim, op="spmm"):
@@ -148,17 +120,9 @@ def choose(stats, dim, op="spmm"):
     if e is None:
         e = {"if_split": 1 if reg.endswith("skewed") else 0, "vec_size": 1}
     plan = Plan(if_split=0, vec_size=1, granularity=None, lanes_per_row=0, vec_width=0, cta_threads=0,
-                rows_per_group=0, gather_batch=0, col_tile=0, window_rows=0, cta_rows=0)
+                rows_per_group=0, gather_batch=0, col_tile=0)
     plan.update(e)
     plan["regime"] = reg
-    plan["path"] = "gather"
-    # Rows that reference nearby columns (banded, locality-ordered): the window kernel, from the dim
-    # at which it was measured to win; its shape comes from the table's "window" section.
-    win = table().get("entries", {}).get("window", {}).get(_dim_key(dim))
-    if (op == "spmm" and win and stats.get("window_hit", 0.0) >= WINDOW_MIN_HIT and dim % 4 == 0
-            and not reg.endswith("skewed")):
-        plan.update(if_split=0, granularity=None, lanes_per_row=int(win.get("lanes_per_row", 0)), vec_width=4,
-                    col_tile=0, window_rows=int(win["window_rows"]), cta_rows=int(win["cta_rows"]), path="window")
     if plan["if_split"] and not plan.get("granularity"):
         plan["granularity"] = auto_granularity(stats["real_avg"])
     return plan

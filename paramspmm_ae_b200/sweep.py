@@ -7,15 +7,13 @@ predicted configuration against the best one on matrices the forests were not tr
 
 The swept space is that of the sm_100a kernels: PCSR split on/off and partition length, block
 height (vec_size 1 or 2), lanes per row (rows per warp), rows per lane group, gather depth, CTA
-size, column tiles; for banded matrices the window kernel's shape.
+size, column tiles.
 
     python -m paramspmm_ae_b200.sweep fit     --table paramspmm_ae_b200/config_table.json
-    python -m paramspmm_ae_b200.sweep window  --table paramspmm_ae_b200/config_table.json
     python -m paramspmm_ae_b200.sweep holdout --out paramspmm_ae_b200/decider_holdout.json
 
 ``fit`` times every candidate on the fitting matrices of each row-length regime and writes, per
-(regime, dim), the configuration with the smallest summed time.  ``window`` does the same for the
-window kernel on a banded matrix and records the dims at which it beats the gather kernel.
+(regime, dim), the configuration with the smallest summed time.
 ``holdout`` takes matrices that ``fit`` never sees (other generators' parameters, sizes and seeds),
 times for each (matrix, dim) the whole candidate space and the configuration the table gives, and
 records table-choice time / best time.  Each candidate is verified against the plain-CSR result of
@@ -61,7 +59,7 @@ def fitting_matrices(n, device, which):
 
 def holdout_matrices(device, scale=1.0):
     """Fourteen matrices no fit ever sees: other sizes, mean degrees 4..600, R-MAT and Chung-Lu
-    exponents, band widths inside and outside the window kernel's reach, all six regimes."""
+    exponents, narrow and wide bands, all six regimes."""
     s = lambda x: max(2048, int(x * scale))
     return [
         ("uniform_k8", synth.uniform_rows(s(500_000), 8, seed=201, device=device)),
@@ -156,8 +154,18 @@ class Timer:
         self.max_row = int(ln.max())
 
     def ms(self, cand):
+        """Milliseconds per launch, or None for a candidate that is not run (hub rows without a
+        split) or that the library rejects for this width / layout."""
+        try:
+            return self._ms(cand)
+        except _lib.PspmmError as e:
+            if e.code in (_lib.PSPMM_E_UNSUPPORTED, _lib.PSPMM_E_CONFIG):
+                return None
+            raise
+
+    def _ms(self, cand):
         m, dim = self.m, self.dim
-        if not cand.get("if_split") and self.max_row > 4096 and not cand.get("window_rows"):
+        if not cand.get("if_split") and self.max_row > 4096:
             return None  # one lane group per hub row would take milliseconds
         V = cand.get("vec_size", 1)
         rp, ci, v, tr = self.lay.get(V, cand.get("granularity") if cand.get("if_split") else None)
@@ -165,7 +173,7 @@ class Timer:
         out = torch.full((nbr * V, dim), float("nan"), device=self.dev)
         cfg = _lib.make_cfg(**{k: int(cand.get(k, 0) or 0) for k in
                                ("lanes_per_row", "vec_width", "cta_threads", "rows_per_group", "gather_batch",
-                                "col_tile", "window_rows", "cta_rows")})
+                                "col_tile")})
         ops.spmm_into(out, self.B, rp, ci, v, target_row=tr, V=V, n_out_rows=nbr, cfg=cfg)
         bad = int(((out[: m.n_rows] - self.ref).abs() > self.tol).sum())
         if bad or bool(torch.isnan(out[: m.n_rows]).any()):
@@ -224,49 +232,6 @@ def fit(args):
     return best
 
 
-WINDOW_SHAPES = ((96, 32), (128, 64), (160, 96), (192, 128), (256, 160), (256, 192))
-
-
-def window(args):
-    """Window kernel vs the gather kernel on a banded fitting matrix, per dim: the fastest window
-    shape is recorded where it beats the table's gather configuration by at least 3 %."""
-    dev = torch.device("cuda:0")
-    _lib.lib()
-    m = synth.banded_rows(args.rows, 16, 32, seed=122, device=dev)
-    st = decider.row_stats(m.rowPtr, m.colIdx)
-    entries, raw = {}, []
-    for dim in args.dims:
-        if dim % 4:
-            continue
-        tm = Timer(m, dim, dev, args.warmup, args.iters)
-        gather = dict(decider.choose(dict(st, window_hit=0.0), dim))
-        g_ms = tm.ms(gather)
-        best = None
-        for (wr, cr), lpr in itertools.product(WINDOW_SHAPES, (16, 32)):
-            if lpr == 32 and dim < 128 and dim != 96:
-                continue
-            if wr * lpr * 16 > 200 * 1024:
-                continue
-            cand = {"window_rows": wr, "cta_rows": cr, "lanes_per_row": lpr, "vec_width": 4}
-            ms = tm.ms(cand)
-            raw.append(dict(cand, dim=dim, ms=ms, gather_ms=g_ms))
-            if best is None or ms < best[0]:
-                best = (ms, cand)
-        print("window dim %3d: gather %.4f ms, window %.4f ms %s" % (dim, g_ms, best[0], best[1]), flush=True)
-        if best[0] < 0.97 * g_ms:
-            entries[str(dim)] = dict(best[1], ms=best[0], gather_ms=g_ms)
-        del tm
-    if args.raw:
-        with open(args.raw, "w") as f:
-            json.dump({"rows": args.rows, "results": raw}, f)
-    if args.table:
-        table = _load_table(args.table)
-        table.setdefault("entries", {})["window"] = entries
-        _save_table(args.table, table, {"window": "python -m paramspmm_ae_b200.sweep window, rows=%d iters=%d, banded "
-                                                  "16 entries per row, half bandwidth 32, seed 122" % (args.rows, args.iters)})
-    return entries
-
-
 def holdout(args):
     dev = torch.device("cuda:0")
     _lib.lib()
@@ -274,7 +239,7 @@ def holdout(args):
     rows_out = []
     t0 = time.time()
     for name, m in holdout_matrices(dev, args.scale):
-        st = decider.row_stats(m.rowPtr, m.colIdx)
+        st = decider.row_stats(m.rowPtr)
         reg = decider.regime(st)
         lay = Layouts(m, dev)
         for dim in args.dims:
@@ -283,21 +248,17 @@ def holdout(args):
             t_ms = tm.ms(dict(plan))
             best = (t_ms, "table")
             n_c = 0
-            space = [c for c in candidates(dim, reg)]
-            if st["window_hit"] >= 0.5 and dim % 4 == 0 and dim >= 32:
-                space += [{"window_rows": wr, "cta_rows": cr, "lanes_per_row": 32 if dim >= 128 else 16, "vec_width": 4}
-                          for wr, cr in WINDOW_SHAPES]
-            for cand in space:
+            for cand in candidates(dim, reg):
                 ms = tm.ms(cand)
                 if ms is None:
                     continue
                 n_c += 1
                 if ms < best[0]:
                     best = (ms, cand)
-            rec = {"matrix": name, "n_rows": m.n_rows, "nnz": m.nnz, "regime": reg, "window_hit": round(st["window_hit"], 3),
+            rec = {"matrix": name, "n_rows": m.n_rows, "nnz": m.nnz, "regime": reg,
                    "dim": dim, "table_ms": round(t_ms, 5), "best_ms": round(best[0], 5),
                    "normalised_performance": round(best[0] / t_ms, 4), "candidates": n_c,
-                   "table_choice": {k: plan[k] for k in ("if_split", "vec_size", "granularity", "path") if k in plan},
+                   "table_choice": {k: plan[k] for k in ("if_split", "vec_size", "granularity") if k in plan},
                    "table_kernel": plan.kernel_cfg(),
                    "best": best[1]}
             rows_out.append(rec)
@@ -313,8 +274,7 @@ def holdout(args):
                "worst": round(float(ratios.min()), 4),
                "share_within_5_percent": round(float((ratios >= 0.95).double().mean()), 4),
                "per_regime_mean": {k: round(sum(v) / len(v), 4) for k, v in sorted(by_regime.items())},
-               "vec_size_2_best_in": sum(1 for r in rows_out if isinstance(r["best"], dict) and r["best"].get("vec_size") == 2),
-               "window_best_in": sum(1 for r in rows_out if isinstance(r["best"], dict) and r["best"].get("window_rows"))}
+               "vec_size_2_best_in": sum(1 for r in rows_out if isinstance(r["best"], dict) and r["best"].get("vec_size") == 2)}
     out = {"what": "table-choice time vs the fastest of the whole candidate space, per (hold-out matrix, dim); "
                    "normalised_performance = best_ms / table_ms (1 = the table picked the fastest); matrices, sizes "
                    "and seeds are disjoint from the fitting set; back-to-back launches, %d iterations, B200" % args.iters,
@@ -337,11 +297,6 @@ def main():
     p.add_argument("--quick", action="store_true")
     p.add_argument("--raw", default=None, help="write every timing to this file")
     p.add_argument("--table", default=table)
-    p = sub.add_parser("window")
-    p.add_argument("--rows", type=int, default=1_000_000)
-    p.add_argument("--dims", type=int, nargs="*", default=list(range(32, 257, 16)))
-    p.add_argument("--raw", default=None)
-    p.add_argument("--table", default=table)
     p = sub.add_parser("holdout")
     p.add_argument("--dims", type=int, nargs="*", default=[16, 32, 64, 128, 256])
     p.add_argument("--scale", type=float, default=1.0, help="shrink the hold-out matrices (quick checks)")
@@ -351,7 +306,7 @@ def main():
         q.add_argument("--iters", type=int, default=20)
         q.add_argument("--warmup", type=int, default=3)
     args = ap.parse_args()
-    {"fit": fit, "window": window, "holdout": holdout}[args.cmd](args)
+    {"fit": fit, "holdout": holdout}[args.cmd](args)
 
 
 if __name__ == "__main__":

@@ -653,79 +653,3 @@ def test_pull_transport_single_rank(dev, oracle, mats, exchange, row_chunks):
     src = op.symmetric_input(64)   # a producer writes the block in place: no staging copy
     src.copy_(Bd)
     close(op.forward(src), want)
-
-
-# ----------------------------------------------------------------------------- window kernel
-@pytest.mark.parametrize("name", ["banded", "powerlaw", "rmat", "hub", "tiny"])
-def test_window_spmm_matches_oracle(dev, oracle, mats, name):
-    """pspmm_cfg.window_rows > 0: rows of B staged in shared memory.  Right for every matrix (entries
-    outside the staged range come from global memory): banded (all entries inside), power-law and
-    R-MAT (most outside), a hub row, a 7-row matrix; widths that are and are not multiples of the
-    128-column tile; every window shape incl. one larger than the matrix; strided operands."""
-    from paramspmm_ae_b200 import _lib, ops
-    m = mats[name]
-    rp, ci, v = m.numpy()
-    d = m.to(dev)
-    for dim in (4, 16, 64, 100, 128, 132, 256, 260):
-        B = dense(m.n_cols, dim, 400 + dim)
-        want = oracle.spmm_csr(rp, ci, v, B.numpy())
-        Bd = torch.full((m.n_cols, dim + 4), float("nan"), device=dev)
-        Bd[:, :dim] = B.to(dev)
-        for wr, cr, lanes in ((128, 64, 0), (96, 32, 16), (33, 7, 32), (4096, 2048, 0)):
-            out = torch.full((m.n_rows, dim + 8), float("nan"), device=dev)[:, :dim]
-            cfg = _lib.make_cfg(window_rows=wr, cta_rows=cr, lanes_per_row=lanes)
-            ops.spmm_into(out, Bd[:, :dim], d.rowPtr, d.colIdx, d.val, cfg=cfg)
-            close(out, want)
-
-
-def test_window_spmm_ignores_non_finite_rows_it_does_not_reference(dev, oracle, mats):
-    """Staged rows that no entry references (and the padding of the staging area) never reach a sum."""
-    from paramspmm_ae_b200 import _lib, ops
-    m = mats["banded"]
-    rp, ci, v = m.numpy()
-    used = torch.zeros(m.n_cols, dtype=torch.bool)
-    used[m.colIdx.long()] = True
-    B = dense(m.n_cols, 64, 77)
-    want = oracle.spmm_csr(rp, ci, v, B.numpy())
-    B[~used] = float("inf")
-    d = m.to(dev)
-    out = torch.empty(m.n_rows, 64, device=dev)
-    ops.spmm_into(out, B.to(dev), d.rowPtr, d.colIdx, d.val, cfg=_lib.make_cfg(window_rows=128, cta_rows=64))
-    if bool((~used).any()):
-        close(out, want)
-
-
-def test_window_falls_back_for_layouts_it_does_not_cover(dev, oracle, mats):
-    """Split layouts, unaligned widths and accumulate = 1 take the gather kernel even when the
-    configuration asks for a window."""
-    from paramspmm_ae_b200 import _lib, ops
-    m = mats["banded"]
-    rp, ci, v = m.numpy()
-    d = m.to(dev)
-    cfg = _lib.make_cfg(window_rows=128, cta_rows=64)
-    B = dense(m.n_cols, 47, 3)
-    close(ops.spmm_into(torch.empty(m.n_rows, 47, device=dev), B.to(dev), d.rowPtr, d.colIdx, d.val, cfg=cfg),
-          oracle.spmm_csr(rp, ci, v, B.numpy()))
-    rps, tr = ops.split_csr(m.rowPtr, 7)
-    B = dense(m.n_cols, 64, 4)
-    want = oracle.spmm_csr(rp, ci, v, B.numpy())
-    close(ops.spmm_into(torch.empty(m.n_rows, 64, device=dev), B.to(dev), rps.to(dev), d.colIdx, d.val,
-                        target_row=tr.to(dev), n_out_rows=m.n_rows, cfg=cfg), want)
-    acc = torch.ones(m.n_rows, 64, device=dev)
-    ops.spmm_into(acc, B.to(dev), d.rowPtr, d.colIdx, d.val, cfg=_lib.make_cfg(window_rows=128, accumulate=1))
-    close(acc, want + 1.0)
-    with pytest.raises(_lib.PspmmError):
-        ops.spmm_into(torch.empty(m.n_rows, 64, device=dev), B.to(dev), d.rowPtr, d.colIdx, d.val,
-                      cfg=_lib.make_cfg(window_rows=-1))
-
-
-def test_decider_window_statistic(dev):
-    """window_hit is the share of entries the window kernel finds in shared memory."""
-    from paramspmm_ae_b200 import decider, synth
-    b = synth.banded_rows(5000, 16, 32, seed=22)
-    assert decider.window_hit_rate(b.rowPtr, b.colIdx) == 1.0
-    assert decider.window_hit_rate(b.rowPtr.to(dev), b.colIdx.to(dev)) == 1.0
-    u = synth.uniform_rows(5000, 16, seed=21)
-    assert decider.window_hit_rate(u.rowPtr, u.colIdx) < 0.1
-    wide = synth.banded_rows(5000, 16, 200, seed=22)
-    assert 0.1 < decider.window_hit_rate(wide.rowPtr, wide.colIdx) < 0.9
