@@ -207,8 +207,22 @@ PSPMM_API int pspmm_split_csr_device_static(const int32_t *rowPtr, int64_t n_row
  * Split layouts (rowPtr_split/target_row/n_seg as in pspmm_spmm_csr) need scratch of
  * pspmm_agnn_scratch_bytes(n_seg, dim) bytes, 16-byte aligned, for the partial results of the
  * pieces of split rows; plain CSR needs none (NULL, 0).
+ *
+ * pspmm_agnn_fused_apply_csr is the same pass with a separate aggregation operand:
+ *     out_i = sum_j a_ij * V_j,   a_ij from A and B as above.
+ * With A = B = the projected features and V = the upstream gradient G it yields the layer's backward
+ * product sum_j a_ij G_j (what gnn_conv.py:157 computes from the saved edge array, AGNN_spmm) from
+ * recomputed scores, so training keeps no per-edge array either.  ldV = 0 makes every column use the
+ * one row V[0, :] (a row of ones turns the pass into per-row sums of the scores).  V and ldV follow
+ * the alignment rules of B; this form runs with 128-bit loads and batches of 4.
  */
 PSPMM_API int pspmm_agnn_scratch_bytes(int64_t n_seg, int32_t dim, size_t *bytes);
+PSPMM_API int pspmm_agnn_fused_apply_csr(const int32_t *rowPtr, const int32_t *colIdx, const float *A,
+                                         const float *B, const float *V, float *out, int64_t n_rows, int64_t nnz,
+                                         int32_t dim, int64_t ldA, int64_t ldB, int64_t ldV, int64_t ldOut,
+                                         float beta, int32_t softmax, int32_t vec_width, int32_t lanes_per_row,
+                                         int32_t batch, const int32_t *rowPtr_split, const int32_t *target_row,
+                                         int64_t n_seg, void *scratch, size_t scratch_bytes, void *stream);
 PSPMM_API int pspmm_agnn_fused_csr(const int32_t *rowPtr, const int32_t *colIdx, const float *A,
                                    const float *B, float *out, int64_t n_rows, int64_t nnz, int32_t dim,
                                    int64_t ldA, int64_t ldB, int64_t ldOut, float beta, int32_t softmax,

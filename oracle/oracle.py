@@ -197,13 +197,18 @@ def sddmm_bcsr(rowPtr_b, colIdx_b, val_b, A, B, target_row=None):
     return out
 
 
-def agnn_aggregate(rowPtr, colIdx, A, B, beta=1.0, softmax=True):
+def agnn_aggregate(rowPtr, colIdx, A, B, beta=1.0, softmax=True, V=None):
     """out_i = sum_j a_ij B_j over the stored pattern, a_ij = softmax_j(beta <A_i, B_j>) or, with
     softmax=False, the raw scaled scores: the composition SDDMM -> ``* attention_w`` -> SpMM of the
     reference's AGNN layer (gnn_conv.py:130-151), with the per-row edge softmax in between when
-    asked for.  Computed row by row in float64 (numpy), returned as float32."""
+    asked for.  With ``V`` the aggregated rows are V_j instead of B_j (the layer's backward product
+    AGNN_spmm(edge_attentions, d_output), gnn_conv.py:157, for V = d_output); a single row
+    ``[1, dim]`` is shared by all columns.  Computed row by row in float64 (numpy), returned as float32."""
     rowPtr, colIdx = np.asarray(rowPtr, dtype=np.int64), np.asarray(colIdx, dtype=np.int64)
     A64, B64 = np.asarray(A, dtype=np.float64), np.asarray(B, dtype=np.float64)
+    V64 = B64 if V is None else np.asarray(V, dtype=np.float64)
+    if V64.shape[0] == 1 and B64.shape[0] != 1:
+        V64 = np.broadcast_to(V64, B64.shape)
     n = rowPtr.shape[0] - 1
     out = np.zeros((n, B64.shape[1]), dtype=np.float64)
     for i in range(n):
@@ -217,7 +222,7 @@ def agnn_aggregate(rowPtr, colIdx, A, B, beta=1.0, softmax=True):
             w /= w.sum()
         else:
             w = s
-        out[i] = w @ nb
+        out[i] = w @ V64[colIdx[lo:hi]]
     return out.astype(np.float32)
 
 

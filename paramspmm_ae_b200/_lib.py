@@ -85,6 +85,8 @@ _SIGNATURES = {
     "pspmm_split_csr_device": [_vp, _i64, _i32, _vp, _vp, _i64, _vp, ctypes.c_size_t, _vp],
     "pspmm_split_csr_device_static": [_vp, _i64, _i32, _vp, _vp, _i64, _vp],
     "pspmm_agnn_scratch_bytes": [_i64, _i32, ctypes.POINTER(ctypes.c_size_t)],
+    "pspmm_agnn_fused_apply_csr": [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i32, _i64, _i64, _i64, _i64,
+                                   ctypes.c_float, _i32, _i32, _i32, _i32, _vp, _vp, _i64, _vp, ctypes.c_size_t, _vp],
     "pspmm_agnn_fused_csr": [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i32, _i64, _i64, _i64, ctypes.c_float, _i32,
                              _i32, _i32, _i32, _vp, _vp, _i64, _vp, ctypes.c_size_t, _vp],
     "pspmm_pull_rows": [ctypes.POINTER(RowSources), _vp, _i64, _vp, _i32, _i64, _i64, _i64, _i32, _vp],

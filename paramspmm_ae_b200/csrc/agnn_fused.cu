@@ -2,13 +2,15 @@
 //
 //     s_ij  = beta * <A_i, B_j>                 for every stored (i, j)          (the SDDMM)
 //     a_ij  = softmax_j(s_ij)  or  s_ij                                           (edge softmax, optional)
-//     out_i = sum_j a_ij * B_j                                                    (the SpMM)
+//     out_i = sum_j a_ij * V_j        (V = B in the forward pass)                 (the SpMM)
 //
 // in ONE pass over the pattern: every gathered row B_j is used for its score and for the
 // aggregation while it sits in registers, the per-edge values never reach memory, and the
 // softmax is the running-maximum ("online") form, so a row needs no second sweep.  This is the
 // AGNN propagation (A = B = the projected node features) without the two edge-array round trips
-// and with half the gathers of SDDMM followed by SpMM.
+// and with half the gathers of SDDMM followed by SpMM.  With a separate aggregation operand V
+// (template flag SEP: a second gather per entry) the same pass gives the layer's backward products
+// from recomputed scores: sum_j a_ij G_j for an upstream gradient G, again without an edge array.
 //
 // Work unit = segment (CSR row or PCSR row piece); a group of LPR lanes owns one segment, lane gl
 // holds the slice [(cf*LPR + gl)*4, +4) of A_i and of the accumulator.  Entries are taken BS at a
@@ -33,10 +35,11 @@ struct AgnnArgs {
     const int32_t *colIdx;
     const float *A;
     const float *B;
+    const float *Vm;  // aggregated rows (SEP kernels); row stride ldV, 0 = one row shared by all columns
     float *out;
     float *scratch;  // [n_seg][4 + dim_pad] partials of split rows: max, sum, 2 unused, accumulator
     int64_t n_seg;
-    int64_t ldA, ldB, ldOut;
+    int64_t ldA, ldB, ldV, ldOut;
     int32_t dim, dim_pad;
     float beta;
     int32_t softmax;
@@ -76,7 +79,7 @@ __device__ __forceinline__ float group_transpose_reduce(float (&p)[BS], int gl)
     return q[0];
 }
 
-template <int LPR, int CF, int BS, int VW>
+template <int LPR, int CF, int BS, int VW, bool SEP = false>
 __global__ void __launch_bounds__(256) agnn_fused_kernel(const AgnnArgs a)
 {
     static_assert(BS <= LPR, "a batch cannot be wider than the lane group");
@@ -140,6 +143,7 @@ __global__ void __launch_bounds__(256) agnn_fused_kernel(const AgnnArgs a)
             const bool mine = (lb + off + sub) < hb;
             const bool full = (off + BS <= len);
             FVec<VW> x[BS][CF];
+            FVec<VW> y[SEP ? BS : 1][SEP ? CF : 1];  // the rows that are aggregated, when they are not B's
             float part[BS];
             int ce[BS];
 #pragma unroll
@@ -157,6 +161,13 @@ __global__ void __launch_bounds__(256) agnn_fused_kernel(const AgnnArgs a)
 #pragma unroll
                     for (int cf = 0; cf < CF; ++cf)
                         x[e][cf] = ldg_vec_if<VW>(brow + voff[cf], on);
+                }
+                if constexpr (SEP) {
+                    const float *vrow = a.Vm + (int64_t)ce[e] * a.ldV;
+                    const bool on = (off + e) < len;
+#pragma unroll
+                    for (int cf = 0; cf < CF; ++cf)
+                        y[e][cf] = ldg_vec_if<VW>(vrow + voff[cf], on);
                 }
             }
 #pragma unroll
@@ -203,8 +214,12 @@ __global__ void __launch_bounds__(256) agnn_fused_kernel(const AgnnArgs a)
 #pragma unroll
                 for (int cf = 0; cf < CF; ++cf)
 #pragma unroll
-                    for (int i = 0; i < VW; ++i)
-                        acc[cf][i] = fmaf(pe, x[e][cf].v[i], acc[cf][i]);
+                    for (int i = 0; i < VW; ++i) {
+                        if constexpr (SEP)
+                            acc[cf][i] = fmaf(pe, y[e][cf].v[i], acc[cf][i]);
+                        else
+                            acc[cf][i] = fmaf(pe, x[e][cf].v[i], acc[cf][i]);
+                    }
             }
         }
     }
@@ -278,12 +293,12 @@ __global__ void __launch_bounds__(256) agnn_combine_kernel(const AgnnArgs a)
     }
 }
 
-template <int LPR, int CF, int BS, int VW>
+template <int LPR, int CF, int BS, int VW, bool SEP = false>
 void launch_fused(const AgnnArgs &a, cudaStream_t st)
 {
     const int gpc = 256 / LPR;
     const int64_t gx = (a.n_seg + gpc - 1) / gpc;
-    agnn_fused_kernel<LPR, CF, BS, VW><<<(unsigned)gx, 256, 0, st>>>(a);
+    agnn_fused_kernel<LPR, CF, BS, VW, SEP><<<(unsigned)gx, 256, 0, st>>>(a);
 }
 
 }  // namespace
@@ -304,8 +319,25 @@ extern "C" int pspmm_agnn_fused_csr(const int32_t *rowPtr, const int32_t *colIdx
                                     const int32_t *rowPtr_split, const int32_t *target_row,
                                     int64_t n_seg, void *scratch, size_t scratch_bytes, void *stream)
 {
+    return pspmm_agnn_fused_apply_csr(rowPtr, colIdx, A, B, B, out, n_rows, nnz, dim, ldA, ldB, ldB, ldOut, beta,
+                                      softmax, vec_width, lanes_per_row, batch, rowPtr_split, target_row, n_seg,
+                                      scratch, scratch_bytes, stream);
+}
+
+extern "C" int pspmm_agnn_fused_apply_csr(const int32_t *rowPtr, const int32_t *colIdx, const float *A,
+                                          const float *B, const float *V, float *out, int64_t n_rows, int64_t nnz,
+                                          int32_t dim, int64_t ldA, int64_t ldB, int64_t ldV, int64_t ldOut,
+                                          float beta, int32_t softmax, int32_t vec_width, int32_t lanes_per_row,
+                                          int32_t batch, const int32_t *rowPtr_split, const int32_t *target_row,
+                                          int64_t n_seg, void *scratch, size_t scratch_bytes, void *stream)
+{
     if (n_rows < 0 || nnz < 0 || dim <= 0)
         return PSPMM_E_ARG;
+    if (!V || (ldV != 0 && ldV < dim))
+        return PSPMM_E_ARG;
+    const bool sep = (V != B) || (ldV != ldB);
+    if (sep && (ldV % 4 != 0 || ((uintptr_t)V) % 16 != 0))
+        return PSPMM_E_UNSUPPORTED;
     if (n_rows >= INT32_MAX || nnz > INT32_MAX)
         return PSPMM_E_RANGE;
     const bool split = target_row != nullptr || rowPtr_split != nullptr;
@@ -334,6 +366,8 @@ extern "C" int pspmm_agnn_fused_csr(const int32_t *rowPtr, const int32_t *colIdx
     a.colIdx = colIdx;
     a.A = A;
     a.B = B;
+    a.Vm = V;
+    a.ldV = ldV;
     a.out = out;
     a.scratch = (float *)scratch;
     a.n_seg = split ? n_seg : n_rows;
@@ -358,8 +392,11 @@ extern "C" int pspmm_agnn_fused_csr(const int32_t *rowPtr, const int32_t *colIdx
     // entries per batch (BS).  Few lanes per row put more entries into every warp instruction (the
     // 128-bit form at 16 lanes is bound by instruction issue); wide loads keep the L1 wavefronts
     // full (the 128-bit form at 4 lanes is bound by the L1 data pipe).  Defaults = measured best.
-    const bool can8 = dim % 8 == 0 && dim >= 32 && ldA % 8 == 0 && ldB % 8 == 0 && ((uintptr_t)A) % 32 == 0 &&
-                      ((uintptr_t)B) % 32 == 0;
+    // (a separate aggregation operand doubles the gathered registers: built with 128-bit loads, batches of 4)
+    const bool can8 = !sep && dim % 8 == 0 && dim >= 32 && ldA % 8 == 0 && ldB % 8 == 0 &&
+                      ((uintptr_t)A) % 32 == 0 && ((uintptr_t)B) % 32 == 0;
+    if (sep)
+        batch = 4;
     if (vec_width != 0 && vec_width != 4 && vec_width != 8)
         return PSPMM_E_CONFIG;
     const int vw = (vec_width == 8 && !can8) ? 4 : (vec_width ? vec_width : (can8 ? 8 : 4));
@@ -373,6 +410,12 @@ extern "C" int pspmm_agnn_fused_csr(const int32_t *rowPtr, const int32_t *colIdx
         lpr *= 2;
         cf = (nvec + lpr - 1) / lpr;
     }
+    if (sep && lanes_per_row == 0) {  // two gathered rows per entry: at most two slices per lane keeps them in registers
+        while (cf > 2 && lpr < 32) {
+            lpr *= 2;
+            cf = (nvec + lpr - 1) / lpr;
+        }
+    }
     if (cf > cf_max)
         return PSPMM_E_UNSUPPORTED;
     if (cf == 3)
@@ -385,6 +428,17 @@ extern "C" int pspmm_agnn_fused_csr(const int32_t *rowPtr, const int32_t *colIdx
     if (cf * vw >= 8 && bs > 8)
         bs = 8;
     bool ok = false;
+#define AGNN_CASE_SEP(LPR_, CF_)                                    \
+    if (!ok && sep && vw == 4 && lpr == LPR_ && cf == CF_ && bs == 4) { \
+        launch_fused<LPR_, CF_, 4, 4, true>(a, st);                 \
+        ok = true;                                                  \
+    }
+    AGNN_CASE_SEP(4, 1) AGNN_CASE_SEP(4, 2) AGNN_CASE_SEP(4, 4) AGNN_CASE_SEP(8, 1) AGNN_CASE_SEP(8, 2)
+    AGNN_CASE_SEP(8, 4) AGNN_CASE_SEP(16, 1) AGNN_CASE_SEP(16, 2) AGNN_CASE_SEP(16, 4) AGNN_CASE_SEP(32, 1)
+    AGNN_CASE_SEP(32, 2)
+#undef AGNN_CASE_SEP
+    if (sep && !ok)
+        return PSPMM_E_UNSUPPORTED;
 #define AGNN_CASE(LPR_, CF_, BS_, VW_)                             \
     if (!ok && vw == VW_ && lpr == LPR_ && cf == CF_ && bs == BS_) { \
         launch_fused<LPR_, CF_, BS_, VW_>(a, st);                  \

@@ -84,9 +84,28 @@ class GINFunction(torch.autograd.Function):
 # (SDDMM -> scale -> SpMM in one pass).  Set to False to always use the three-kernel composition.
 FUSE_AGNN_INFERENCE = True
 
+# With gradients enabled the same layers run AGNNFusedFunction: the forward is the fused kernel, and
+# the backward recomputes the edge scores inside the kernel instead of reading a saved edge array,
+# so a training step writes no per-edge array at all (the reference's composition writes the
+# attention values in the forward and the score gradient in the backward, 4 bytes per edge each,
+# gnn_conv.py:130-180).  Outputs and gradients are the reference's up to fp32 summation order.
+# Set to False to train through the three-kernel composition (AGNNFunction).
+FUSE_AGNN_TRAINING = True
+
 
 def _can_fuse(P, dim):
     return getattr(P, "vec_size", 1) == 1 and dim % 4 == 0 and dim <= 256
+
+
+def _is_operator_colidx(P, colIdx):
+    """The fused backward weights edges by the operator's own column ids; callers pass them as an
+    [nnz, 1] column (GNN.py:224-225).  Checked once per (operator, tensor) pair, not per step."""
+    seen = P.__dict__.setdefault("_colidx_checked", {})
+    key = (colIdx.data_ptr(), tuple(colIdx.shape))
+    if key not in seen:
+        flat = colIdx.reshape(-1)
+        seen[key] = bool(flat.shape == P.colIdx.shape and flat.dtype == P.colIdx.dtype and torch.equal(flat, P.colIdx))
+    return seen[key]
 
 
 class AGNNFunction(torch.autograd.Function):
@@ -114,6 +133,62 @@ class AGNNFunction(torch.autograd.Function):
             d_att = d_att.reshape(-1)[P.mask]  # back to CSR entry order
         d_attention_w = torch.mm(d_att[None, :].expand(n_heads, -1), ctx.colIdx.float()).transpose(0, 1)
         return d_input, d_weights, d_attention_w, None, None
+
+
+class AGNNFusedFunction(torch.autograd.Function):
+    """AGNN layer on a CSR / split-CSR operator without edge arrays.
+
+    forward   X' = X W,  out_i = sum_j beta <X'_i, X'_j> X'_j                 (one fused pass)
+    backward  D_i = sum_j beta <X'_i, X'_j> G_j   (fused pass, scores recomputed, gradient rows gathered)
+              dX = D W^T,  dW = X^T D                                      (gnn_conv.py:157-160)
+              d_beta = sum over edges of <G_i, G_j> * colIdx[e]              (gnn_conv.py:163-172: the
+              reference multiplies the score gradient by the column-index column it is handed); here
+              as row sums of the scores <G_i, H_j>, H_j = colIdx-weight_j * G_j, from a third fused pass
+              whose aggregation operand is one shared row of ones.
+    Like the reference's backward, the edge values are treated as constants with respect to X'."""
+
+    @staticmethod
+    def forward(ctx, X, weights, attention_w, P, colIdx):
+        from . import ops
+        Xp = torch.mm(X, weights)
+        split = P.target_row is not None
+        beta = float(attention_w.detach().reshape(()))
+        out = ops.agnn_fused(Xp, Xp, P.rowPtr, P.colIdx, beta, softmax=False, target_row=P.target_row,
+                             n_out_rows=Xp.shape[0] if split else None)
+        if not split and out.shape[0] != Xp.shape[0]:  # inputs padded beyond the matrix: zero rows, as the SpMM gives
+            out = torch.cat([out, out.new_zeros(Xp.shape[0] - out.shape[0], out.shape[1])])
+        ctx.save_for_backward(X, weights, Xp)
+        ctx.P, ctx.beta, ctx.colIdx = P, beta, colIdx
+        return out
+
+    @staticmethod
+    def backward(ctx, d_output):
+        from . import ops
+        X, weights, Xp = ctx.saved_tensors
+        P, beta = ctx.P, ctx.beta
+        G = d_output.contiguous()
+        split = P.target_row is not None
+        n_out = G.shape[0] if split else None
+
+        def apply(A, B, V, b):
+            o = ops.agnn_fused(A, B, P.rowPtr, P.colIdx, b, softmax=False, target_row=P.target_row,
+                               n_out_rows=n_out, V=V)
+            if o.shape[0] != G.shape[0]:
+                o = torch.cat([o, o.new_zeros(G.shape[0] - o.shape[0], o.shape[1])])
+            return o
+
+        D = apply(Xp, Xp, G, beta)
+        d_input = torch.mm(D, weights.t())
+        d_weights = torch.mm(X.t(), D)
+        d_att = None
+        if ctx.needs_input_grad[2]:
+            # The reference weights every edge's score gradient by the float value of the column-index
+            # column it is handed, i.e. by the edge's column id j: scale row j of G by j and sum all scores.
+            H = G * torch.arange(G.shape[0], device=G.device, dtype=G.dtype)[:, None]
+            ones = torch.ones(1, G.shape[1], device=G.device, dtype=G.dtype)
+            S = apply(G, H, ones, 1.0)  # every column of row i holds sum_j <G_i, H_j>
+            d_att = S[:, 0].double().sum().to(G.dtype).reshape(1, 1)
+        return d_input, d_weights, d_att, None, None
 
 
 class _Conv(torch.nn.Module):
@@ -171,4 +246,7 @@ class AGNNConv(_Conv):
             split = P.target_row is not None
             return ops.agnn_fused(Xp, Xp, P.rowPtr, P.colIdx, self._beta(), softmax=False,
                                   target_row=P.target_row, n_out_rows=P.mtx_nodes if split else None)
+        if (FUSE_AGNN_TRAINING and torch.is_grad_enabled() and _can_fuse(P, self.weights.size(1))
+                and _is_operator_colidx(P, colIdx)):
+            return AGNNFusedFunction.apply(X, self.weights, self.attention_w, P, colIdx)
         return AGNNFunction.apply(X, self.weights, self.attention_w, P, colIdx)

@@ -501,7 +501,7 @@ def vec_split_sddmm_profile(A, B, rowPtr_split, colIdx, val, target_row, nnz, CF
 
 
 def agnn_fused(A, B, rowPtr, colIdx, beta=1.0, softmax=True, target_row=None, n_out_rows=None, out=None,
-               batch=0, lanes_per_row=0, vec_width=0):
+               batch=0, lanes_per_row=0, vec_width=0, V=None):
     """out_i = sum_j a_ij B_j with a_ij = softmax_j(beta <A_i, B_j>) (or the raw scaled scores when
     ``softmax`` is false) over the stored pattern, in one pass and without a per-edge array.
 
@@ -509,6 +509,10 @@ def agnn_fused(A, B, rowPtr, colIdx, beta=1.0, softmax=True, target_row=None, n_
     csr_sddmm -> ``* attention_w`` -> csr_spmm (gnn_conv.py:130-151).  ``rowPtr`` is the CSR row
     pointer, or the split row pointer when ``target_row`` is given (then ``n_out_rows`` is
     required).  dim must be a multiple of 4, at most 256.
+
+    ``V`` (same shape as ``B``, or a single row ``[1, dim]`` that every column shares) replaces ``B``
+    in the aggregation: ``out_i = sum_j a_ij V_j``.  With ``A = B`` = the projected features and
+    ``V`` = an upstream gradient this is the layer's backward product from recomputed scores.
     """
     _check_cuda(A, "A", torch.float32, 2)
     _check_cuda(B, "B", torch.float32, 2)
@@ -519,6 +523,12 @@ def agnn_fused(A, B, rowPtr, colIdx, beta=1.0, softmax=True, target_row=None, n_
     if A.stride(1) != 1 or B.stride(1) != 1:
         raise RuntimeError("dense operands must be row-major")
     dim = A.shape[1]
+    ldV = None
+    if V is not None:
+        _check_cuda(V, "V", torch.float32, 2)
+        if V.shape[1] != dim or V.shape[0] not in (1, B.shape[0]):
+            raise RuntimeError("V must be [%d, %d] or a single shared row [1, %d]" % (B.shape[0], dim, dim))
+        ldV = 0 if (V.shape[0] == 1 and B.shape[0] != 1) else V.stride(0)
     n_seg = rowPtr.shape[0] - 1
     split = target_row is not None
     if split:
@@ -539,11 +549,17 @@ def agnn_fused(A, B, rowPtr, colIdx, beta=1.0, softmax=True, target_row=None, n_
         sbytes = need.value
         scratch = torch.empty((sbytes + 15) // 16 * 4, dtype=torch.float32, device=A.device)
     seg_ptr = _ptr(rowPtr)
-    check(lib().pspmm_agnn_fused_csr(null if split else seg_ptr, _ptr(colIdx), _ptr(A), _ptr(B), _ptr(out),
-                                     n_out_rows, colIdx.shape[0], dim, A.stride(0), B.stride(0), out.stride(0),
-                                     float(beta), 1 if softmax else 0, int(vec_width), int(lanes_per_row), int(batch),
-                                     seg_ptr if split else null, _ptr(target_row) if split else null,
-                                     n_seg if split else 0, _ptr(scratch) if split else null, sbytes, _stream()))
+    tail = (float(beta), 1 if softmax else 0, int(vec_width), int(lanes_per_row), int(batch),
+            seg_ptr if split else null, _ptr(target_row) if split else null, n_seg if split else 0,
+            _ptr(scratch) if split else null, sbytes, _stream())
+    if V is None:
+        check(lib().pspmm_agnn_fused_csr(null if split else seg_ptr, _ptr(colIdx), _ptr(A), _ptr(B), _ptr(out),
+                                         n_out_rows, colIdx.shape[0], dim, A.stride(0), B.stride(0), out.stride(0),
+                                         *tail))
+    else:
+        check(lib().pspmm_agnn_fused_apply_csr(null if split else seg_ptr, _ptr(colIdx), _ptr(A), _ptr(B), _ptr(V),
+                                               _ptr(out), n_out_rows, colIdx.shape[0], dim, A.stride(0), B.stride(0),
+                                               ldV, out.stride(0), *tail))
     return out
 
 

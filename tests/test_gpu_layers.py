@@ -88,3 +88,61 @@ def test_gin_and_agnn_layers_match_dense_algebra():
     fused = ops.agnn_fused(Xp.float().contiguous(), Xp.float().contiguous(), g.rowPtr.to(dev), g.colIdx.to(dev),
                            float(agnn.attention_w.detach().reshape(())), softmax=False)
     _close(fused, E @ Xp)
+
+
+@pytest.mark.parametrize("split", [False, True])
+def test_agnn_layer_trains_without_edge_arrays(split):
+    """AGNNConv with gradients enabled runs AGNNFusedFunction (forward and backward recompute the
+    scores in the kernel): output, input and weight gradients against dense fp64 algebra with the
+    edge values held constant in the backward, as the reference's layer defines it
+    (gnn_conv.py:153-180); the attention gradient against the reference's expression evaluated in
+    fp64; and everything against the three-kernel composition on the same parameters."""
+    from paramspmm_ae_b200 import gnn_conv, ops, pcsr
+    dev = torch.device("cuda:0")
+    g, A = _graph(dev)
+    n = g.n_rows
+    if split:
+        rps, tr = ops.split_csr(g.rowPtr, 8)
+        P = pcsr.pcsr_sddmm(None, 1, True, n, g.nnz, rps, g.colIdx, g.val, tr, CF=1, blkWarpNum=8)
+    else:
+        P = pcsr.pcsr_sddmm(None, 1, False, n, g.nnz, g.rowPtr, g.colIdx, g.val, None, CF=1, blkWarpNum=8)
+    colIdx = g.colIdx.to(dev).unsqueeze(-1)
+    torch.manual_seed(8)
+    layer = gnn_conv.AGNNConv(16, 32).to(dev)
+    X = torch.randn(n, 16, device=dev) * 0.5
+    G = torch.randn(n, 32, device=dev)
+
+    def run(fused):
+        old = gnn_conv.FUSE_AGNN_TRAINING
+        gnn_conv.FUSE_AGNN_TRAINING = fused
+        try:
+            for p in layer.parameters():
+                p.grad = None
+            x = X.clone().requires_grad_(True)
+            out = layer(x, {32: P}, colIdx)
+            assert (type(out.grad_fn).__name__ == "AGNNFusedFunctionBackward") == fused
+            out.backward(G)
+            return out.detach(), x.grad, layer.weights.grad.clone(), layer.attention_w.grad.clone()
+        finally:
+            gnn_conv.FUSE_AGNN_TRAINING = old
+
+    out, gx, gw, ga = run(True)
+    out_u, gx_u, gw_u, ga_u = run(False)
+    beta = float(layer.attention_w.detach().reshape(()))
+    W64 = layer.weights.detach().double()
+    Xp = X.double() @ W64
+    mask = (A != 0).double()
+    E = (Xp @ Xp.t()) * mask * beta
+    D = E @ G.double()
+    _close(out, E @ Xp)
+    _close(gx, D @ W64.t())
+    _close(gw, X.double().t() @ D)
+    cols = torch.arange(n, device=dev, dtype=torch.float64)
+    want_ga = (((G.double() @ G.double().t()) * mask) * cols[None, :]).sum()
+    scale = ((((G.double() @ G.double().t()) * mask).abs()) * cols[None, :]).sum()
+    assert abs(float(ga) - float(want_ga)) <= 1e-5 * float(scale)      # a signed sum of ~3000 products times ids
+    assert abs(float(ga_u) - float(want_ga)) <= 1e-5 * float(scale)
+    assert ga.shape == ga_u.shape == (1, 1)
+    _close(out, out_u)
+    _close(gx, gx_u)
+    _close(gw, gw_u)

@@ -577,6 +577,34 @@ def test_agnn_fused_matches_the_oracle(dev, oracle, mats, dim, softmax):
             close(got, want)
 
 
+@pytest.mark.parametrize("dim", [4, 32, 64, 100, 128, 256])
+@pytest.mark.parametrize("softmax", [False, True])
+def test_agnn_fused_with_separate_aggregation_operand(dev, oracle, mats, dim, softmax):
+    """out_i = sum_j a_ij V_j with the scores from A and B (pspmm_agnn_fused_apply_csr): a full
+    matrix V, and one row shared by all columns (the row sums of the scores); plain and split."""
+    from paramspmm_ae_b200 import ops
+    for name in ("powerlaw", "rmat", "hub"):
+        m = mats[name]
+        rp, ci, _ = m.numpy()
+        A = torch.nn.functional.normalize(dense(m.n_rows, dim, 910 + dim), dim=1)
+        B = torch.nn.functional.normalize(dense(m.n_cols, dim, 920 + dim), dim=1)
+        V = dense(m.n_cols, dim, 930 + dim)
+        ones = torch.ones(1, dim)
+        d = m.to(dev)
+        for Vm in (V, ones):
+            want = oracle.agnn_aggregate(rp, ci, A.numpy(), B.numpy(), 0.7, softmax, V=Vm.numpy())
+            for lanes in (0, 8, 32):
+                got = ops.agnn_fused(A.to(dev), B.to(dev), d.rowPtr, d.colIdx, 0.7, softmax, V=Vm.to(dev),
+                                     lanes_per_row=lanes if lanes * 16 >= dim or lanes == 0 else 0)
+                close(got, want)
+            rps, tr = ops.split_csr(m.rowPtr, 32)
+            got = ops.agnn_fused(A.to(dev), B.to(dev), rps.to(dev), d.colIdx, 0.7, softmax, target_row=tr.to(dev),
+                                 n_out_rows=m.n_rows, V=Vm.to(dev))
+            close(got, want)
+    with pytest.raises(RuntimeError):
+        ops.agnn_fused(A.to(dev), B.to(dev), d.rowPtr, d.colIdx, V=torch.ones(2, dim, device=dev))
+
+
 def test_agnn_fused_equals_the_unfused_composition(dev, mats):
     """With softmax off and A == B the fused kernel is the reference's AGNN forward:
     csr_sddmm -> * beta -> csr_spmm."""
