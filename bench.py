@@ -285,29 +285,28 @@ def main():
 
     # ---- inputs, resident in HBM before any timing starts
     mats = build_matrices(n, dev, seed_shift=100 * rank)
-    plans, layouts = {}, {}
+    plans, runners, shared = {}, {}, {}
     for name, m in mats.items():
         st = decider.row_stats(m.rowPtr)
         for dim in dims:
-            plans[name, dim] = decider.choose(st, dim)
-        grans = sorted({p["granularity"] for (nm, _), p in plans.items() if nm == name and p["if_split"]})
-        for g in grans:
-            rps, tr = ops.split_csr(m.rowPtr.cpu(), g)
-            layouts[name, g] = (rps.to(dev), tr.to(dev))
+            p = plans[name, dim] = decider.choose(st, dim)
+            # one set of layout arrays per (matrix, layout), shared by the dims that use it
+            key = (name, int(p["if_split"]), p.get("granularity"), int(p.get("bucketed", 0)))
+            if key not in shared:
+                shared[key] = decider.PlannedSpMM(p, m.rowPtr, m.colIdx, m.val)
+            base = shared[key]
+            r = runners[name, dim] = decider.PlannedSpMM.__new__(decider.PlannedSpMM)
+            r.__dict__.update(base.__dict__)
+            r.plan = p
     Bs = {dim: synth.dense_uniform(n, dim, 1000 + dim, dev) for dim in dims}
     Cs = {dim: torch.empty(n, dim, device=dev) for dim in dims}
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     cases = [(name, dim) for dim in dims for name in MATRICES]
 
     def launch(name, dim):
-        m, p = mats[name], plans[name, dim]
-        cfg = _lib.make_cfg(**p.kernel_cfg())
-        if p["if_split"]:
-            rps, tr = layouts[name, p["granularity"]]
-            ops.spmm_into(Cs[dim], Bs[dim], rps, m.colIdx, m.val, target_row=tr, n_out_rows=n, cfg=cfg)
-            return 2
-        ops.spmm_into(Cs[dim], Bs[dim], m.rowPtr, m.colIdx, m.val, cfg=cfg)
-        return 1
+        r = runners[name, dim]
+        r(Cs[dim], Bs[dim])
+        return r.launches
 
     def one_pass(events=None):
         launches = 0
@@ -353,12 +352,12 @@ def main():
     sweep = []
     for (name, dim), ms in zip(cases, mean_ms):
         p = plans[name, dim]
-        n_seg = layouts[name, p["granularity"]][1].numel() if p["if_split"] else None
+        n_seg = runners[name, dim].n_seg if p["if_split"] else None
         by = spmm_bytes(n, n, mats[name].nnz, dim, n_seg)
         sweep.append({"matrix": name, "dim": dim, "ms": round(ms, 5),
                       "gflops": round(2.0 * mats[name].nnz * dim / ms / 1e6, 1),
                       "gbs": round(by / ms / 1e6, 1), "frac": round(by / ms / 1e6 / peak, 4),
-                      "split": int(p["if_split"])})
+                      "split": int(p["if_split"]), "bucketed": int(p.get("bucketed", 0))})
 
     def roofline_of(i):
         r = {"bound": "hbm", "achieved": sweep[i]["gbs"], "peak": peak, "unit": "GB/s", "frac": sweep[i]["frac"],
@@ -531,7 +530,7 @@ def main():
     scaleout = None
     if not args.no_scaleout:
         from paramspmm_ae_b200 import workloads
-        del Bs, Cs, mats, layouts, flush
+        del Bs, Cs, mats, runners, shared, flush
         torch.cuda.empty_cache()
         try:
             r = workloads.scaleout_brief(scale=args.c5_scale, nnz=args.c5_nnz, iters=args.scaleout_iters, rank=rank,

@@ -62,6 +62,8 @@ typedef struct pspmm_cfg {
                                 several launches over column ranges.  0 = one launch */
     int32_t hint_CF;         /* legacy coarsening factor, validated only */
     int32_t hint_blkWarpNum; /* legacy warps per block, validated only */
+    int32_t bucketed;        /* SpMM on a split layout only: 1 = the split arrays are a length-bucketed plan (see
+                                pspmm_spmm_csr): segments in any order, flags in the two high bits of target_row */
     int32_t accumulate;      /* SpMM only: 0 = C is overwritten (every row is written, empty rows with zeros);
                                 1 = the product is added to what C holds (reduction instructions; the order in
                                 which contributions reach a row is not fixed).  Lets a caller sum products over
@@ -87,6 +89,14 @@ PSPMM_API int pspmm_resolve_cfg(pspmm_cfg *cfg, int32_t dim, int64_t ldB, int64_
  * the output may have a different row count from B (row shards) and C needs no prior zeroing:
  * rows without entries are written as zeros.  Rows cut into several pieces are accumulated
  * with vector atomics, so their summation order is not fixed.
+ *
+ * Length-bucketed plan (cfg->bucketed = 1; an internal layout of this library, not one of the
+ * reference's): the segments may come in any order, typically sorted by length so that the lane
+ * groups of a warp walk equally long pieces, with colIdx / val permuted to match (segment s owns
+ * entries rowPtr_split[s] .. rowPtr_split[s+1]).  target_row[s] then holds the row in its low 30
+ * bits, bit 31 set when the row has more than one segment (all of them add with atomics) and
+ * bit 30 set on exactly one segment of such a row (the pre-pass zeroes the row there).  Every row
+ * must appear: rows without entries as empty segments.  n_rows must be below 2^30.
  */
 PSPMM_API int pspmm_spmm_csr(const int32_t *rowPtr, const int32_t *colIdx, const float *val,
                    const float *B, float *C, int64_t n_rows, int64_t n_cols, int64_t nnz,

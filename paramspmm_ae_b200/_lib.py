@@ -32,7 +32,7 @@ class PspmmCfg(ctypes.Structure):
 
     _fields_ = [("lanes_per_row", _i32), ("vec_width", _i32), ("cta_threads", _i32),
                 ("rows_per_group", _i32), ("gather_batch", _i32), ("col_tile", _i32), ("hint_CF", _i32),
-                ("hint_blkWarpNum", _i32), ("accumulate", _i32)]
+                ("hint_blkWarpNum", _i32), ("bucketed", _i32), ("accumulate", _i32)]
 
 
 class MtxInfo(ctypes.Structure):
@@ -139,6 +139,6 @@ def check(code):
 
 
 def make_cfg(CF=0, blkWarpNum=0, lanes_per_row=0, vec_width=0, cta_threads=0, rows_per_group=0,
-             gather_batch=0, col_tile=0, accumulate=0):
+             gather_batch=0, col_tile=0, accumulate=0, bucketed=0):
     return PspmmCfg(lanes_per_row, vec_width, cta_threads, rows_per_group, gather_batch, col_tile, CF, blkWarpNum,
-                    accumulate)
+                    bucketed, accumulate)

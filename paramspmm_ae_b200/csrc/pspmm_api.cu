@@ -64,6 +64,8 @@ int pspmm_validate_cfg(const pspmm_cfg *cfg, bool sddmm)
         return PSPMM_E_CONFIG;
     if (cfg->col_tile < 0 || cfg->col_tile % 4 != 0)
         return PSPMM_E_CONFIG;
+    if (cfg->bucketed != 0 && (cfg->bucketed != 1 || sddmm))
+        return PSPMM_E_CONFIG;
     return PSPMM_OK;
 }
 
@@ -243,6 +245,35 @@ zero_shared_rows_kernel(const int32_t *__restrict__ target_row, int64_t n_seg, i
             zero_part(r, sl, lanes_row);
 }
 
+// Pre-pass of a length-bucketed plan: rows that are cut into several segments receive REDs from all
+// of them and must start from zero; the segment flagged as the first one of its row zeroes it.
+// (Rows with a single segment, empty ones included, are stored by the SpMM kernel itself.)
+// One warp looks at 32 segments and zeroes the flagged rows one after the other, all lanes on a row.
+__global__ void __launch_bounds__(256)
+zero_first_pieces_kernel(const int32_t *__restrict__ target_row, int64_t n_seg, int V, float *C, int64_t ldC,
+                         int dim, int vecok)
+{
+    const int64_t s = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int lane = threadIdx.x & 31;
+    const unsigned t = s < n_seg ? (unsigned)__ldg(target_row + s) : 0u;
+    unsigned todo = __ballot_sync(PSPMM_FULL_MASK, (t & PSPMM_SEG_FIRST) != 0);
+    while (todo) {
+        const int src = __ffs(todo) - 1;
+        todo &= todo - 1;
+        const int64_t r = (int64_t)(__shfl_sync(PSPMM_FULL_MASK, t, src) & PSPMM_SEG_ROW_MASK);
+        for (int w = 0; w < V; ++w) {
+            float *row = C + (r * V + w) * ldC;
+            if (vecok) {
+                for (int j = lane * 4; j < dim; j += 128)
+                    *reinterpret_cast<float4 *>(row + j) = make_float4(0.f, 0.f, 0.f, 0.f);
+            } else {
+                for (int j = lane; j < dim; j += 32)
+                    row[j] = 0.f;
+            }
+        }
+    }
+}
+
 // ----------------------------------------------------------------------------- SpMM
 static int check_sizes(int64_t n_rows, int64_t n_cols, int64_t nnz, int32_t dim)
 {
@@ -325,10 +356,15 @@ static int spmm_launch(const int32_t *segPtr, const int32_t *target_row, int64_t
         }
     }
 
+    const bool bucketed = target_row && cfg && cfg->bucketed;
     if (target_row && !accumulate) {
         const int vecok = (dim % 4 == 0 && ldC % 4 == 0 && ((uintptr_t)C) % 16 == 0) ? 1 : 0;
-        zero_shared_rows_kernel<<<(unsigned)((n_seg + 255) / 256), 256, 0, st>>>(
-            target_row, n_seg, n_out_blk_rows, s.rpg, V, C, ldC, dim, vecok);
+        if (bucketed)
+            zero_first_pieces_kernel<<<(unsigned)((n_seg + 255) / 256), 256, 0, st>>>(target_row, n_seg, V, C, ldC,
+                                                                                      dim, vecok);
+        else
+            zero_shared_rows_kernel<<<(unsigned)((n_seg + 255) / 256), 256, 0, st>>>(
+                target_row, n_seg, n_out_blk_rows, s.rpg, V, C, ldC, dim, vecok);
     }
 
     SpmmArgs a;
@@ -344,6 +380,7 @@ static int spmm_launch(const int32_t *segPtr, const int32_t *target_row, int64_t
     a.ldC = ldC;
     a.nvec = dim / s.vw;
     a.rows_per_group = s.rpg;
+    a.bucketed = bucketed ? 1 : 0;
     a.keep_fraction = l2_keep_fraction((double)n_cols * (double)ldB * 4.0);
     const int64_t per_cta = (int64_t)(s.threads / s.lpr) * s.rpg;
     const int64_t gx = (n_seg + per_cta - 1) / per_cta;

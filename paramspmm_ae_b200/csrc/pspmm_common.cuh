@@ -36,7 +36,13 @@ struct SpmmArgs {
     int32_t nvec;               // dim / VW: vectors per dense row
     int32_t rows_per_group;
     float keep_fraction;        // share of B's lines marked evict-last in L2 (0..1]
+    int32_t bucketed;           // target_row carries PSPMM_SEG_* flags, segments come in any order
 };
+
+// Flags in target_row of a length-bucketed plan (pspmm_cfg.bucketed): the low 30 bits are the row.
+#define PSPMM_SEG_MULTI 0x80000000u  // the row is cut into several segments: every one of them adds with REDs
+#define PSPMM_SEG_FIRST 0x40000000u  // the first of them: the pre-pass zeroes the row when it meets this one
+#define PSPMM_SEG_ROW_MASK 0x3fffffffu
 
 struct SddmmArgs {
     const int32_t *segPtr;

@@ -216,7 +216,17 @@ __global__ void __launch_bounds__(256, SpmmOcc<MLP>::MIN_CTAS) spmm_seg_kernel(c
             int64_t orow = first + row;
             bool shared = false;
             int next = 0;
-            if (split) {
+            if (split && a.bucketed) {
+                // Length-bucketed plan: segments in any order, flags in the high bits of the target.
+                const unsigned me = (unsigned)st[row + 1];
+                const unsigned nx = (unsigned)st[row + 2];
+                if (row + 1 < nrow && ((nx ^ me) & PSPMM_SEG_ROW_MASK) == 0) {
+                    ++row;  // the group's next segment is another piece of the same row
+                    continue;
+                }
+                orow = me & PSPMM_SEG_ROW_MASK;
+                shared = (me & PSPMM_SEG_MULTI) != 0;
+            } else if (split) {
                 const int me = st[row + 1];
                 next = st[row + 2];
                 if (next == me && row + 1 < nrow) {
@@ -246,7 +256,7 @@ __global__ void __launch_bounds__(256, SpmmOcc<MLP>::MIN_CTAS) spmm_seg_kernel(c
                         acc[w][cf][i] = 0.f;
                 }
             }
-            if (!ACC && split) {
+            if (!ACC && split && !a.bucketed) {
                 // Rows strictly between this segment's row and the next segment's row (and, for
                 // the very first segment, the rows before it) have no entries: zero short runs
                 // here; runs longer than PSPMM_GAP_MAX are left to the pre-pass.

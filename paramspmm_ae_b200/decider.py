@@ -15,6 +15,8 @@ import json
 import math
 import os
 
+import torch
+
 _HERE = os.path.dirname(os.path.abspath(__file__))
 TABLE_PATH = os.path.join(_HERE, "config_table.json")
 
@@ -97,7 +99,8 @@ class Plan(dict):
 
     def kernel_cfg(self):
         return {k: int(self.get(k, 0) or 0)
-                for k in ("lanes_per_row", "vec_width", "cta_threads", "rows_per_group", "gather_batch", "col_tile")}
+                for k in ("lanes_per_row", "vec_width", "cta_threads", "rows_per_group", "gather_batch", "col_tile",
+                          "bucketed")}
 
 
 def choose(stats, dim, op="spmm"):
@@ -120,12 +123,56 @@ def choose(stats, dim, op="spmm"):
     if e is None:
         e = {"if_split": 1 if reg.endswith("skewed") else 0, "vec_size": 1}
     plan = Plan(if_split=0, vec_size=1, granularity=None, lanes_per_row=0, vec_width=0, cta_threads=0,
-                rows_per_group=0, gather_batch=0, col_tile=0)
+                rows_per_group=0, gather_batch=0, col_tile=0, bucketed=0)
     plan.update(e)
     plan["regime"] = reg
     if plan["if_split"] and not plan.get("granularity"):
         plan["granularity"] = auto_granularity(stats["real_avg"])
     return plan
+
+
+class PlannedSpMM:
+    """A plan bound to one matrix: builds the arrays the plan's layout needs once (the PCSR split on
+    the device, or the length-bucketed plan with its permuted entries) and launches the SpMM with
+    the plan's kernel parameters.  ``rowPtr`` / ``colIdx`` / ``val`` are CUDA tensors of a CSR matrix."""
+
+    def __init__(self, plan, rowPtr, colIdx, val, n_cols=None):
+        from . import ops
+        self.plan, self.n_rows = plan, rowPtr.shape[0] - 1
+        self.V = int(plan.get("vec_size", 1) or 1)
+        self.n_seg_rows = self.n_rows  # (block-)rows of the output
+        if self.V > 1:  # V x 1 blocks: built by the host builder (scipy's tobsr layout), then moved back
+            dev = rowPtr.device
+            if n_cols is None:
+                n_cols = int(colIdx.max()) + 1 if colIdx.numel() else 1
+            rowPtr, colIdx, val = (t.to(dev) for t in ops.bcsr_from_csr(rowPtr.cpu(), colIdx.cpu(), val.cpu(), n_cols, self.V))
+            self.n_seg_rows = rowPtr.shape[0] - 1
+        self.colIdx, self.val, self.target = colIdx, val, None
+        self.segPtr = rowPtr
+        if plan.get("bucketed") and plan["if_split"]:
+            self.segPtr, self.colIdx, self.val, self.target = ops.bucket_pcsr(rowPtr, colIdx, val, int(plan["granularity"]))
+        elif plan["if_split"]:
+            self.segPtr, self.target = ops.split_csr_device(rowPtr, int(plan["granularity"]))
+        self.n_seg = self.segPtr.shape[0] - 1
+
+    def __call__(self, out, B, accumulate=False):
+        from . import _lib, ops
+        kw = self.plan.kernel_cfg()
+        if accumulate:  # built for 128-bit loads at one gather-batch depth
+            kw.update(vec_width=0, gather_batch=0, accumulate=1)
+        dst = out
+        if out.shape[0] < self.n_seg_rows * self.V:  # block layouts write whole blocks: an odd row count needs a pad row
+            dst = torch.empty(self.n_seg_rows * self.V, out.shape[1], dtype=out.dtype, device=out.device)
+        ops.spmm_into(dst, B, self.segPtr, self.colIdx, self.val, target_row=self.target, V=self.V,
+                      n_out_rows=self.n_seg_rows, cfg=_lib.make_cfg(**kw))
+        if dst is not out:
+            out.copy_(dst[: out.shape[0]])
+        return out
+
+    @property
+    def launches(self):
+        """Kernels per product: the SpMM, plus the zeroing pre-pass of a split layout."""
+        return 2 if self.target is not None else 1
 
 
 def legacy_tuple(plan, dim):
@@ -234,19 +281,17 @@ def main(argv=None):
             plan = decider.plan(graph, dim)
             legacy = decider.config_PCSR(graph, dim)
             X = torch.ones(n, dim, device=dev)
-            cfg = _lib.make_cfg(**plan.kernel_cfg())
             out = torch.empty(n, dim, device=dev)
-            if plan["if_split"]:
-                g = int(plan["granularity"])
-                if g not in layouts:
-                    layouts[g] = ops.split_csr_device(rp, g)
-                seg, tr = layouts[g]
-            else:
-                seg, tr = rp, None
-            ops.spmm_into(out, X, seg, ci, v, target_row=tr, n_out_rows=n, cfg=cfg)
+            key = (int(plan["if_split"]), plan.get("granularity"), int(plan.get("bucketed", 0)))
+            if key not in layouts:
+                layouts[key] = PlannedSpMM(plan, rp, ci, v)
+            op = layouts[key]
+            op.plan = plan
+            op(out, X)
             veri.reference(dim)
             veri.compare(out.cpu(), name)
-            ms = ops.spmm_time_ms(X, seg, ci, v, tr, cfg=cfg, n_out_rows=n)
+            ms = ops.spmm_time_ms(X, op.segPtr, op.colIdx, op.val, op.target, cfg=_lib.make_cfg(**plan.kernel_cfg()),
+                                  n_out_rows=n)
             rec = {"mtx": name, "nodes": n, "edges": nnz, "dim": dim, "regime": plan["regime"],
                    "if_split": int(plan["if_split"]), "vec_size": int(plan["vec_size"]),
                    "granularity": plan["granularity"], "kernel": plan.kernel_cfg(), "legacy_tuple": list(legacy),

@@ -205,6 +205,60 @@ def split_csr_device(rowPtr, granularity):
     return [rps, tr]
 
 
+SEG_MULTI, SEG_FIRST, SEG_ROW_MASK = 0x80000000, 0x40000000, 0x3FFFFFFF
+
+
+def bucket_pcsr(rowPtr, colIdx, val, granularity):
+    """Length-bucketed plan of a (block-)CSR matrix for ``pspmm_cfg.bucketed``: the rows are cut into
+    pieces of at most ``granularity`` entries exactly as :func:`split_csr` cuts them, the pieces are
+    then ordered by length, longest first (a stable sort: pieces of one row stay together and in
+    order), rows without entries follow as empty pieces, and the entries are permuted to match.
+    Returns ``(segPtr, colIdx_p, val_p, target)``; ``target`` carries the row in its low 30 bits,
+    bit 31 on every piece of a row that has several, bit 30 on the first of those.
+
+    This is an internal layout of the sm_100a kernels (the lane groups of a warp then walk equally
+    long pieces and no batch of gathers is cut short by a neighbouring row's end); the arrays the
+    reference defines, ``split_csr``'s, are untouched by it.  Built with torch ops on the device the
+    inputs live on; it is set-up work, done once per matrix and partition length."""
+    rp = rowPtr.long()
+    n = rp.numel() - 1
+    if n >= SEG_FIRST:
+        raise RuntimeError("the bucketed plan holds row ids in 30 bits")
+    dev = rp.device
+    ln = rp[1:] - rp[:-1]
+    g = int(granularity)
+    pieces = torch.div(ln + g - 1, g, rounding_mode="floor")          # per row; 0 for empty rows
+    S = int(pieces.sum())
+    tr = torch.repeat_interleave(torch.arange(n, device=dev), pieces)   # row of every piece (non-decreasing)
+    first_piece = torch.cumsum(pieces, 0) - pieces                      # index of each row's first piece
+    k = torch.arange(S, device=dev) - first_piece[tr]                   # position of the piece inside its row
+    start = rp[:-1][tr] + k * g
+    plen = torch.minimum(rp[1:][tr], start + g) - start
+    multi = pieces[tr] > 1
+    order = torch.argsort(plen, descending=True, stable=True)
+    empty = torch.nonzero(pieces == 0).flatten()
+    flags = multi.long() * SEG_MULTI + (multi & (k == 0)).long() * SEG_FIRST
+    target = torch.cat([(tr | flags)[order], empty])
+    plen_b = torch.cat([plen[order], torch.zeros_like(empty)])
+    seg = torch.zeros(target.numel() + 1, dtype=torch.long, device=dev)
+    seg[1:] = torch.cumsum(plen_b, 0)
+    # entries: piece `order[i]` moves to segment i
+    new_start = torch.empty(S, dtype=torch.long, device=dev)
+    new_start[order] = seg[:S]
+    piece_of_entry = torch.repeat_interleave(torch.arange(S, device=dev), plen)
+    # entries are stored piece after piece in the original arrays, so entry e belongs to piece_of_entry[e]
+    pos = new_start[piece_of_entry] + (torch.arange(piece_of_entry.numel(), device=dev) + int(rp[0]) - start[piece_of_entry])
+    lo = int(rp[0])
+    src_c, src_v = colIdx[lo: lo + pos.numel()], val[lo: lo + pos.numel()]
+    ci_p = torch.empty_like(src_c)
+    v_p = torch.empty_like(src_v)
+    ci_p[pos] = src_c
+    v_p[pos] = src_v
+    # values above 2^31 wrap into the sign bit of int32, which is where the kernels look for them
+    target32 = torch.where(target >= 2**31, target - 2**32, target).to(torch.int32)
+    return seg.to(torch.int32), ci_p, v_p, target32
+
+
 def bcsr_from_csr(rowPtr, colIdx, val, n_cols, V=2):
     """CSR (CPU tensors) -> V x 1 block CSR laid out as scipy's tobsr((V,1)) does
     (what graph_input.py:245-266 of the reference builds)."""

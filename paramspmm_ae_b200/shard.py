@@ -501,25 +501,20 @@ class ShardedSpMM:
         """The CUDA operator with the configuration the decider picks for the row-length statistics
         of this shard (or of one column block of it) and the (slice of the) dense width; a split
         layout, when chosen, is built once on the device from the row pointer and kept."""
-        from . import _lib, decider, ops
+        from . import decider
 
         stats = decider.row_stats(self.rowPtr if rowPtr is None else rowPtr)
-        layouts = {}
+        bound = {}
 
         def local_spmm(out, B, rowPtr, colIdx, val, accumulate=False):
             p = decider.choose(stats, B.shape[1])
-            kw = p.kernel_cfg()
-            if accumulate:  # built for 128-bit loads at one gather-batch depth
-                kw.update(vec_width=0, gather_batch=0, accumulate=1)
-            cfg = _lib.make_cfg(**kw)
-            if p["if_split"]:
-                g = int(p["granularity"])
-                if g not in layouts:
-                    layouts[g] = ops.split_csr_device(rowPtr, g)
-                rps, tr = layouts[g]
-                return ops.spmm_into(out, B, rps, colIdx, val, target_row=tr, n_out_rows=rowPtr.shape[0] - 1,
-                                     cfg=cfg)
-            return ops.spmm_into(out, B, rowPtr, colIdx, val, cfg=cfg)
+            # (a bucketed plan permutes the entries, so it belongs to one column / value array pair)
+            key = (int(p["if_split"]), p.get("granularity"), int(p.get("bucketed", 0)), colIdx.data_ptr(), val.data_ptr())
+            if key not in bound:  # layout arrays of this plan, built once on the device and kept
+                bound[key] = decider.PlannedSpMM(p, rowPtr, colIdx, val)
+            op = bound[key]
+            op.plan = p
+            return op(out, B, accumulate=accumulate)
 
         return local_spmm
 

@@ -106,9 +106,12 @@ def candidates(dim, regime, quick=False, vecs=(1, 2), cta_threads=(64, 128, 256)
             continue  # column ranges narrower than a lane group make no sense; tiles measured at one shape
         if tile and tile < 128 and skew:
             continue  # narrow column ranges re-read A for every range: only the even regimes try them
-        yield {"vec_size": vec, "if_split": int(gran > 0), "granularity": gran or None,
-               "lanes_per_row": lpr, "vec_width": vw, "rows_per_group": rpg, "cta_threads": thr,
-               "gather_batch": mlp, "col_tile": tile}
+        base = {"vec_size": vec, "if_split": int(gran > 0), "granularity": gran or None,
+                "lanes_per_row": lpr, "vec_width": vw, "rows_per_group": rpg, "cta_threads": thr,
+                "gather_batch": mlp, "col_tile": tile, "bucketed": 0}
+        yield base
+        if skew and gran and vec == 1 and not tile:
+            yield dict(base, bucketed=1)  # the same pieces ordered by length
 
 
 class Layouts:
@@ -117,8 +120,8 @@ class Layouts:
     def __init__(self, m, device):
         self.m, self.dev, self.cache = m, device, {}
 
-    def get(self, vec, gran):
-        key = (vec, gran)
+    def get(self, vec, gran, bucketed=False):
+        key = (vec, gran, bool(bucketed))
         if key in self.cache:
             return self.cache[key]
         m = self.m
@@ -131,7 +134,9 @@ class Layouts:
                                              ops.bcsr_from_csr(c.rowPtr, c.colIdx, c.val, m.n_cols, vec))
             rp, ci, v = self.cache["b", vec]
         tr = None
-        if gran:
+        if gran and bucketed:
+            rp, ci, v, tr = ops.bucket_pcsr(rp, ci, v, gran)
+        elif gran:
             rp, tr = ops.split_csr_device(rp, gran)
         self.cache[key] = (rp, ci, v, tr)
         return self.cache[key]
@@ -168,12 +173,13 @@ class Timer:
         if not cand.get("if_split") and self.max_row > 4096:
             return None  # one lane group per hub row would take milliseconds
         V = cand.get("vec_size", 1)
-        rp, ci, v, tr = self.lay.get(V, cand.get("granularity") if cand.get("if_split") else None)
+        rp, ci, v, tr = self.lay.get(V, cand.get("granularity") if cand.get("if_split") else None,
+                                     cand.get("bucketed"))
         nbr = (m.n_rows + V - 1) // V
         out = torch.full((nbr * V, dim), float("nan"), device=self.dev)
         cfg = _lib.make_cfg(**{k: int(cand.get(k, 0) or 0) for k in
                                ("lanes_per_row", "vec_width", "cta_threads", "rows_per_group", "gather_batch",
-                                "col_tile")})
+                                "col_tile", "bucketed")})
         ops.spmm_into(out, self.B, rp, ci, v, target_row=tr, V=V, n_out_rows=nbr, cfg=cfg)
         bad = int(((out[: m.n_rows] - self.ref).abs() > self.tol).sum())
         if bad or bool(torch.isnan(out[: m.n_rows]).any()):

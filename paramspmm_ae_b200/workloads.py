@@ -166,6 +166,42 @@ def agnn_layer(n=232_965, pairs=57_180_000, dim=64, seed=41, iters=10, grans=(0,
     out["fused"] = fused
     out["fused_best_ms"] = min(f["fused_ms"] for f in fused)
     out["fused_softmax_best_ms"] = min(f["fused_softmax_ms"] for f in fused)
+    # One training step of the layer (projection, propagation, backward to the input, the weights and
+    # the attention weight): the reference's three-kernel composition, which writes the attention
+    # values and the score gradient per edge, against the fused function, which writes neither.
+    from . import gnn_conv, pcsr
+    gfast = min((f for f in fused if (f["vec_width"], f["lanes_per_row"], f["batch"]) == (0, 0, 0)),
+                key=lambda f: f["fused_ms"])["granularity"]
+    rps, tr = layouts[gfast]
+    P = pcsr.pcsr_sddmm(None, 1, True, n, nnz, rps, g.colIdx, g.val, tr, CF=(dim + 31) // 32, blkWarpNum=8)
+    torch.manual_seed(seed + 5)
+    conv = gnn_conv.AGNNConv(dim, dim).to(dev)
+    col = g.colIdx.unsqueeze(-1)
+    Gup = synth.dense_normal(n, dim, seed + 6, dev)
+    Xin = X.clone().requires_grad_(True)
+
+    def train_step():
+        for p_ in conv.parameters():
+            p_.grad = None
+        Xin.grad = None
+        conv(Xin, {dim: P}, col).backward(Gup)
+
+    steps = {}
+    old = gnn_conv.FUSE_AGNN_TRAINING
+    try:
+        for label, flag in (("three_kernels", False), ("fused", True)):
+            gnn_conv.FUSE_AGNN_TRAINING = flag
+            torch.cuda.reset_peak_memory_stats()
+            base = torch.cuda.memory_allocated()
+            steps[label + "_ms"] = round(_time_ms(train_step, warmup=2, iters=iters), 4)
+            steps[label + "_peak_extra_bytes"] = int(torch.cuda.max_memory_allocated() - base)
+            steps[label + "_grads"] = [Xin.grad.clone(), conv.weights.grad.clone()]
+    finally:
+        gnn_conv.FUSE_AGNN_TRAINING = old
+    for a_, b_ in zip(steps.pop("three_kernels_grads"), steps.pop("fused_grads")):
+        scale = float(a_.abs().max())
+        torch.testing.assert_close(b_, a_, rtol=1e-4, atol=1e-5 * max(1.0, scale))
+    out["layer_training_step"] = dict(steps, granularity=gfast)
     return out
 
 

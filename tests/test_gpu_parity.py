@@ -681,3 +681,62 @@ def test_pull_transport_single_rank(dev, oracle, mats, exchange, row_chunks):
     src = op.symmetric_input(64)   # a producer writes the block in place: no staging copy
     src.copy_(Bd)
     close(op.forward(src), want)
+
+
+# ----------------------------------------------------------------------------- length-bucketed plan
+@pytest.mark.parametrize("name", ["powerlaw", "rmat", "hub", "uniform16", "tiny"])
+@pytest.mark.parametrize("gran", [1, 7, 32, 512])
+def test_bucketed_plan_spmm_matches_oracle(dev, oracle, mats, name, gran):
+    """pspmm_cfg.bucketed: the pieces of split_csr ordered by length, entries permuted, flags in the
+    high bits of target_row; every kernel shape, overwrite and accumulate, CSR and 2 x 1 blocks."""
+    from paramspmm_ae_b200 import _lib, ops
+    m = mats[name]
+    rp, ci, v = m.numpy()
+    d = m.to(dev)
+    seg, ci_p, v_p, tg = ops.bucket_pcsr(d.rowPtr, d.colIdx, d.val, gran)
+    assert seg.dtype == torch.int32 and tg.dtype == torch.int32 and int(seg[-1]) == m.nnz
+    ln = (seg[1:] - seg[:-1])
+    assert bool((ln[:-1] >= ln[1:]).all()) and int(ln.max()) <= gran
+    rows = (tg.long() & ops.SEG_ROW_MASK)
+    assert int(torch.bincount(rows, minlength=m.n_rows).min()) >= 1  # every row appears, empty ones too
+    for dim in (4, 16, 47, 64, 128, 256):
+        B = dense(m.n_cols, dim, 200 + dim)
+        want = oracle.spmm_csr(rp, ci, v, B.numpy())
+        for lanes, rpg, thr in ((0, 0, 0), (4, 2, 64), (32, 8, 128), (16, 1, 256)):
+            cfg = _lib.make_cfg(bucketed=1, lanes_per_row=lanes, rows_per_group=rpg, cta_threads=thr)
+            out = torch.full((m.n_rows, dim), float("nan"), device=dev)
+            ops.spmm_into(out, B.to(dev), seg, ci_p, v_p, target_row=tg, n_out_rows=m.n_rows, cfg=cfg)
+            close(out, want)
+        if dim % 4 == 0:
+            acc = torch.ones(m.n_rows, dim, device=dev)
+            ops.spmm_into(acc, B.to(dev), seg, ci_p, v_p, target_row=tg, n_out_rows=m.n_rows,
+                          cfg=_lib.make_cfg(bucketed=1, accumulate=1))
+            close(acc, want + 1.0)
+    # 2 x 1 blocks through the same plan builder
+    rpb, cb, vb = ops.bcsr_from_csr(m.rowPtr, m.colIdx, m.val, m.n_cols, 2)
+    seg, cb_p, vb_p, tg = ops.bucket_pcsr(rpb.to(dev), cb.to(dev), vb.to(dev), gran)
+    B = dense(m.n_cols, 64, 9)
+    nbr = rpb.shape[0] - 1
+    out = torch.full((nbr * 2, 64), float("nan"), device=dev)
+    ops.spmm_into(out, B.to(dev), seg, cb_p, vb_p, target_row=tg, V=2, n_out_rows=nbr, cfg=_lib.make_cfg(bucketed=1))
+    close(out[: m.n_rows], oracle.spmm_csr(rp, ci, v, B.numpy()))
+
+
+def test_planned_spmm_runs_every_layout(dev, oracle, mats):
+    """decider.PlannedSpMM: plain, split and bucketed plans give the same product."""
+    from paramspmm_ae_b200 import decider
+    m = mats["powerlaw"]
+    rp, ci, v = m.numpy()
+    d = m.to(dev)
+    B = dense(m.n_cols, 64, 12)
+    want = oracle.spmm_csr(rp, ci, v, B.numpy())
+    for kw in (dict(if_split=0), dict(if_split=1, granularity=32), dict(if_split=1, granularity=32, bucketed=1)):
+        plan = decider.Plan(vec_size=1, lanes_per_row=0, vec_width=0, cta_threads=0, rows_per_group=0,
+                            gather_batch=0, col_tile=0, bucketed=0, granularity=None)
+        plan.update(kw)
+        op = decider.PlannedSpMM(plan, d.rowPtr, d.colIdx, d.val)
+        out = torch.full((m.n_rows, 64), float("nan"), device=dev)
+        op(out, B.to(dev))
+        close(out, want)
+        op(out, B.to(dev), accumulate=True)
+        close(out, 2 * want)

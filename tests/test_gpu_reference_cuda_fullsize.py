@@ -65,7 +65,7 @@ def _assert_rows_close(ours, theirs, row_len, what):
 @pytest.mark.parametrize("name", ["uniform", "banded", "rmat"])
 @pytest.mark.parametrize("dim", [16, 64, 128, 256])
 def test_full_size_spmm_equals_reference_cuda(ref_spmm, mats, name, dim):
-    from paramspmm_ae_b200 import _lib, baselines, decider, ops, synth
+    from paramspmm_ae_b200 import baselines, decider, ops, synth
     dev = torch.device("cuda:0")
     m = mats[name]
     X = synth.dense_uniform(N, dim, 1000 + dim, dev)
@@ -82,13 +82,9 @@ def test_full_size_spmm_equals_reference_cuda(ref_spmm, mats, name, dim):
     _assert_rows_close(ops.csr_spmm(X, m.rowPtr, m.colIdx, m.val, CF, 8), theirs, row_len, "csr_spmm")
     _assert_rows_close(ops.csr_split_spmm(X, rps, m.colIdx, m.val, tr, CF, 8), theirs, row_len, "csr_split_spmm")
     plan = decider.choose(decider.row_stats(m.rowPtr), dim)
-    cfg = _lib.make_cfg(**plan.kernel_cfg())
+    op = decider.PlannedSpMM(plan, m.rowPtr, m.colIdx, m.val)
     C = torch.full((N, dim), float("nan"), device=dev)
-    if plan["if_split"]:
-        p_rps, p_tr = ops.split_csr_device(m.rowPtr, int(plan["granularity"]))
-        run = lambda: ops.spmm_into(C, X, p_rps, m.colIdx, m.val, target_row=p_tr, n_out_rows=N, cfg=cfg)
-    else:
-        run = lambda: ops.spmm_into(C, X, m.rowPtr, m.colIdx, m.val, cfg=cfg)
+    run = lambda: op(C, X)
     run()
     _assert_rows_close(C, theirs, row_len, "decider-planned launch")
 
