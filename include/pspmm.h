@@ -41,7 +41,7 @@ extern "C" {
 #define PSPMM_E_CONFIG (-2)   /* a pspmm_cfg field or CF / blkWarpNum hint outside its domain */
 #define PSPMM_E_CUDA (-3)     /* a CUDA runtime call or kernel launch failed */
 #define PSPMM_E_UNSUPPORTED (-4)
-#define PSPMM_E_RANGE (-5)    /* a size exceeds what int32 indices can address */
+#define PSPMM_E_RANGE (-5)    /* a size exceeds what int32 indices (or a fixed built-in buffer) can address */
 #define PSPMM_E_IO (-6)       /* a file cannot be opened, mapped, written or renamed */
 #define PSPMM_E_FORMAT (-7)   /* a file's contents contradict its header (or its checksum) */
 #define PSPMM_E_NOMEM (-8)    /* host memory for temporary arrays could not be obtained */

@@ -28,7 +28,7 @@ extern "C" const char *pspmm_strerror(int code)
     case PSPMM_E_CONFIG: return "invalid configuration (CF must be 1..8 (1..4 for SDDMM), blkWarpNum 4 or 8, lanes_per_row a power of two <= 32, vec_width 1/2/4, cta_threads 32/64/128/256, rows_per_group 1..16)";
     case PSPMM_E_CUDA: return "CUDA error (see pspmm_last_cuda_error)";
     case PSPMM_E_UNSUPPORTED: return "unsupported combination";
-    case PSPMM_E_RANGE: return "size exceeds the int32 index range";
+    case PSPMM_E_RANGE: return "size exceeds the int32 index range (or, for pspmm_split_csr_device_static, the 16,777,216 rows its built-in scratch covers)";
     case PSPMM_E_IO: return "file cannot be opened, mapped, written or renamed";
     case PSPMM_E_FORMAT: return "file contents contradict the header or the checksum";
     case PSPMM_E_NOMEM: return "out of host memory";
