@@ -287,7 +287,7 @@ def main():
     mats = build_matrices(n, dev, seed_shift=100 * rank)
     plans, runners, shared = {}, {}, {}
     for name, m in mats.items():
-        st = decider.row_stats(m.rowPtr)
+        st = decider.row_stats(m.rowPtr, m.colIdx)
         for dim in dims:
             p = plans[name, dim] = decider.choose(st, dim)
             # one set of layout arrays per (matrix, layout), shared by the dims that use it

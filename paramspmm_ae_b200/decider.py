@@ -35,30 +35,58 @@ def dynamic_CF_prompter(dim, CF_set=None, warp_size=32):
     return [cf for cf in CF_set if gap_calculator(dim, cf, warp_size) < 32]
 
 
-def row_stats(rowPtr):
-    """nnz-per-row summary of a CSR row pointer (torch tensor or numpy array, any device)."""
-    import torch
+NEAR_DIAGONAL = 256  # |column - row| up to which an entry counts as local
 
+
+def near_diagonal_share(rowPtr, colIdx, reach=NEAR_DIAGONAL):
+    """Share of the entries whose column lies within `reach` of their row: close to 1 for banded and
+    locality-ordered matrices, whose rows of the dense operand are re-read out of L1 by neighbouring
+    rows, close to 0 for scattered columns, whose gathers go to L2 and DRAM.  (The reference's
+    statistics carry the same information as max_bw / avg_bw, graph_input.py:392-410.)"""
+    rp = torch.as_tensor(rowPtr).long()
+    ci = torch.as_tensor(colIdx).long()
+    n = rp.numel() - 1
+    if n <= 0 or ci.numel() == 0:
+        return 0.0
+    rows = torch.repeat_interleave(torch.arange(n, device=rp.device), rp[1:] - rp[:-1])
+    return float(((ci - rows).abs() <= reach).double().mean())
+
+
+def row_stats(rowPtr, colIdx=None):
+    """nnz-per-row summary of a CSR row pointer (torch tensor or numpy array, any device); with the
+    column indices also `near_diag`, the share of entries close to the diagonal."""
     rp = torch.as_tensor(rowPtr).long()
     ln = (rp[1:] - rp[:-1]).double()
     n = ln.numel()
     if n == 0:
-        return {"n_rows": 0, "nnz": 0, "avg": 0.0, "cov": 0.0, "max": 0, "real_avg": 0.0}
+        return {"n_rows": 0, "nnz": 0, "avg": 0.0, "cov": 0.0, "max": 0, "real_avg": 0.0, "near_diag": 0.0}
     nnz = int(rp[-1] - rp[0])
     avg = nnz / n
     nonempty = int((ln > 0).sum())
     std = float(ln.std(unbiased=True)) if n > 1 else 0.0
     real_avg = nnz / nonempty if nonempty and nonempty / n < 0.98 else avg
     return {"n_rows": n, "nnz": nnz, "avg": avg, "cov": std / avg if avg else 0.0,
-            "max": int(ln.max()), "real_avg": real_avg}
+            "max": int(ln.max()), "real_avg": real_avg,
+            "near_diag": near_diagonal_share(rp, colIdx) if colIdx is not None else 0.0}
+
+
+SIZES = ("tiny", "short", "medium", "long")
+KINDS = ("even", "local", "skewed")
 
 
 def regime(stats):
-    """Bucket of the nnz-per-row distribution: mean length class x skew class."""
+    """Bucket of the matrix: mean row length class x {skewed, local, even}.  Skewed = row lengths
+    vary strongly (hub rows: they need the row split); local = even lengths with nearly all columns
+    next to the diagonal (L1-bound gathers); even = the rest (scattered columns, L2 / DRAM bound)."""
     avg = stats["avg"]
-    size = "short" if avg < 24 else ("medium" if avg < 128 else "long")
-    skew = "skewed" if (stats["cov"] > 0.75 or stats["max"] > 16 * max(avg, 1.0)) else "even"
-    return size + "_" + skew
+    size = "tiny" if avg < 6 else ("short" if avg < 24 else ("medium" if avg < 128 else "long"))
+    if stats["cov"] > 0.75 or stats["max"] > 16 * max(avg, 1.0):
+        kind = "skewed"
+    elif stats.get("near_diag", 0.0) >= 0.9:
+        kind = "local"
+    else:
+        kind = "even"
+    return size + "_" + kind
 
 
 def auto_granularity(real_avg_degree):
@@ -109,12 +137,17 @@ def choose(stats, dim, op="spmm"):
     per_regime = table().get("entries", {}).get(op, {})
     ent = per_regime.get(reg, {})
     if not ent:
-        # A regime the sweep has not measured borrows from the nearest measured one of the same
-        # skew class (kernel shape depends on the dim first, the row-length class second).
-        size, skew = reg.split("_")
-        order = {"short": ("medium", "long"), "medium": ("short", "long"), "long": ("medium", "short")}[size]
-        for other in order:
-            ent = per_regime.get(other + "_" + skew, {})
+        # A regime the sweep has not measured borrows from the nearest measured size of the same kind
+        # (the kernel shape depends on the dim first, the row-length class second); a local matrix
+        # without any local measurement is treated as an even one.
+        size, kind = reg.split("_")
+        i = SIZES.index(size)
+        near = sorted((s for s in SIZES if s != size), key=lambda s: abs(SIZES.index(s) - i))
+        for k in ([kind] if kind != "local" else ["local", "even"]):
+            for other in ([size] if k != kind else []) + near:
+                ent = per_regime.get(other + "_" + k, {})
+                if ent:
+                    break
             if ent:
                 break
     e = ent.get(_dim_key(dim)) or ent.get("*")
@@ -206,8 +239,10 @@ class SpMMDecider(object):
         return if_split, vec_size, CF, W
 
     def plan(self, graph, dim):
-        stats = row_stats(graph.csr_data.rowPtr)
-        return choose(stats, dim)
+        key = id(graph)
+        if getattr(self, "_stats_of", None) != key:  # the statistics of a graph are computed once, not per dim
+            self._stats, self._stats_of = row_stats(graph.csr_data.rowPtr, graph.csr_data.colIdx), key
+        return choose(self._stats, dim)
 
     def config_PCSR(self, graph, dim):
         if dim not in self.model_dict:
@@ -223,7 +258,7 @@ def install_tuner():
     from . import ops
 
     def tuner(op, dim, mean_len, V, split):
-        size = "short" if mean_len < 24 else ("medium" if mean_len < 128 else "long")
+        size = "tiny" if mean_len < 6 else ("short" if mean_len < 24 else ("medium" if mean_len < 128 else "long"))
         ent = table().get("entries", {}).get(op, {})
         e = (ent.get(size + "_even", {}) or {}).get(_dim_key(dim)) or {}
         return {k: int(e.get(k, 0) or 0) for k in ("lanes_per_row", "vec_width", "cta_threads", "rows_per_group",

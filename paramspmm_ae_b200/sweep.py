@@ -32,33 +32,43 @@ import torch
 
 from . import _lib, decider, ops, synth
 
-ALL_REGIMES = ["short_even", "short_skewed", "medium_even", "medium_skewed", "long_even", "long_skewed"]
+ALL_REGIMES = ["tiny_even", "tiny_skewed", "short_even", "short_local", "short_skewed", "medium_even", "medium_local",
+               "medium_skewed", "long_even", "long_skewed"]
 
 
 def fitting_matrices(n, device, which):
-    """Matrices the table is fitted on.  Seeds and sizes differ from the benchmark's matrices
-    (bench.py: seeds 21-23 at 10^6 rows) and from the hold-out set below."""
+    """Matrices the table is fitted on, per regime.  Seeds and sizes differ from the benchmark's
+    matrices (bench.py: seeds 21-23 at 10^6 rows) and from the hold-out set below."""
+    scale = max(1, (n - 1).bit_length())
+    makers = {
+        "tiny_even": lambda: [("uniform4", synth.uniform_rows(n, 4, seed=127, device=device))],
+        "tiny_skewed": lambda: [("rmat4", synth.rmat(scale, 4 * n, n=n, seed=128, device=device))],
+        "short_even": lambda: [("uniform16", synth.uniform_rows(n, 16, seed=121, device=device))],
+        "short_local": lambda: [("banded16", synth.banded_rows(n, 16, 32, seed=122, device=device)),
+                                ("banded12_bw100", synth.banded_rows(n, 12, 100, seed=130, device=device))],
+        "short_skewed": lambda: [("rmat16", synth.rmat(scale, 16 * n, n=n, seed=123, device=device)),
+                                 ("powerlaw12", synth.powerlaw_graph(n // 2, (n // 2) * 6, seed=124, device=device))],
+        "medium_even": lambda: [("uniform64", synth.uniform_rows(n // 4, 64, seed=125, device=device))],
+        "medium_local": lambda: [("banded64_bw96", synth.banded_rows(n // 4, 64, 96, seed=129, device=device))],
+        "medium_skewed": lambda: [("powerlaw50", synth.powerlaw_graph(n // 4, (n // 4) * 25, seed=131, device=device)),
+                                  ("rmat40", synth.rmat(max(1, scale - 2), 10 * n, seed=132, device=device))],
+        "long_even": lambda: [("uniform256", synth.uniform_rows(n // 16, 256, seed=126, device=device))],
+        "long_skewed": lambda: [("powerlaw490", synth.powerlaw_graph(232965 if n >= 1_000_000 else n // 8,
+                                                                     (232965 if n >= 1_000_000 else n // 8) * 245,
+                                                                     seed=141, device=device))],
+    }
     out = {}
-    if "short_even" in which:
-        out["short_even"] = [("uniform16", synth.uniform_rows(n, 16, seed=121, device=device)),
-                             ("banded16", synth.banded_rows(n, 16, 32, seed=122, device=device))]
-    if "short_skewed" in which:
-        out["short_skewed"] = [("rmat16", synth.rmat(max(1, (n - 1).bit_length()), 16 * n, n=n, seed=123, device=device)),
-                               ("powerlaw12", synth.powerlaw_graph(n // 2, (n // 2) * 6, seed=124, device=device))]
-    if "medium_even" in which:
-        out["medium_even"] = [("uniform64", synth.uniform_rows(n // 4, 64, seed=125, device=device))]
-    if "medium_skewed" in which:
-        out["medium_skewed"] = [("powerlaw50", synth.powerlaw_graph(n // 4, (n // 4) * 25, seed=131, device=device))]
-    if "long_even" in which:
-        out["long_even"] = [("uniform256", synth.uniform_rows(n // 16, 256, seed=126, device=device))]
-    if "long_skewed" in which:
-        k = 232965 if n >= 1_000_000 else n // 8
-        out["long_skewed"] = [("powerlaw490", synth.powerlaw_graph(k, k * 245, seed=141, device=device))]
+    for r in which:
+        for name, m in makers[r]():  # a matrix is fitted for the regime the decider puts it in
+            got = decider.regime(decider.row_stats(m.rowPtr, m.colIdx))
+            if got != r:
+                print("note: fitting matrix %s falls into %s, not %s" % (name, got, r), flush=True)
+            out.setdefault(got, []).append((name, m))
     return out
 
 
 def holdout_matrices(device, scale=1.0):
-    """Fourteen matrices no fit ever sees: other sizes, mean degrees 4..600, R-MAT and Chung-Lu
+    """Eighteen matrices no fit ever sees: other sizes, mean degrees 4..600, R-MAT and Chung-Lu
     exponents, narrow and wide bands, all six regimes."""
     s = lambda x: max(2048, int(x * scale))
     return [
@@ -76,6 +86,10 @@ def holdout_matrices(device, scale=1.0):
         ("chunglu_g3.0_deg11", synth.powerlaw_graph(s(600_000), s(3_000_000), gamma=3.0, seed=212, device=device)),
         ("chunglu_g2.5_deg61", synth.powerlaw_graph(s(150_000), s(4_500_000), gamma=2.5, seed=213, device=device)),
         ("chunglu_g2.1_deg600", synth.powerlaw_graph(s(50_000), s(15_000_000), gamma=2.1, seed=214, device=device)),
+        ("uniform_k24", synth.uniform_rows(s(400_000), 24, seed=215, device=device)),
+        ("banded_k6_bw20", synth.banded_rows(s(900_000), 6, 20, seed=216, device=device)),
+        ("rmat_deg5", synth.rmat(20, s(5_000_000), seed=217, device=device)),
+        ("rmat_skew_deg30", synth.rmat(19, s(15_000_000), a=0.65, b=0.15, c=0.15, seed=218, device=device)),
     ]
 
 
@@ -90,6 +104,8 @@ def candidates(dim, regime, quick=False, vecs=(1, 2), cta_threads=(64, 128, 256)
     mlps = (4, 8) if quick else (4, 8, 16)
     skew = regime.endswith("skewed")
     long_rows = regime.startswith("long") or regime.startswith("medium")
+    if regime.startswith("tiny"):
+        rpgs = (4, 8) if quick else (2, 4, 8, 16)  # very short rows: more of them per lane group
     if skew or long_rows:
         grans = [0, 32, 64, 128] if not long_rows else [0, 64, 128, 256, 512]
     else:
@@ -245,7 +261,7 @@ def holdout(args):
     rows_out = []
     t0 = time.time()
     for name, m in holdout_matrices(dev, args.scale):
-        st = decider.row_stats(m.rowPtr)
+        st = decider.row_stats(m.rowPtr, m.colIdx)
         reg = decider.regime(st)
         lay = Layouts(m, dev)
         for dim in args.dims:

@@ -81,7 +81,7 @@ def test_full_size_spmm_equals_reference_cuda(ref_spmm, mats, name, dim):
     # this library: the legacy entry points, and the configuration the decider picks (what bench.py times)
     _assert_rows_close(ops.csr_spmm(X, m.rowPtr, m.colIdx, m.val, CF, 8), theirs, row_len, "csr_spmm")
     _assert_rows_close(ops.csr_split_spmm(X, rps, m.colIdx, m.val, tr, CF, 8), theirs, row_len, "csr_split_spmm")
-    plan = decider.choose(decider.row_stats(m.rowPtr), dim)
+    plan = decider.choose(decider.row_stats(m.rowPtr, m.colIdx), dim)
     op = decider.PlannedSpMM(plan, m.rowPtr, m.colIdx, m.val)
     C = torch.full((N, dim), float("nan"), device=dev)
     run = lambda: op(C, X)
