@@ -212,13 +212,42 @@ def test_table_plans_become_valid_kernel_configurations():
             plan = decider.Plan(if_split=0, vec_size=1, granularity=None)
             plan.update(e)
             cfg = _lib.make_cfg(**plan.kernel_cfg())
-            assert cfg.col_tile in (0, 128)
+            assert cfg.col_tile in (0, 32, 64, 128) and cfg.bucketed in (0, 1)
             dim = int(dim_key)
             rc = lib.pspmm_resolve_cfg(ctypes.byref(cfg), dim, dim, dim, 1, ctypes.c_void_p(256), ctypes.c_void_p(256))
             assert rc == _lib.PSPMM_OK, (regime, dim_key, e)
             assert cfg.lanes_per_row in (2, 4, 8, 16, 32) and cfg.cta_threads in (32, 64, 128, 256)
             seen += 1
     assert seen >= 64
+
+
+def test_table_measures_every_regime_and_the_decider_reaches_them():
+    """The committed table holds a measured entry for every regime the fit covers and for every
+    dim key; the regime rule sends the generators' matrices where the fit put them; a regime
+    without measurements borrows from its nearest measured neighbour."""
+    import torch
+    from paramspmm_ae_b200 import decider, sweep, synth
+    tab = decider.load_table()
+    regimes = tab["entries"]["spmm"]
+    for r in sweep.ALL_REGIMES:
+        assert r in regimes, r
+        assert set(regimes[r]) == {str(d) for d in range(16, 257, 16)}, r
+    cases = [(synth.uniform_rows(4000, 4, seed=1), "tiny_even"), (synth.uniform_rows(4000, 16, seed=1), "short_even"),
+             (synth.banded_rows(4000, 16, 32, seed=1), "short_local"), (synth.uniform_rows(3000, 64, seed=1), "medium_even"),
+             (synth.banded_rows(3000, 64, 96, seed=1), "medium_local"), (synth.rmat(12, 4 * 4096, seed=1), "tiny_skewed"),
+             (synth.rmat(12, 16 * 4096, seed=1), "short_skewed"), (synth.powerlaw_graph(3000, 75000, seed=1), "medium_skewed")]
+    for m, want in cases:
+        st = decider.row_stats(m.rowPtr, m.colIdx)
+        assert decider.regime(st) == want, (want, st)
+        for dim in (16, 100, 256, 300):
+            p = decider.choose(st, dim)
+            assert p["regime"] == want and p["vec_size"] in (1, 2)
+            assert (p["granularity"] is not None) == bool(p["if_split"])
+    # without column indices a banded matrix is an even one; long_local borrows (no fit matrix for it)
+    b = synth.banded_rows(4000, 16, 32, seed=1)
+    assert decider.regime(decider.row_stats(b.rowPtr)) == "short_even"
+    st = {"n_rows": 10, "nnz": 3000, "avg": 300.0, "cov": 0.1, "max": 310, "real_avg": 300.0, "near_diag": 1.0}
+    assert decider.regime(st) == "long_local" and decider.choose(st, 64)["regime"] == "long_local"
 
 
 def test_header_is_plain_c_and_declares_what_the_python_shim_binds(tmp_path):
