@@ -392,7 +392,7 @@ def main():
             from paramspmm_ae_b200 import baselines
             gather = []
             for key in sorted({("rmat", 128), (sweep[top]["matrix"], sweep[top]["dim"])}):
-                if key not in cases or key[1] not in (16, 32, 64, 128, 256):
+                if key not in cases or key[1] % 4 != 0:
                     continue
                 m, ms = mats[key[0]], mean_ms[cases.index(key)]
                 flush.zero_()

@@ -197,7 +197,7 @@ def gespmm_profile(X, rowPtr, colIdx, val):
 def gather_ceiling_ms(colIdx, B, run=64, warmup=3, iters=10):
     """Milliseconds the GPU needs just to fetch B[colIdx[k]] for every k (8 row loads in flight per
     lane, nothing else): the floor of any row-major-gather SpMM over this column stream and dense
-    operand (see csrc/baselines.cu).  dim must be 16, 32, 64, 128 or 256."""
+    operand (see csrc/baselines.cu).  dim must be a multiple of 4."""
     _check_cuda(colIdx, "colIdx", torch.int32, 1)
     _check_cuda(B, "B", torch.float32, 2)
     nnz, dim = colIdx.shape[0], B.shape[1]

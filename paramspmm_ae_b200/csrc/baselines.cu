@@ -232,11 +232,13 @@ PB_API int pspmm_baselines_gespmm(const int32_t *rowPtr, const int32_t *colIdx, 
 template <int LPR>
 __global__ void __launch_bounds__(256) gather_ceiling_kernel(const int32_t *__restrict__ colIdx, int64_t nnz,
                                                              const float *__restrict__ B, int64_t ldB,
-                                                             int run, float4 *__restrict__ sink)
+                                                             int run, int active, float4 *__restrict__ sink)
 {
     const int gl = threadIdx.x % LPR;
     const int64_t group = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) / LPR;
     const int64_t k0 = group * run;
+    if (gl >= active || k0 >= nnz)
+        return;  // lanes beyond the last 16-byte slice of a row, groups beyond the stream
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     const float *base = B + gl * 4;
     int64_t k = k0;
@@ -259,16 +261,25 @@ __global__ void __launch_bounds__(256) gather_ceiling_kernel(const int32_t *__re
         const float4 x = __ldg(reinterpret_cast<const float4 *>(base + (int64_t)__ldg(colIdx + k) * ldB));
         acc.x += x.x; acc.y += x.y; acc.z += x.z; acc.w += x.w;
     }
-    if (k0 < nnz)
-        sink[(int64_t)blockIdx.x * blockDim.x + threadIdx.x] = acc;
+    sink[(int64_t)blockIdx.x * blockDim.x + threadIdx.x] = acc;
 }
 
-// dim: a multiple of 4 with dim/4 in {4, 8, 16, 32, 64} (64: two passes of 32 lanes over the two
-// halves of a row).  run: entries per lane group (a multiple of 8, e.g. 64).  sink: device buffer of
-// pspmm_baselines_gather_sink_bytes(nnz, dim, run) bytes.  colIdx must be 16-byte aligned.
+// dim: a multiple of 4.  Rows wider than 128 floats are fetched in passes of 32 lanes over
+// successive 512-byte parts (the time of all passes counts).  run: entries per lane group (a
+// multiple of 8, e.g. 64).  sink: device buffer of pspmm_baselines_gather_sink_bytes(nnz, dim, run)
+// bytes.  colIdx must be 16-byte aligned.
+static int gather_lanes(int32_t dim)
+{
+    const int nvec = dim / 4;
+    int lpr = 4;
+    while (lpr < nvec && lpr < 32)
+        lpr <<= 1;
+    return lpr;
+}
+
 PB_API int64_t pspmm_baselines_gather_sink_bytes(int64_t nnz, int32_t dim, int32_t run)
 {
-    const int lpr = dim / 4 > 32 ? 32 : dim / 4;
+    const int lpr = gather_lanes(dim);
     const int64_t groups = (nnz + run - 1) / run;
     const int64_t threads = (groups * lpr + 255) / 256 * 256;
     return threads * 16;
@@ -277,26 +288,25 @@ PB_API int64_t pspmm_baselines_gather_sink_bytes(int64_t nnz, int32_t dim, int32
 PB_API int pspmm_baselines_gather_ceiling(const int32_t *colIdx, int64_t nnz, const float *B, int32_t dim,
                                           int64_t ldB, int32_t run, void *sink, void *stream)
 {
-    if (!colIdx || !B || !sink || nnz <= 0 || dim % 4 != 0 || run <= 0 || run % 8 != 0 ||
+    if (!colIdx || !B || !sink || nnz <= 0 || dim <= 0 || dim % 4 != 0 || run <= 0 || run % 8 != 0 ||
         ((uintptr_t)colIdx) % 16 != 0 || ((uintptr_t)B) % 16 != 0 || ldB % 4 != 0)
         return -1;
     const int nvec = dim / 4;
-    if (nvec != 4 && nvec != 8 && nvec != 16 && nvec != 32 && nvec != 64)
-        return -1;
     cudaStream_t st = (cudaStream_t)stream;
-    const int lpr = nvec > 32 ? 32 : nvec;
+    const int lpr = gather_lanes(dim);
     const int64_t groups = (nnz + run - 1) / run;
     const unsigned grid = (unsigned)((groups * lpr + 255) / 256);
-    for (int half = 0; half < (nvec > 32 ? 2 : 1); ++half) {
-        const float *b = B + half * 128;
+    for (int v0 = 0; v0 < nvec; v0 += lpr) {
+        const float *b = B + (int64_t)v0 * 4;
+        const int active = nvec - v0 < lpr ? nvec - v0 : lpr;
         if (lpr == 4)
-            gather_ceiling_kernel<4><<<grid, 256, 0, st>>>(colIdx, nnz, b, ldB, run, (float4 *)sink);
+            gather_ceiling_kernel<4><<<grid, 256, 0, st>>>(colIdx, nnz, b, ldB, run, active, (float4 *)sink);
         else if (lpr == 8)
-            gather_ceiling_kernel<8><<<grid, 256, 0, st>>>(colIdx, nnz, b, ldB, run, (float4 *)sink);
+            gather_ceiling_kernel<8><<<grid, 256, 0, st>>>(colIdx, nnz, b, ldB, run, active, (float4 *)sink);
         else if (lpr == 16)
-            gather_ceiling_kernel<16><<<grid, 256, 0, st>>>(colIdx, nnz, b, ldB, run, (float4 *)sink);
+            gather_ceiling_kernel<16><<<grid, 256, 0, st>>>(colIdx, nnz, b, ldB, run, active, (float4 *)sink);
         else
-            gather_ceiling_kernel<32><<<grid, 256, 0, st>>>(colIdx, nnz, b, ldB, run, (float4 *)sink);
+            gather_ceiling_kernel<32><<<grid, 256, 0, st>>>(colIdx, nnz, b, ldB, run, active, (float4 *)sink);
     }
     PB_CUDA(cudaGetLastError());
     return 0;

@@ -488,7 +488,10 @@ def scaleout_brief(scale=24, nnz=512_000_000, dim=128, seed=51, iters=5, warmup=
         recv = sh_pull._receive_buffer(max(1, sh_pull.n_needed), dim, B_shard)
         rot = first[(rank + 1) % world] % max(1, sh_pull.n_needed)
         res["fetch_alone_ms"] = timed(lambda: ops.pull_rows(recv, peers, first, want_rows, rotate=rot, ctas=sh_pull.pull_ctas))
+        for c in (32, 128, 256):
+            res["fetch_alone_%d_ctas_ms" % c] = timed(lambda: ops.pull_rows(recv, peers, first, want_rows, rotate=rot, ctas=c))
         res["fetch_alone_all_sms_ms"] = timed(lambda: ops.pull_rows(recv, peers, first, want_rows, rotate=rot, ctas=1184))
+        res["pull_ctas"] = sh_pull.pull_ctas
         res["fetched_bytes"] = int(sh_pull.n_needed) * dim * 4
         res["spmm_on_fetched_rows_ms"] = timed(lambda: sh_pull.local_spmm(out, recv, sh_pull.rowPtr, sh_pull.colIdx, sh_pull.val))
     res.update(notes)
