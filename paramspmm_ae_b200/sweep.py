@@ -113,6 +113,9 @@ def candidates(dim, regime, quick=False, vecs=(1, 2), cta_threads=(64, 128, 256)
     if quick:
         vecs, cta_threads = (1,), (256,)
     tiles = [0] + [t for t in (32, 64, 128) if t < dim and dim % 4 == 0]
+    if dim >= 96 and dim % 4 == 0 and not skew:
+        # equal parts: a width that is not a multiple of 64 would otherwise end in a narrow remainder launch
+        tiles += [t for t in sorted({(-(-dim // parts) + 3) // 4 * 4 for parts in (2, 3, 4)}) if t not in tiles and 32 <= t < dim]
     for vec, gran, lpr, rpg, mlp, thr, tile in itertools.product(vecs, grans, lprs, rpgs, mlps, cta_threads, tiles):
         if vec != 1 and (mlp != 8 or thr != 256 or tile):
             continue  # block kernels are built with one gather depth; measured at one CTA size, untiled
