@@ -85,7 +85,7 @@ PSPMM_API int pspmm_resolve_cfg(pspmm_cfg *cfg, int32_t dim, int64_t ldB, int64_
  * Stands in for csr_spmm (SpMM/SpMM.cpp:77-141 -> SpMM_kernel.cu:129-197, 1157-1243) when
  * rowPtr_split/target_row are NULL, and for csr_split_spmm (SpMM.cpp:143-207 ->
  * SpMM_kernel.cu:199-272, 1245-1360) when they are given; in the split form `rowPtr` may be
- * NULL.  target_row must be non-decreasing (what split_csr produces).  Unlike the reference
+ * NULL.  val may be NULL: every stored entry then counts as 1 (the product with the pattern itself).  target_row must be non-decreasing (what split_csr produces).  Unlike the reference
  * the output may have a different row count from B (row shards) and C needs no prior zeroing:
  * rows without entries are written as zeros.  Rows cut into several pieces are accumulated
  * with vector atomics, so their summation order is not fixed.

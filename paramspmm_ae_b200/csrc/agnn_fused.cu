@@ -392,9 +392,10 @@ extern "C" int pspmm_agnn_fused_apply_csr(const int32_t *rowPtr, const int32_t *
     // entries per batch (BS).  Few lanes per row put more entries into every warp instruction (the
     // 128-bit form at 16 lanes is bound by instruction issue); wide loads keep the L1 wavefronts
     // full (the 128-bit form at 4 lanes is bound by the L1 data pipe).  Defaults = measured best.
-    // (a separate aggregation operand doubles the gathered registers: built with 128-bit loads, batches of 4)
-    const bool can8 = !sep && dim % 8 == 0 && dim >= 32 && ldA % 8 == 0 && ldB % 8 == 0 &&
-                      ((uintptr_t)A) % 32 == 0 && ((uintptr_t)B) % 32 == 0;
+    // (a separate aggregation operand doubles the gathered registers: batches of 4, and with 256-bit
+    // loads one slice per lane)
+    const bool can8 = dim % 8 == 0 && dim >= 32 && ldA % 8 == 0 && ldB % 8 == 0 && ((uintptr_t)A) % 32 == 0 &&
+                      ((uintptr_t)B) % 32 == 0 && (!sep || (ldV % 8 == 0 && ((uintptr_t)V) % 32 == 0));
     if (sep)
         batch = 4;
     if (vec_width != 0 && vec_width != 4 && vec_width != 8)
@@ -410,8 +411,8 @@ extern "C" int pspmm_agnn_fused_apply_csr(const int32_t *rowPtr, const int32_t *
         lpr *= 2;
         cf = (nvec + lpr - 1) / lpr;
     }
-    if (sep && lanes_per_row == 0) {  // two gathered rows per entry: at most two slices per lane keeps them in registers
-        while (cf > 2 && lpr < 32) {
+    if (sep && lanes_per_row == 0) {  // two gathered rows per entry: at most two slices per lane (one of 32 bytes) keeps them in registers
+        while (cf > (vw == 8 ? 1 : 2) && lpr < 32) {
             lpr *= 2;
             cf = (nvec + lpr - 1) / lpr;
         }
@@ -428,14 +429,16 @@ extern "C" int pspmm_agnn_fused_apply_csr(const int32_t *rowPtr, const int32_t *
     if (cf * vw >= 8 && bs > 8)
         bs = 8;
     bool ok = false;
-#define AGNN_CASE_SEP(LPR_, CF_)                                    \
-    if (!ok && sep && vw == 4 && lpr == LPR_ && cf == CF_ && bs == 4) { \
-        launch_fused<LPR_, CF_, 4, 4, true>(a, st);                 \
-        ok = true;                                                  \
+#define AGNN_CASE_SEP(LPR_, CF_, VW_)                                 \
+    if (!ok && sep && vw == VW_ && lpr == LPR_ && cf == CF_ && bs == 4) { \
+        launch_fused<LPR_, CF_, 4, VW_, true>(a, st);                 \
+        ok = true;                                                    \
     }
-    AGNN_CASE_SEP(4, 1) AGNN_CASE_SEP(4, 2) AGNN_CASE_SEP(4, 4) AGNN_CASE_SEP(8, 1) AGNN_CASE_SEP(8, 2)
-    AGNN_CASE_SEP(8, 4) AGNN_CASE_SEP(16, 1) AGNN_CASE_SEP(16, 2) AGNN_CASE_SEP(16, 4) AGNN_CASE_SEP(32, 1)
-    AGNN_CASE_SEP(32, 2)
+    AGNN_CASE_SEP(4, 1, 4) AGNN_CASE_SEP(4, 2, 4) AGNN_CASE_SEP(4, 4, 4) AGNN_CASE_SEP(8, 1, 4) AGNN_CASE_SEP(8, 2, 4)
+    AGNN_CASE_SEP(8, 4, 4) AGNN_CASE_SEP(16, 1, 4) AGNN_CASE_SEP(16, 2, 4) AGNN_CASE_SEP(16, 4, 4)
+    AGNN_CASE_SEP(32, 1, 4) AGNN_CASE_SEP(32, 2, 4)
+    AGNN_CASE_SEP(4, 1, 8) AGNN_CASE_SEP(8, 1, 8) AGNN_CASE_SEP(16, 1, 8) AGNN_CASE_SEP(32, 1, 8)
+    AGNN_CASE_SEP(4, 2, 8) AGNN_CASE_SEP(8, 2, 8) AGNN_CASE_SEP(16, 2, 8)
 #undef AGNN_CASE_SEP
     if (sep && !ok)
         return PSPMM_E_UNSUPPORTED;

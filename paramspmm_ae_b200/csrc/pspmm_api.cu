@@ -418,8 +418,8 @@ extern "C" int pspmm_spmm_csr(const int32_t *rowPtr, const int32_t *colIdx, cons
         return PSPMM_E_ARG;
     if (!B || !C || ldB < dim || ldC < dim)
         return PSPMM_E_ARG;
-    if (nnz > 0 && (!colIdx || !val))
-        return PSPMM_E_ARG;
+    if (nnz > 0 && !colIdx)
+        return PSPMM_E_ARG;  // (val may be NULL: the pattern with unit values)
     if (split && n_seg >= INT32_MAX)
         return PSPMM_E_RANGE;
     return spmm_launch(split ? rowPtr_split : rowPtr, target_row, split ? n_seg : n_rows, colIdx,

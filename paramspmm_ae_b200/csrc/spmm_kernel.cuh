@@ -170,8 +170,10 @@ __global__ void __launch_bounds__(256, SpmmOcc<MLP>::MIN_CTAS) spmm_seg_kernel(c
         for (int i = gl; i < fill; i += LPR) {
             const int k = cur + i;
             if constexpr (V == 1) {
+                // (no value array: the pattern itself, every stored entry counts as 1)
                 *reinterpret_cast<int2 *>(ent + 2 * i) =
-                    make_int2(ldg_stream_b32(a.colIdx + k, stream), ldg_stream_b32(a.val + k, stream));
+                    make_int2(ldg_stream_b32(a.colIdx + k, stream),
+                              a.val ? ldg_stream_b32(a.val + k, stream) : __float_as_int(1.f));
             } else {
                 ent[(1 + V) * i] = ldg_stream_b32(a.colIdx + k, stream);
 #pragma unroll

@@ -91,6 +91,7 @@ FUSE_AGNN_INFERENCE = True
 # gnn_conv.py:130-180).  Outputs and gradients are the reference's up to fp32 summation order.
 # Set to False to train through the three-kernel composition (AGNNFunction).
 FUSE_AGNN_TRAINING = True
+FUSED_APPLY_VEC_WIDTH = 0  # floats per lane per load in the backward pass: 0 = the library's choice, 4 or 8
 
 
 def _can_fuse(P, dim):
@@ -143,8 +144,8 @@ class AGNNFusedFunction(torch.autograd.Function):
               dX = D W^T,  dW = X^T D                                      (gnn_conv.py:157-160)
               d_beta = sum over edges of <G_i, G_j> * colIdx[e]              (gnn_conv.py:163-172: the
               reference multiplies the score gradient by the column-index column it is handed); here
-              as row sums of the scores <G_i, H_j>, H_j = colIdx-weight_j * G_j, from a third fused pass
-              whose aggregation operand is one shared row of ones.
+              as sum_i <G_i, T_i> with T = P H, H_j = j * G_j, P the pattern with unit values: one
+              SpMM without a value array and a dot product.
     Like the reference's backward, the edge values are treated as constants with respect to X'."""
 
     @staticmethod
@@ -172,7 +173,7 @@ class AGNNFusedFunction(torch.autograd.Function):
 
         def apply(A, B, V, b):
             o = ops.agnn_fused(A, B, P.rowPtr, P.colIdx, b, softmax=False, target_row=P.target_row,
-                               n_out_rows=n_out, V=V)
+                               n_out_rows=n_out, V=V, vec_width=FUSED_APPLY_VEC_WIDTH)
             if o.shape[0] != G.shape[0]:
                 o = torch.cat([o, o.new_zeros(G.shape[0] - o.shape[0], o.shape[1])])
             return o
@@ -183,11 +184,13 @@ class AGNNFusedFunction(torch.autograd.Function):
         d_att = None
         if ctx.needs_input_grad[2]:
             # The reference weights every edge's score gradient by the float value of the column-index
-            # column it is handed, i.e. by the edge's column id j: scale row j of G by j and sum all scores.
+            # column it is handed, i.e. by the edge's column id j: sum_e <G_i, G_j> j = sum_i <G_i, (P H)_i>
+            # with H_j = j G_j and P the pattern with unit values.
             H = G * torch.arange(G.shape[0], device=G.device, dtype=G.dtype)[:, None]
-            ones = torch.ones(1, G.shape[1], device=G.device, dtype=G.dtype)
-            S = apply(G, H, ones, 1.0)  # every column of row i holds sum_j <G_i, H_j>
-            d_att = S[:, 0].double().sum().to(G.dtype).reshape(1, 1)
+            rows = G.shape[0] if split else P.rowPtr.shape[0] - 1
+            T = torch.empty(rows, G.shape[1], device=G.device, dtype=G.dtype)
+            ops.spmm_into(T, H, P.rowPtr, P.colIdx, None, target_row=P.target_row, n_out_rows=rows)
+            d_att = (G[:rows].double() * T.double()).sum().to(G.dtype).reshape(1, 1)
         return d_input, d_weights, d_att, None, None
 
 

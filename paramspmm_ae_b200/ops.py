@@ -283,9 +283,12 @@ def _spmm_inputs(X, rowPtr, colIdx, val, target_row, V):
     _check_cuda(X, "input", torch.float32, 2)
     _check_cuda(rowPtr, "rowPtr", torch.int32, 1)
     _check_cuda(colIdx, "colIdx", torch.int32, 1)
-    _check_cuda(val, "values", torch.float32, 1 if V == 1 else 2)
-    if V > 1 and val.shape[1] != V:
-        raise RuntimeError("values must have %d columns" % V)
+    if val is None and V != 1:
+        raise RuntimeError("block layouts need their value array (it also is their mask)")
+    if val is not None:
+        _check_cuda(val, "values", torch.float32, 1 if V == 1 else 2)
+        if V > 1 and val.shape[1] != V:
+            raise RuntimeError("values must have %d columns" % V)
     if target_row is not None:
         _check_cuda(target_row, "target_row", torch.int32, 1)
         if target_row.shape[0] != rowPtr.shape[0] - 1:
@@ -308,7 +311,8 @@ def spmm_into(out, X, rowPtr, colIdx, val, target_row=None, V=1, n_out_rows=None
     """Launch the SpMM into a caller-provided output (also used by the multi-GPU row shards).
 
     ``n_out_rows`` counts (block-)rows of the output; it defaults to the number of segments
-    when there is no split and must be given for split layouts.
+    when there is no split and must be given for split layouts.  ``val=None`` (CSR layouts)
+    multiplies by the pattern itself: every stored entry counts as 1.
     """
     dim = X.shape[1]
     n_seg = rowPtr.shape[0] - 1

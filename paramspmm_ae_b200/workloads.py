@@ -201,6 +201,16 @@ def agnn_layer(n=232_965, pairs=57_180_000, dim=64, seed=41, iters=10, grans=(0,
     for a_, b_ in zip(steps.pop("three_kernels_grads"), steps.pop("fused_grads")):
         scale = float(a_.abs().max())
         torch.testing.assert_close(b_, a_, rtol=1e-4, atol=1e-5 * max(1.0, scale))
+    # the backward product alone (scores recomputed, gradient rows gathered) at both load widths
+    Xp = torch.mm(X, conv.weights.detach())
+    Dout = torch.empty(n, dim, device=dev)
+    for vw in (4, 8):
+        steps["backward_product_vw%d_ms" % vw] = round(_time_ms(
+            lambda: ops.agnn_fused(Xp, Xp, rps, g.colIdx, beta, False, target_row=tr, n_out_rows=n, out=Dout, V=Gup,
+                                   vec_width=vw), iters=iters), 4)
+    Tout = torch.empty(n, dim, device=dev)
+    steps["pattern_spmm_ms"] = round(_time_ms(lambda: ops.spmm_into(Tout, Gup, rps, g.colIdx, None, target_row=tr,
+                                                                    n_out_rows=n), iters=iters), 4)
     out["layer_training_step"] = dict(steps, granularity=gfast)
     return out
 

@@ -722,6 +722,25 @@ def test_bucketed_plan_spmm_matches_oracle(dev, oracle, mats, name, gran):
     close(out[: m.n_rows], oracle.spmm_csr(rp, ci, v, B.numpy()))
 
 
+def test_spmm_without_values_multiplies_by_the_pattern(dev, oracle, mats):
+    """val = NULL: every stored entry counts as 1 (plain, split and bucketed layouts)."""
+    from paramspmm_ae_b200 import _lib, ops
+    m = mats["powerlaw"]
+    rp, ci, v = m.numpy()
+    d = m.to(dev)
+    for dim in (16, 64, 100):
+        B = dense(m.n_cols, dim, 60 + dim)
+        want = oracle.spmm_csr(rp, ci, np.ones_like(v), B.numpy())
+        out = torch.full((m.n_rows, dim), float("nan"), device=dev)
+        close(ops.spmm_into(out, B.to(dev), d.rowPtr, d.colIdx, None), want)
+        rps, tr = ops.split_csr_device(d.rowPtr, 32)
+        out.fill_(float("nan"))
+        close(ops.spmm_into(out, B.to(dev), rps, d.colIdx, None, target_row=tr, n_out_rows=m.n_rows), want)
+    with pytest.raises(RuntimeError):
+        rpb, cb, vb = ops.bcsr_from_csr(m.rowPtr, m.colIdx, m.val, m.n_cols, 2)
+        ops._spmm_inputs(B.to(dev), rpb.to(dev), cb.to(dev), None, None, 2)
+
+
 def test_planned_spmm_runs_every_layout(dev, oracle, mats):
     """decider.PlannedSpMM: plain, split and bucketed plans give the same product."""
     from paramspmm_ae_b200 import decider
