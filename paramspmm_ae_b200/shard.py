@@ -112,7 +112,7 @@ class ShardedSpMM:
             raise ValueError("the copy-engine transport moves whole row chunks: use exchange='pipelined'")
         if transport == "pull" and exchange not in ("needed", "needed_pipelined"):
             raise ValueError("the pull transport fetches referenced rows: use exchange='needed' or 'needed_pipelined'")
-        self.pull_ctas = 64
+        self.pull_ctas = 128  # thread blocks of one fetch: enough loads in flight to fill NVLink (measured), few enough to leave the SMs to the SpMM
         self.transport, self._peer = transport, None
         self.rank, self.world, self.group, self.dim_chunks = rank, world, group, dim_chunks
         self.exchange, self.row_chunks = exchange, row_chunks
@@ -144,7 +144,11 @@ class ShardedSpMM:
         else:
             self.local_spmm = local_spmm if local_spmm is not None else self._planned_spmm()
         overlap = dim_chunks > 1 or exchange in ("pipelined", "needed_pipelined") or transport == "pull"
-        self._side = torch.cuda.Stream() if (self.device.type == "cuda" and overlap) else None
+        # The fetch kernels of the pull transport run beside SpMM launches that fill the GPU on their
+        # own: a high-priority stream lets their few thread blocks take SM slots as the SpMM's blocks
+        # retire instead of queueing behind the whole grid.
+        self._side = (torch.cuda.Stream(priority=-1 if transport == "pull" else 0)
+                      if (self.device.type == "cuda" and overlap) else None)
         self._pull_streams = ([torch.cuda.Stream() for _ in range(min(3, world - 1))]
                               if (self._side is not None and transport == "copy_engine") else [])
 
