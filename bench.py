@@ -544,8 +544,7 @@ def main():
                         "replicated_gflops": gf(r["replicated_ms"]), "allgather_gflops": gf(r["allgather_ms"]),
                         "exchange_gflops": gf(r["exchange_ms"]),
                         "exchange_form": "rows referenced by the shard only, fetched from the owners' peer-mapped blocks "
-                                         "by the pull kernel in %d chunks, products overlapped (transport %s)"
-                                         % (r["row_chunks"], r["transport"]),
+                                         "by the pull kernel: %s (transport %s)" % (r["exchange_form"], r["transport"]),
                         "detail": r}
         except Exception as e:  # the headline number must not depend on this leg
             scaleout = {"unavailable": "%s: %s" % (type(e).__name__, e)}

@@ -51,6 +51,14 @@ rank starting at a different owner), straight into its compact operand.  With
 The kernel waits on nothing; a one-element all-reduce before the fetches (every block is in place)
 and one after them (every peer has finished reading) order it against the producers.
 
+``exchange="needed_rowgroups"`` (pull transport) pipelines without cutting A by columns: the
+shard's rows are cut into ``row_chunks`` contiguous groups of about equal entry counts, the rows
+of the dense operand are fetched in the order in which the groups first need them (fetch k brings
+what group k references and no earlier group did, hub columns therefore in fetch 0), and the
+product of row group k, a plain overwrite of its own rows of C at full row length, starts when
+fetches 0..k have arrived, beside fetch k+1.  Every entry of A is read once, no product adds into
+another's output, and the groups are views of the shard's arrays.
+
 ``dim_chunks > 1`` splits the dense columns into slices and gathers slice s+1 on a side
 stream while the SpMM of slice s runs (the kernels take explicit leading dimensions, so a
 slice of C is written in place).
@@ -102,16 +110,20 @@ class ShardedSpMM:
     def __init__(self, rowPtr, colIdx, val, n_cols, rank, world, row_bounds=None, col_bounds=None,
                  device="cuda", group=None, local_spmm=None, dim_chunks=1, exchange="allgather",
                  row_chunks=4, transport="nccl", local_block=None):
-        if exchange not in ("allgather", "needed", "pipelined", "needed_pipelined"):
-            raise ValueError("exchange must be 'allgather', 'needed', 'pipelined' or 'needed_pipelined'")
+        if exchange not in ("allgather", "needed", "pipelined", "needed_pipelined", "needed_rowgroups"):
+            raise ValueError("exchange must be 'allgather', 'needed', 'pipelined', 'needed_pipelined' or "
+                             "'needed_rowgroups'")
         if row_chunks < 1:
             raise ValueError("row_chunks must be at least 1")
         if transport not in ("nccl", "copy_engine", "pull"):
             raise ValueError("transport must be 'nccl', 'copy_engine' or 'pull'")
         if transport == "copy_engine" and exchange != "pipelined":
             raise ValueError("the copy-engine transport moves whole row chunks: use exchange='pipelined'")
-        if transport == "pull" and exchange not in ("needed", "needed_pipelined"):
-            raise ValueError("the pull transport fetches referenced rows: use exchange='needed' or 'needed_pipelined'")
+        if transport == "pull" and exchange not in ("needed", "needed_pipelined", "needed_rowgroups"):
+            raise ValueError("the pull transport fetches referenced rows: use exchange='needed', "
+                             "'needed_pipelined' or 'needed_rowgroups'")
+        if exchange == "needed_rowgroups" and transport != "pull":
+            raise ValueError("exchange='needed_rowgroups' is built on the pull transport")
         self.pull_ctas = 128  # thread blocks of one fetch: enough loads in flight to fill NVLink (measured), few enough to leave the SMs to the SpMM
         self.transport, self._peer = transport, None
         self.rank, self.world, self.group, self.dim_chunks = rank, world, group, dim_chunks
@@ -136,9 +148,11 @@ class ShardedSpMM:
             self._plan_row_chunks(ci.to(device))
         elif exchange == "needed_pipelined":
             self._plan_needed_row_chunks(ci.to(device))
+        elif exchange == "needed_rowgroups":
+            self._plan_needed_row_groups(ci.to(device))
         else:
             self.colIdx = remap_columns(ci.to(device), self.col_bounds, self.max_rows)
-        if exchange in ("pipelined", "needed_pipelined"):
+        if exchange in ("pipelined", "needed_pipelined", "needed_rowgroups"):
             self.block_spmm = [local_spmm if local_spmm is not None else self._planned_spmm(rp_k)
                                for rp_k, _, _ in self.blocks]
         else:
@@ -238,6 +252,49 @@ class ShardedSpMM:
             a += sizes[kk]
         self.n_needed = base
         self.val = self.colIdx = None
+
+    def _plan_needed_row_groups(self, cols_global):
+        """Set-up of the row-group pipeline: contiguous groups of local rows with about equal entry
+        counts; the compact operand is ordered by the group that first references a row (inside a
+        group by column, hence by owner); fetch k = the rows first needed by group k."""
+        dev = cols_global.device
+        K, W, n_loc = self.row_chunks, self.world, self.hi - self.lo
+        rp = self.rowPtr.long()
+        nnz = int(rp[-1])
+        targets = torch.tensor([(nnz * k) // K for k in range(1, K)], dtype=torch.long, device=dev)
+        cuts = torch.searchsorted(rp, targets).clamp_(0, n_loc)
+        bounds = torch.cummax(torch.cat([torch.zeros(1, dtype=torch.long, device=dev), cuts,
+                                         torch.tensor([n_loc], device=dev)]), 0).values
+        self.group_bounds = [int(x) for x in bounds.cpu()]
+        c = cols_global.long()
+        need = torch.unique(c)                      # sorted distinct global column ids
+        inv = torch.searchsorted(need, c)           # entry -> index into need
+        rows = torch.repeat_interleave(torch.arange(n_loc, device=dev), rp[1:] - rp[:-1])
+        grp = torch.searchsorted(bounds[1:].contiguous(), rows, right=True).clamp_(max=K - 1)  # group of every entry's row
+        first = torch.full((need.numel(),), K, dtype=torch.long, device=dev).scatter_reduce(0, inv, grp, "amin")
+        del rows, grp
+        order = torch.argsort(first, stable=True)   # compact order: by first group, then by column
+        pos = torch.empty_like(order)
+        pos[order] = torch.arange(order.numel(), device=dev)
+        self.colIdx = pos[inv].to(torch.int32)
+        del inv, pos
+        cb = self.col_bounds.to(dev)
+        counts = torch.bincount(first, minlength=K)[:K]
+        self.chunk_plan, self.blocks, base = [], [], 0
+        need_o = need[order]
+        for k in range(K):
+            cnt = int(counts[k])
+            ids = need_o[base: base + cnt]          # ascending global column ids of this fetch
+            cuts_k = torch.searchsorted(ids, cb)
+            recv_counts = (cuts_k[1:] - cuts_k[:-1]).cpu()
+            own = torch.repeat_interleave(torch.arange(W, device=dev), recv_counts.to(dev))
+            wanted = (ids - cb[own]).to(torch.int32)
+            self.chunk_plan.append((base, cnt, [int(x) for x in recv_counts], None, wanted))
+            r0, r1 = self.group_bounds[k], self.group_bounds[k + 1]
+            a, b = int(rp[r0]), int(rp[r1])
+            self.blocks.append(((self.rowPtr[r0: r1 + 1] - self.rowPtr[r0]).contiguous(), self.colIdx[a:b], self.val[a:b]))
+            base += cnt
+        self.n_needed = base
 
     def _forward_needed_pipelined(self, B_shard, out):
         import torch.distributed as dist
@@ -348,6 +405,13 @@ class ShardedSpMM:
         if self.exchange == "needed":
             main.wait_event(events[0])
             self.local_spmm(out, recv, self.rowPtr, self.colIdx, self.val)
+        elif self.exchange == "needed_rowgroups":
+            for kk in range(self.row_chunks):
+                main.wait_event(events[kk])  # fetches are in stream order: 0..kk have arrived
+                r0, r1 = self.group_bounds[kk], self.group_bounds[kk + 1]
+                if r1 > r0:
+                    rp, ci, v = self.blocks[kk]
+                    self.block_spmm[kk](out[r0:r1], recv, rp, ci, v)
         else:
             for kk in range(self.row_chunks):
                 main.wait_event(events[kk])

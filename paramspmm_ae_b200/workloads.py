@@ -410,9 +410,11 @@ def scaleout_brief(scale=24, nnz=512_000_000, dim=128, seed=51, iters=5, warmup=
     * ``replicated``  every rank already holds the whole dense operand: the local SpMM alone;
     * ``allgather``   one NCCL all-gather of the dense row blocks, then the SpMM;
     * ``exchange``    only the rows a shard references, fetched by the pull kernel from the owners'
-                      peer-mapped blocks in ``row_chunks`` chunks, the product of a chunk running
-                      beside the fetch of the next (``needed_pipelined`` / ``pull``); the same in one
-                      piece (``needed`` / ``pull``) and its two legs alone are reported beside it.
+                      peer-mapped blocks: in one piece followed by the product (``needed`` / ``pull``),
+                      and in ``row_chunks`` fetches ordered by the row group that first needs a row,
+                      the product of a row group running beside the next fetch
+                      (``needed_rowgroups`` / ``pull``); the faster of the two is the figure, both and
+                      the two legs of the first alone are reported.
 
     Times are CUDA-event times on the launching stream, maximum over ranks.  The replicated product
     is checked on sampled rows against fp64 dense algebra, the other forms against it.
@@ -431,7 +433,7 @@ def scaleout_brief(scale=24, nnz=512_000_000, dim=128, seed=51, iters=5, warmup=
     notes = {}
     try:
         sh_pull = ShardedSpMM(m.rowPtr, m.colIdx, m.val, n, rank, world, exchange="needed", transport="pull", **common)
-        sh_pipe = ShardedSpMM(m.rowPtr, m.colIdx, m.val, n, rank, world, exchange="needed_pipelined",
+        sh_pipe = ShardedSpMM(m.rowPtr, m.colIdx, m.val, n, rank, world, exchange="needed_rowgroups",
                               transport="pull", row_chunks=row_chunks, **common)
         src = sh_pull.symmetric_input(dim)  # peer-mapped blocks, where a producer would leave its rows
         src_pipe = sh_pipe.symmetric_input(dim)
@@ -488,8 +490,13 @@ def scaleout_brief(scale=24, nnz=512_000_000, dim=128, seed=51, iters=5, warmup=
     res["exchange_one_piece_ms"] = timed(lambda: sh_pull.forward(src, out))
     torch.testing.assert_close(out, out_rep, **tol)
     out.fill_(float("nan"))
-    res["exchange_ms"] = timed(lambda: sh_pipe.forward(src_pipe, out))
+    res["exchange_pipelined_ms"] = timed(lambda: sh_pipe.forward(src_pipe, out))
     torch.testing.assert_close(out, out_rep, **tol)
+    res["exchange_ms"] = min(res["exchange_one_piece_ms"], res["exchange_pipelined_ms"])
+    res["exchange_form"] = ("one fetch, then the product" if res["exchange_ms"] == res["exchange_one_piece_ms"]
+                            else "%d fetches ordered by first use, products of row groups overlapped" % row_chunks)
+    if transport == "pull":
+        res["first_fetch_share"] = round(sh_pipe.chunk_plan[0][1] / max(1, sh_pipe.n_needed), 4)
     res["needed_rows_fraction"] = round(sh_pull.n_needed / n, 4)
     if transport == "pull":
         # the two legs of the one-piece form alone: the fetch, and the product on the compact operand

@@ -11,7 +11,7 @@ pytestmark = pytest.mark.gpu
 
 MODES = [("allgather", "nccl", 1), ("allgather", "nccl", 4), ("needed", "nccl", 1), ("pipelined", "nccl", 1),
          ("needed_pipelined", "nccl", 1), ("pipelined", "copy_engine", 1), ("needed", "pull", 1),
-         ("needed_pipelined", "pull", 1)]
+         ("needed_pipelined", "pull", 1), ("needed_rowgroups", "pull", 1)]
 
 
 def _worker(rank, world, port, q):

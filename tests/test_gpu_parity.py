@@ -661,7 +661,8 @@ def test_pull_rows_copies_the_listed_rows(dev, dim):
         ops.pull_rows(torch.empty(n, dim, device=dev), blocks, first, rows_d, rotate=n)
 
 
-@pytest.mark.parametrize("exchange,row_chunks", [("needed", 1), ("needed_pipelined", 3)])
+@pytest.mark.parametrize("exchange,row_chunks", [("needed", 1), ("needed_pipelined", 3), ("needed_rowgroups", 3),
+                                                 ("needed_rowgroups", 7)])
 def test_pull_transport_single_rank(dev, oracle, mats, exchange, row_chunks):
     """The pull transport with one rank (the owner's block is this GPU's own buffer): same product
     as the plain kernel, twice in a row (buffers, streams and events are reused)."""

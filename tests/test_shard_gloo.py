@@ -200,13 +200,22 @@ def _pull_worker(rank, world, port, exchange, row_chunks, q):
             for s in range(world):
                 r = rows[first[s]: first[s + 1]].long()
                 assert r.numel() == 0 or (int(r.min()) >= 0 and int(r.max()) < blocks[s].shape[0])
-                assert bool((r[1:] > r[:-1]).all())  # ascending and distinct inside an owner
+                assert bool((r[1:] > r[:-1]).all())  # ascending and distinct inside an owner (and a fetch)
                 recv[base + first[s]: base + first[s + 1]] = blocks[s][r]
             end += first[-1]
         assert end == op.n_needed and not bool(torch.isnan(recv[: op.n_needed]).any())
         want = orc.spmm_csr(*m.numpy(), B.numpy())[op.lo: op.hi]
         if exchange == "needed":
             got = orc.spmm_csr(op.rowPtr.numpy(), op.colIdx.numpy(), op.val.numpy(), recv.numpy())
+        elif exchange == "needed_rowgroups":
+            # group k may only touch what fetches 0..k bring
+            ends = [base + first[-1] for base, first, _ in lists]
+            parts = []
+            for k, (rp, ci, v) in enumerate(op.blocks):
+                assert ci.numel() == 0 or int(ci.max()) < ends[k]
+                parts.append(orc.spmm_csr(rp.numpy(), ci.numpy(), v.numpy(), recv.numpy()))
+            assert [p.shape[0] for p in parts] == [b - a for a, b in zip(op.group_bounds, op.group_bounds[1:])]
+            got = np.concatenate(parts)
         else:
             got = sum(orc.spmm_csr(rp.numpy(), ci.numpy(), v.numpy(), recv.numpy()) for rp, ci, v in op.blocks)
         q.put((rank, bool(np.allclose(got, want, rtol=1e-5, atol=1e-5)), op.n_needed))
@@ -214,7 +223,8 @@ def _pull_worker(rank, world, port, exchange, row_chunks, q):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("exchange,row_chunks", [("needed", 1), ("needed_pipelined", 3)])
+@pytest.mark.parametrize("exchange,row_chunks", [("needed", 1), ("needed_pipelined", 3), ("needed_rowgroups", 3),
+                                                 ("needed_rowgroups", 1)])
 @pytest.mark.parametrize("world", [2, 3])
 def test_pull_transport_row_lists_gloo(world, exchange, row_chunks):
     ctx = mp.get_context("spawn")
