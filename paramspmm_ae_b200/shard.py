@@ -388,14 +388,16 @@ class ShardedSpMM:
                 src[:rows].copy_(B_shard)
             if fence is not None:
                 dist.all_reduce(fence, group=self.group)  # every block is in place
-            for base, cnt, recv_splits, _, want_rows in self.chunk_plan:
+            for kk, (base, cnt, recv_splits, _, want_rows) in enumerate(self.chunk_plan):
                 first = [0]
                 for c in recv_splits:
                     first.append(first[-1] + c)
                 if cnt:
                     # start at the next rank's rows so that the ranks read different owners at a time
                     rotate = first[(self.rank + 1) % self.world] % cnt
-                    ops.pull_rows(recv[base: base + cnt], peers, first, want_rows, rotate=rotate, ctas=self.pull_ctas)
+                    # no product of this call runs beside the first fetch: it may use every SM
+                    ops.pull_rows(recv[base: base + cnt], peers, first, want_rows, rotate=rotate,
+                                  ctas=self.pull_ctas if kk else 8 * self.pull_ctas)
                 ev = torch.cuda.Event()
                 ev.record(side)
                 events.append(ev)
