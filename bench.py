@@ -38,13 +38,13 @@ NNZ_PER_ROW = 16
 DIMS = list(range(16, 257, 16))
 MATRICES = ("uniform", "banded", "rmat")
 FALLBACK_HBM_GBS = 6650.0
-# DRAM bytes of one launch (dram__bytes_read.sum + dram__bytes_write.sum of an `ncu` capture of that
-# launch at 1,000,000 rows) and the source revision the captured library was built from.  A launch
-# whose kernel configuration has changed since its capture reports no traffic.
+# DRAM bytes of one SpMM (dram__bytes_read.sum + dram__bytes_write.sum of an `ncu` capture at
+# 1,000,000 rows, summed over the launches of its column tiles) and the source revision the captured
+# library was built from.
 NCU_DRAM_BYTES = {
-    ("uniform", 64): (3.172e9, "fcf53ef"), ("banded", 64): (0.602e9, "fcf53ef"), ("rmat", 64): (0.715e9, "fcf53ef"),
-    ("uniform", 128): (7.447e9, "fcf53ef"), ("banded", 128): (1.116e9, "fcf53ef"), ("rmat", 128): (2.014e9, "fcf53ef"),
-    ("uniform", 256): (16.086e9, "fcf53ef"), ("banded", 256): (2.149e9, "fcf53ef"), ("rmat", 256): (5.775e9, "fcf53ef"),
+    ("uniform", 64): (3.171e9, "ea49569"), ("banded", 64): (0.605e9, "ea49569"), ("rmat", 64): (0.712e9, "ea49569"),
+    ("uniform", 128): (6.272e9, "ea49569"), ("banded", 128): (1.131e9, "ea49569"), ("rmat", 128): (1.908e9, "ea49569"),
+    ("uniform", 256): (12.452e9, "ea49569"), ("banded", 256): (2.195e9, "ea49569"), ("rmat", 256): (5.784e9, "ea49569"),
 }
 
 
