@@ -403,7 +403,7 @@ def scaleout_spmm(scale=24, nnz=512_000_000, dim=128, seed=51, iters=5, warmup=2
 
 
 def scaleout_brief(scale=24, nnz=512_000_000, dim=128, seed=51, iters=5, warmup=2, rank=0, world=1,
-                   device="cuda:0", row_chunks=4):
+                   device="cuda:0", row_chunks=8):
     """The three strong-scaling curves of the row-sharded SpMM that the benchmark line carries at
     every GPU count (same global R-MAT matrix and dense operand as :func:`scaleout_spmm`):
 
