@@ -511,6 +511,18 @@ def scaleout_brief(scale=24, nnz=512_000_000, dim=128, seed=51, iters=5, warmup=
         res["pull_ctas"] = sh_pull.pull_ctas
         res["fetched_bytes"] = int(sh_pull.n_needed) * dim * 4
         res["spmm_on_fetched_rows_ms"] = timed(lambda: sh_pull.local_spmm(out, recv, sh_pull.rowPtr, sh_pull.colIdx, sh_pull.val))
+        if world > 1:
+            # the same copy kernel with the roles swapped: local rows gathered and WRITTEN into the next rank's
+            # peer-mapped block (nothing reads that block any more), same row count as one owner's share of a fetch
+            nxt = (rank + 1) % world
+            cnt = min(first[nxt + 1] - first[nxt], peers[nxt].shape[0], B_shard.shape[0])
+            if cnt > 0:
+                rows_local = torch.sort(torch.randperm(B_shard.shape[0], device=dev)[:cnt]).values.to(torch.int32)
+                res["remote_write_rows"] = int(cnt)
+                res["remote_write_ms"] = timed(lambda: ops.pull_rows(peers[nxt][:cnt], [B_shard], [0, cnt], rows_local,
+                                                                     ctas=sh_pull.pull_ctas))
+                res["remote_read_same_rows_ms"] = timed(lambda: ops.pull_rows(recv[:cnt], [peers[nxt]], [0, cnt], rows_local,
+                                                                              ctas=sh_pull.pull_ctas))
     res.update(notes)
     for k in list(res):
         if k.endswith("_ms"):
