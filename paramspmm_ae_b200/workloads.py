@@ -363,6 +363,20 @@ def scaleout_spmm(scale=24, nnz=512_000_000, dim=128, seed=51, iters=5, warmup=2
     out_ag.fill_(float("nan"))
     ms_needed = timed(lambda: sh_needed.forward(B_shard, out_ag), "needed rows")
     torch.testing.assert_close(out_ag, out_rep, **tol)
+    # the three legs of that form alone: pack (gather into a send buffer), all-to-all, product
+    legs = {}
+    legs["pack_ms"] = timed(lambda: B_shard.index_select(0, sh_needed.send_rows), "  needed: pack alone")
+    send_buf = B_shard.index_select(0, sh_needed.send_rows)
+    recv_buf = torch.empty(sh_needed.n_needed, dim, device=dev)
+    if world > 1:
+        legs["all_to_all_ms"] = timed(lambda: dist.all_to_all_single(recv_buf, send_buf, output_split_sizes=sh_needed.recv_splits,
+                                                                     input_split_sizes=sh_needed.send_splits), "  needed: all-to-all alone")
+    else:
+        recv_buf.copy_(send_buf)
+    legs["product_ms"] = timed(lambda: sh_needed.local_spmm(out_ag, recv_buf, sh_needed.rowPtr, sh_needed.colIdx, sh_needed.val),
+                               "  needed: product alone")
+    legs["bytes_received"] = int(sh_needed.n_needed) * dim * 4
+    del send_buf, recv_buf
     out_ag.fill_(float("nan"))
     ms_pipe = timed(lambda: sh_pipe.forward(B_shard, out_ag), "pipelined row chunks")
     torch.testing.assert_close(out_ag, out_rep, **tol)
@@ -394,7 +408,7 @@ def scaleout_spmm(scale=24, nnz=512_000_000, dim=128, seed=51, iters=5, warmup=2
             "needed_rows_pipelined_ms": round(ms_np, 4), "needed_rows_pipelined_gflops": round(gf(ms_np), 1),
             "needed_rows_exchange_spmm_ms": round(ms_needed, 4),
             "needed_rows_exchange_spmm_gflops": round(gf(ms_needed), 1),
-            "needed_rows_fraction": round(sh_needed.n_needed / n, 4),
+            "needed_rows_fraction": round(sh_needed.n_needed / n, 4), "needed_legs": {k: round(v, 4) for k, v in legs.items()},
             "spmm_replicated_gflops": round(gf(ms_rep), 1), "allgather_spmm_gflops": round(gf(ms_ag), 1),
             "allgather_overlapped_gflops": round(gf(ms_ov), 1),
             "compulsory_bytes_global": by, "spmm_replicated_gbs_global": round(by / ms_rep / 1e6, 1),
