@@ -45,6 +45,7 @@ NCU_DRAM_BYTES = {
     ("uniform", 64): (3.171e9, "ea49569"), ("banded", 64): (0.605e9, "ea49569"), ("rmat", 64): (0.712e9, "ea49569"),
     ("uniform", 128): (6.272e9, "ea49569"), ("banded", 128): (1.131e9, "ea49569"), ("rmat", 128): (1.908e9, "ea49569"),
     ("uniform", 256): (12.452e9, "ea49569"), ("banded", 256): (2.195e9, "ea49569"), ("rmat", 256): (5.784e9, "ea49569"),
+    ("uniform", 240): (15.854e9, "16831dc"), ("banded", 240): (2.056e9, "16831dc"), ("rmat", 240): (5.389e9, "16831dc"),
 }
 
 
