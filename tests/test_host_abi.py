@@ -272,3 +272,60 @@ def test_header_is_plain_c_and_declares_what_the_python_shim_binds(tmp_path):
     subprocess.run(["gcc", "-std=c99", "-I", os.path.join(root, "include"), str(src), "-o", str(exe),
                     _lib.LIB_PATH, "-Wl,-rpath," + os.path.dirname(_lib.LIB_PATH)], check=True)
     assert subprocess.run([str(exe)]).returncode == 0
+
+
+def test_new_entry_points_validate_before_touching_the_device(pspmm_lib):
+    """pspmm_pull_rows, pspmm_agnn_fused_apply_csr, the bucketed flag and the block SDDMM's row count
+    of A: bad arguments come back as codes (no CUDA call is reached with them)."""
+    from paramspmm_ae_b200 import _lib
+    null, one = ctypes.c_void_p(0), ctypes.c_void_p(16)
+    src = _lib.RowSources()
+    src.n_src = 1
+    src.base[0] = 16
+    src.first[0], src.first[1] = 0, 8
+    call = lambda n, dim, lds, ldd, rot, s=src: pspmm_lib.pspmm_pull_rows(ctypes.byref(s), one, n, one, dim, lds, ldd, rot, 0, null)
+    assert call(8, 0, 16, 16, 0) == _lib.PSPMM_E_ARG            # dim
+    assert call(8, 16, 8, 16, 0) == _lib.PSPMM_E_ARG            # row stride smaller than dim
+    assert call(8, 16, 16, 16, 8) == _lib.PSPMM_E_ARG           # rotate outside the list
+    assert call(9, 16, 16, 16, 0) == _lib.PSPMM_E_ARG           # the sources do not cover the list
+    assert call(8, 18, 20, 20, 0) == _lib.PSPMM_E_UNSUPPORTED   # not 128-bit accessible
+    assert call(0, 16, 16, 16, 0) == _lib.PSPMM_OK              # nothing to copy
+    bad = _lib.RowSources()
+    bad.n_src = _lib.MAX_ROW_SOURCES + 1
+    assert call(8, 16, 16, 16, 0, bad) == _lib.PSPMM_E_ARG
+    # bucketed is a 0/1 flag of the SpMM only
+    assert pspmm_lib.pspmm_spmm_csr(one, one, one, one, one, 4, 4, 4, 16, 16, 16, ctypes.byref(_lib.make_cfg(bucketed=2)),
+                                    null, null, 0, null) == _lib.PSPMM_E_CONFIG
+    assert pspmm_lib.pspmm_sddmm_csr(one, one, one, one, one, 4, 4, 16, 16, 16, ctypes.byref(_lib.make_cfg(bucketed=1)),
+                                     null, null, 0, null) == _lib.PSPMM_E_CONFIG
+    # block SDDMM: A must reach into the last block-row
+    cfg = _lib.make_cfg()
+    assert pspmm_lib.pspmm_sddmm_bcsr(one, one, one, 2, one, one, one, 5, 8, 4, 16, 16, 16, ctypes.byref(cfg),
+                                      null, null, 0, null) == _lib.PSPMM_E_ARG
+    # fused aggregation with a separate operand: V missing, V's stride too small
+    f = pspmm_lib.pspmm_agnn_fused_apply_csr
+    assert f(one, one, one, one, null, one, 4, 4, 16, 16, 16, 16, 16, 1.0, 0, 0, 0, 0, null, null, 0, null, 0, null) == _lib.PSPMM_E_ARG
+    assert f(one, one, one, one, one, one, 4, 4, 16, 16, 16, 8, 16, 1.0, 0, 0, 0, 0, null, null, 0, null, 0, null) == _lib.PSPMM_E_ARG
+
+
+def test_block_builder_rejects_bad_columns_and_inconsistent_counts(pspmm_lib):
+    """The host block builder range-checks column ids and never writes more blocks than the row
+    pointer it is given allows."""
+    import numpy as np
+    from paramspmm_ae_b200 import _lib
+    p = lambda a: ctypes.c_void_p(a.ctypes.data)
+    rp = np.array([0, 2, 3, 5], dtype=np.int32)
+    ci = np.array([0, 3, 1, 2, 9], dtype=np.int32)    # 9 is outside [0, 4)
+    v = np.ones(5, dtype=np.float32)
+    rpb = np.zeros(3, dtype=np.int32)
+    nblk = ctypes.c_int64(0)
+    assert pspmm_lib.pspmm_bcsr_count(p(rp), p(ci), 3, 4, 2, p(rpb), ctypes.byref(nblk)) == _lib.PSPMM_E_ARG
+    ci[4] = 3
+    assert pspmm_lib.pspmm_bcsr_count(p(rp), p(ci), 3, 4, 2, p(rpb), ctypes.byref(nblk)) == _lib.PSPMM_OK
+    assert rpb.tolist() == [0, 3, 5] and nblk.value == 5
+    # a row pointer that promises fewer blocks than the rows hold: an error, and the arrays' tails stay untouched
+    lie = np.array([0, 1, 2], dtype=np.int32)
+    cb = np.full(6, -7, dtype=np.int32)
+    vb = np.full(12, -7.0, dtype=np.float32)
+    assert pspmm_lib.pspmm_bcsr_fill(p(rp), p(ci), p(v), 3, 4, 2, p(lie), p(cb), p(vb)) == _lib.PSPMM_E_ARG
+    assert (cb[2:] == -7).all() and (vb[4:] == -7).all()
