@@ -60,7 +60,10 @@ class GCNFunction(torch.autograd.Function):
             d_input = _aggregate(P, torch.mm(d_output, weight.t())) if ctx.needs_input_grad[0] else None
             return d_input, d_weight, None
         H, weight = ctx.saved_tensors
-        d_input, d_weight = P.backward(d_output, H, weight)
+        if ctx.needs_input_grad[0]:
+            d_input, d_weight = P.backward(d_output, H, weight)
+        else:  # the first layer: dH = AG W^T is not formed (the reference forms and drops it)
+            d_input, d_weight = P.backward(d_output, H, weight, input_grad=False)
         return d_input, d_weight, None
 
 

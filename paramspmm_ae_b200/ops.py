@@ -669,25 +669,42 @@ def genmask(rowPtr_bcsr, rowPtr, blkval, nnz):
 
 
 # ----------------------------------------------------------------------------- GCN layer (SpCONV)
-def _conv_forward(V, H, weight, rowPtr, colIdx, val, target_row, CF, W):
-    """A @ (H @ W): dense GEMM (cuBLAS through torch.mm) then SpMM (SpCONV/SpCONV.h:43-193)."""
+def _pad_cols(t, pad):
+    return torch.nn.functional.pad(t, (0, pad)) if pad else t
+
+
+def _conv_forward(V, H, weight, rowPtr, colIdx, val, target_row, CF, W, product=None):
+    """A @ (H @ W): dense GEMM (cuBLAS through torch.mm) then SpMM (SpCONV/SpCONV.h:43-193).
+
+    An output width that is not a multiple of 4 (class counts: 47, 41, ...) is carried as the next
+    multiple of 4 through both products, by a zero column appended to the weights, so that the
+    SpMM runs with 128-bit accesses on 16-byte aligned rows; the extra column is dropped from the
+    result.  ``product`` replaces the SpMM launch (an operator bound to a decider plan)."""
     _check_legacy(CF, W, max_cf=4)  # SpCONV/SpCONV.cpp:93-104
-    HW = torch.mm(H, weight)
+    fout = weight.shape[1]
+    HW = torch.mm(H, _pad_cols(weight, -fout % 4))
     n = HW.shape[0]
-    out = _spmm(HW, rowPtr, colIdx, val, target_row, V, CF, W)
-    return out[:n] if out.shape[0] != n else out  # block variants slice back (SpCONV.h:115-118)
+    out = product(HW) if product else _spmm(HW, rowPtr, colIdx, val, target_row, V, CF, W)
+    if out.shape[0] != n:
+        out = out[:n]  # block variants slice back (SpCONV.h:115-118)
+    return out[:, :fout].contiguous() if out.shape[1] != fout else out
 
 
-def _conv_backward(V, g_out, H, weight, rowPtr, colIdx, val, target_row, CF, W):
+def _conv_backward(V, g_out, H, weight, rowPtr, colIdx, val, target_row, CF, W, product=None, input_grad=True):
     """AG = A @ g_out (A itself, the normalised adjacency is symmetric); dH = AG @ W^T;
-    dW = H^T @ AG (SpCONV/SpCONV.h:57-72)."""
+    dW = H^T @ AG (SpCONV/SpCONV.h:57-72).  Odd widths are padded as in the forward.
+    ``input_grad=False`` leaves dH out (None): the first layer of a network has no use for it."""
     _check_legacy(CF, W, max_cf=4)
-    g_out = g_out.contiguous()
+    fout = g_out.shape[1]
+    pad = -fout % 4
+    g_out = _pad_cols(g_out, pad).contiguous()
     n = g_out.shape[0]
-    AG = _spmm(g_out, rowPtr, colIdx, val, target_row, V, CF, W)
+    AG = product(g_out) if product else _spmm(g_out, rowPtr, colIdx, val, target_row, V, CF, W)
     if AG.shape[0] != n:
         AG = AG[:n]
-    return [torch.mm(AG, weight.t()), torch.mm(H.t(), AG)]
+    d_weight = torch.mm(H.t(), AG)
+    d_input = torch.mm(AG, _pad_cols(weight, pad).t()) if input_grad else None
+    return [d_input, d_weight[:, :fout].contiguous() if pad else d_weight]
 
 
 def csr_spmm_forward(H, weight, rowPtr, colIdx, val, CF, blkWarpNum):

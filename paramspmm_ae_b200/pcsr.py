@@ -28,8 +28,6 @@ _SDDMM_PROFILE = {("csr", False): ops.csr_sddmm_profile, ("csr", True): ops.csr_
                   ("vec", False): ops.vec_sddmm_profile, ("vec", True): ops.vec_split_sddmm_profile}
 _CONV_FWD = {("csr", False): ops.csr_spmm_forward, ("csr", True): ops.csr_split_spmm_forward,
              ("bcsr", False): ops.bcsr_spmm_forward, ("bcsr", True): ops.bcsr_split_spmm_forward}
-_CONV_BWD = {("csr", False): ops.csr_spmm_backward, ("csr", True): ops.csr_split_spmm_backward,
-             ("bcsr", False): ops.bcsr_spmm_backward, ("bcsr", True): ops.bcsr_split_spmm_backward}
 
 
 class _format_spmm(object):
@@ -126,6 +124,36 @@ class pcsr_spmm(object):
                 self.mask = graph.mask.to(device)
         self.vec_size, self.if_split, self.CF, self.blkWarpNum = vec_size, if_split, CF, blkWarpNum
         self.result = None
+        self._planned = None
+
+    @classmethod
+    def from_plan(cls, plan, rowPtr, colIdx, val, mtx_nodes=None, device="cuda"):
+        """Operator bound to a decider plan (``decider.choose`` / ``SpMMDecider.plan``) instead of
+        the legacy tuple: the products with the stored values (``GIN_spmm``, ``forward``,
+        ``backward``, ``get_spmm_result``) run the layout and kernel parameters the plan names,
+        the length-bucketed internal plan included, which the legacy signatures cannot express.
+        The CSR arrays stay attached for everything else (SDDMM, ``AGNN_spmm`` with caller-supplied
+        edge values, the comparators).  The reference has no counterpart: its operators carry
+        ``(vec_size, if_split, CF, blkWarpNum)`` only (PCSR.py:128-204)."""
+        from . import decider
+        n = rowPtr.shape[0] - 1 if mtx_nodes is None else mtx_nodes
+        self = cls(None, 1, False, n, colIdx.shape[0], rowPtr, colIdx, val, None, CF=1, blkWarpNum=8, device=device)
+        self._planned = decider.PlannedSpMM(plan, self.rowPtr, self.colIdx, self.val, n_cols=n)
+        return self
+
+    def _planned_product(self, X):
+        """One output row per input row, as the legacy operators give (rows beyond the matrix zero);
+        a width that is not a multiple of 4 is padded for the launch and cut back."""
+        n, dim = X.shape
+        Xp = ops._pad_cols(X, -dim % 4).contiguous()
+        rows = self._planned.n_rows
+        if n < rows:
+            raise RuntimeError("the matrix has %d rows, the input only %d" % (rows, n))
+        out = torch.empty((n, Xp.shape[1]), dtype=torch.float32, device=X.device)
+        if n > rows:
+            out[rows:].zero_()
+        self._planned(out[:rows], Xp)
+        return out[:, :dim].contiguous() if Xp.shape[1] != dim else out
 
     # -- helpers ------------------------------------------------------------------------
     def _key(self):
@@ -149,7 +177,7 @@ class pcsr_spmm(object):
         X = self._dense_input(dim, x)
         CF = self.CF if CF is None else CF
         W = self.blkWarpNum if blkWarpNum is None else blkWarpNum
-        out = _SPMM[self._key()](X, *self._layout(), CF, W)
+        out = self._planned_product(X) if self._planned else _SPMM[self._key()](X, *self._layout(), CF, W)
         self.result = out[: self.mtx_nodes].to("cpu")  # block layouts pad the row count
 
     def AGNN_spmm(self, spVal, X):
@@ -157,6 +185,8 @@ class pcsr_spmm(object):
         return _SPMM[self._key()](X, *self._layout(spVal), self.CF, self.blkWarpNum)
 
     def GIN_spmm(self, X):
+        if self._planned:
+            return self._planned_product(X)
         return _SPMM[self._key()](X, *self._layout(), self.CF, self.blkWarpNum)
 
     # -- SDDMM --------------------------------------------------------------------------
@@ -180,12 +210,20 @@ class pcsr_spmm(object):
     def forward(self, H, w):
         if H is None or w is None:
             raise ValueError("H and w should be given")
+        if self._planned:
+            return ops._conv_forward(1, H, w, None, None, None, None, self.CF, self.blkWarpNum, product=self._planned_product)
         return _CONV_FWD[self._conv_key()](H, w, *self._layout(), self.CF, self.blkWarpNum)
 
-    def backward(self, d_output, H, w):
+    def backward(self, d_output, H, w, input_grad=True):
+        """(dH, dW) of the layer (PCSR.py:381-432); ``input_grad=False`` skips the dH product and
+        returns None in its place (no reference counterpart: it always forms both)."""
         if d_output is None or H is None:
             raise ValueError("d_output and H should be given")
-        return tuple(_CONV_BWD[self._conv_key()](d_output, H, w, *self._layout(), self.CF, self.blkWarpNum))
+        V = 1 if self.vec_size == 1 else 2
+        layout = (None, None, None, None) if self._planned else self._layout() + ((None,) if not self.if_split else ())
+        return tuple(ops._conv_backward(V, d_output, H, w, *layout, self.CF, self.blkWarpNum,
+                                        product=self._planned_product if self._planned else None,
+                                        input_grad=input_grad))
 
     # -- timing -------------------------------------------------------------------------
     def cf_warpnum_profiling(self, CF, blkWarpNum, dim=None, x=None):

@@ -223,25 +223,29 @@ def gcn_forward_backward(n=2_449_029, pairs=61_900_000, feats=100, hidden=256, c
     t0 = time.time()
     g = synth.powerlaw_graph(n, pairs, seed=seed, device=dev)
     gen_s = time.time() - t0
-    stats = decider.row_stats(g.rowPtr)
+    stats = decider.row_stats(g.rowPtr, g.colIdx)
     dims = [hidden, hidden, classes]
-    ops_by_dim = {}
+    # Two sets of operators: the legacy tuple form the reference's GNN.py builds (layout chosen by
+    # the decider, library-default kernel parameters), and operators bound to the decider's plan
+    # (the table's kernel parameters and the length-bucketed plan where it names it).
+    legacy_by_dim, ops_by_dim = {}, {}
     for d in set(dims):
         plan = decider.choose(stats, d)
         if plan["if_split"]:
             rps, tr = ops.split_csr(g.rowPtr.cpu(), plan["granularity"])
-            ops_by_dim[d] = pcsr.pcsr_spmm(None, 1, True, n, g.nnz, rps, g.colIdx, g.val, tr, CF=1, blkWarpNum=8)
+            legacy_by_dim[d] = pcsr.pcsr_spmm(None, 1, True, n, g.nnz, rps, g.colIdx, g.val, tr, CF=1, blkWarpNum=8)
         else:
-            ops_by_dim[d] = pcsr.pcsr_spmm(None, 1, False, n, g.nnz, g.rowPtr, g.colIdx, g.val, None, CF=1, blkWarpNum=8)
+            legacy_by_dim[d] = pcsr.pcsr_spmm(None, 1, False, n, g.nnz, g.rowPtr, g.colIdx, g.val, None, CF=1, blkWarpNum=8)
+        ops_by_dim[d] = pcsr.pcsr_spmm.from_plan(plan, g.rowPtr, g.colIdx, g.val)
     torch.manual_seed(seed + 2)
     layers = [gnn_conv.GCNConv(a, b).to(dev) for a, b in zip([feats, hidden, hidden], dims)]
     X = synth.dense_normal(n, feats, seed + 1, dev)
     y = torch.randint(0, classes, (n,), device=dev, generator=torch.Generator(device=dev).manual_seed(seed + 3))
 
-    def step():
+    def step(operators=None):
         h = X
         for i, l in enumerate(layers):
-            h = l(h, ops_by_dim)
+            h = l(h, operators or ops_by_dim)
             if i < 2:
                 h = torch.relu(h)
         loss = torch.nn.functional.cross_entropy(h, y)
@@ -265,19 +269,48 @@ def gcn_forward_backward(n=2_449_029, pairs=61_900_000, feats=100, hidden=256, c
         checked["layer1"] = round(check_rows_fp64(g.rowPtr, g.colIdx, g.val, XW, out1, rows, "first GCN layer"), 3)
         del XW, out1
 
-    def timed(reorder):
+    def timed(reorder, operators=None):
         old = gnn_conv.REORDER_NARROW_FIRST
         gnn_conv.REORDER_NARROW_FIRST = reorder
         try:
-            return _time_ms(step, warmup=1, iters=iters), float(step())
+            run = lambda: step(operators)
+            return _time_ms(run, warmup=1, iters=iters), float(run())
         finally:
             gnn_conv.REORDER_NARROW_FIRST = old
 
-    ms, loss = timed(False)            # the reference's operation order, A (H W) in every layer
+    ms_legacy, loss_legacy = timed(False, legacy_by_dim)  # the reference's operation order, A (H W), legacy operators
+    ms, loss = timed(False)            # the same order on the plan-bound operators
     ms_reorder, loss_reorder = timed(True)   # widening layers aggregate first, (A H) W
+
+    # Where a step's time goes: the aggregation alone at each width (legacy and plan-bound), the
+    # class-count width with and without the padding to a multiple of 4, and the dense products.
+    parts = {}
+    for d in sorted(set(dims)):
+        Z = synth.dense_normal(n, d, seed + 7 + d, dev)
+        parts["spmm_dim%d_legacy_ms" % d] = round(_time_ms(lambda: legacy_by_dim[d].GIN_spmm(Z), warmup=2, iters=5), 3)
+        parts["spmm_dim%d_planned_ms" % d] = round(_time_ms(lambda: ops_by_dim[d].GIN_spmm(Z), warmup=2, iters=5), 3)
+        if d % 4:
+            Zp = torch.nn.functional.pad(Z, (0, -d % 4))
+            parts["spmm_dim%d_legacy_padded_ms" % d] = round(_time_ms(lambda: legacy_by_dim[d].GIN_spmm(Zp), warmup=2, iters=5), 3)
+        del Z
+    H1 = synth.dense_normal(n, hidden, seed + 5, dev)
+
+    def dense_products():
+        for a, b in zip([feats, hidden, hidden], dims):
+            w = torch.empty(a, b, device=dev)
+            h = X if a == feats else H1
+            torch.mm(h, w)                                   # forward H W
+            gz = H1[:, :b] if b != hidden else H1
+            if a != feats:
+                torch.mm(gz, w.t())                          # dH = AG W^T (not formed for the first layer)
+            torch.mm(h.t(), gz)                              # dW = H^T AG
+    parts["dense_products_ms"] = round(_time_ms(dense_products, warmup=1, iters=3), 3)
+    del H1
     spmm_flops = 2.0 * g.nnz * (sum(dims) * 2)  # one SpMM per layer forward, one backward
     return {"n": n, "nnz": g.nnz, "generate_s": round(gen_s, 1), "ms_per_step": round(ms, 2),
+            "ms_per_step_legacy_operators": round(ms_legacy, 2), "loss_legacy_operators": loss_legacy,
             "ms_per_step_narrow_first": round(ms_reorder, 2), "loss": loss, "loss_narrow_first": loss_reorder,
+            "parts": parts,
             "spmm_gflop_per_step": round(spmm_flops / 1e9, 1), "regime": decider.regime(stats),
             "fp64_row_checks_worst_error_over_bound": checked, "rows_checked": int(rows.numel())}
 

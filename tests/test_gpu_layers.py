@@ -19,7 +19,12 @@ def _graph(dev, n=257, pairs=1500):
 
 
 def _operator(g, dev, split):
-    from paramspmm_ae_b200 import ops, pcsr
+    from paramspmm_ae_b200 import decider, ops, pcsr
+    if split in ("plan", "plan_split", "plan_bucketed"):  # operators bound to a decider plan
+        plan = decider.Plan(vec_size=1, lanes_per_row=0, vec_width=0, cta_threads=0, rows_per_group=0, gather_batch=0,
+                            col_tile=0, if_split=int(split != "plan"), granularity=8,
+                            bucketed=int(split == "plan_bucketed"))
+        return pcsr.pcsr_spmm.from_plan(plan, g.rowPtr.to(dev), g.colIdx.to(dev), g.val.to(dev))
     if split:
         rps, tr = ops.split_csr(g.rowPtr, 8)
         return pcsr.pcsr_spmm(None, 1, True, g.n_rows, g.nnz, rps, g.colIdx, g.val, tr, CF=1, blkWarpNum=8)
@@ -30,8 +35,8 @@ def _close(got, want):
     torch.testing.assert_close(got.double(), want.double(), rtol=1e-5, atol=1e-4)
 
 
-@pytest.mark.parametrize("split", [False, True])
-@pytest.mark.parametrize("fin,fout", [(12, 32), (32, 12), (16, 16)])
+@pytest.mark.parametrize("split", [False, True, "plan", "plan_split", "plan_bucketed"])
+@pytest.mark.parametrize("fin,fout", [(12, 32), (32, 12), (16, 16), (32, 47), (7, 10)])
 @pytest.mark.parametrize("reorder", [True, False])
 @pytest.mark.parametrize("input_grad", [True, False])
 def test_gcn_layer_forward_and_gradients(split, fin, fout, reorder, input_grad):
@@ -88,6 +93,30 @@ def test_gin_and_agnn_layers_match_dense_algebra():
     fused = ops.agnn_fused(Xp.float().contiguous(), Xp.float().contiguous(), g.rowPtr.to(dev), g.colIdx.to(dev),
                            float(agnn.attention_w.detach().reshape(())), softmax=False)
     _close(fused, E @ Xp)
+
+
+@pytest.mark.parametrize("kind", ["plan", "plan_bucketed"])
+def test_plan_bound_operator_products(kind):
+    """pcsr_spmm.from_plan: aggregation at an odd width, more input rows than the matrix has, the
+    result method, and the methods that keep using the CSR arrays."""
+    dev = torch.device("cuda:0")
+    g, A = _graph(dev)
+    P = _operator(g, dev, kind)
+    X = torch.randn(g.n_rows + 1, 15, device=dev, generator=torch.Generator(device=dev).manual_seed(8))
+    out = P.GIN_spmm(X)
+    assert out.shape == (g.n_rows + 1, 15) and out.is_contiguous()
+    _close(out[: g.n_rows], A @ X[: g.n_rows].double())
+    assert float(out[g.n_rows].abs().max()) == 0.0
+    with pytest.raises(RuntimeError):
+        P.GIN_spmm(X[: g.n_rows - 1])
+    P.get_spmm_result(dim=16)
+    _close(P.result.to(dev), A.sum(1, keepdim=True).expand(-1, 16))
+    e = torch.rand(g.nnz, device=dev)
+    Ae = torch.zeros_like(A)
+    rp, ci, _ = g.numpy()
+    rows = torch.repeat_interleave(torch.arange(g.n_rows), torch.from_numpy(np.diff(rp)).long()).to(dev)
+    Ae[rows, torch.from_numpy(ci).long().to(dev)] = e.double()
+    _close(P.AGNN_spmm(e, X[: g.n_rows, :12].contiguous()), Ae @ X[: g.n_rows, :12].double())
 
 
 @pytest.mark.parametrize("split", [False, True])

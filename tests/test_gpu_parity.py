@@ -440,27 +440,30 @@ def test_spmm_output_rows_follow_the_dense_input(dev, oracle, mats):
         ops.csr_spmm(Xd[: n - 1].contiguous(), d.rowPtr, d.colIdx, d.val, 1, 8)
 
 
-def test_spconv_forward_backward(dev, oracle, mats):
-    """GCN layer A(HW) and its gradients (SpCONV/SpCONV.h:43-72) against dense fp64 algebra."""
+@pytest.mark.parametrize("fout", [24, 23, 1])
+def test_spconv_forward_backward(dev, oracle, mats, fout):
+    """GCN layer A(HW) and its gradients (SpCONV/SpCONV.h:43-72) against dense fp64 algebra; widths
+    that are not a multiple of 4 travel padded through the products and come back cut."""
     from paramspmm_ae_b200 import ops
     m = mats["powerlaw"]  # symmetric: the backward pass multiplies by A, not A^T
     rp, ci, v = m.numpy()
     d = m.to(dev)
     n = m.n_rows
     H = dense(n, 40, 1)
-    W = dense(40, 24, 2)
-    G = dense(n, 24, 3)
+    W = dense(40, fout, 2)
+    G = dense(n, fout, 3)
     HW = (H.double() @ W.double()).float().numpy()
     want = oracle.spmm_csr(rp, ci, v, HW)
     got = ops.csr_spmm_forward(H.to(dev), W.to(dev), d.rowPtr, d.colIdx, d.val, 1, 4)
     np.testing.assert_allclose(got.cpu().numpy(), want, rtol=1e-4, atol=1e-4)
     AG = oracle.spmm_csr(rp, ci, v, G.numpy()).astype(np.float64)
     dH, dW = ops.csr_spmm_backward(G.to(dev), H.to(dev), W.to(dev), d.rowPtr, d.colIdx, d.val, 1, 4)
+    assert dH.shape == (n, 40) and dW.shape == (40, fout) and dW.is_contiguous()
     np.testing.assert_allclose(dH.cpu().numpy(), AG @ W.double().numpy().T, rtol=1e-4, atol=1e-4)
     np.testing.assert_allclose(dW.cpu().numpy(), H.double().numpy().T @ AG, rtol=1e-4, atol=2e-3)
     rpb, cb, vb = ops.bcsr_from_csr(m.rowPtr, m.colIdx, m.val, n, 2)
     got = ops.bcsr_spmm_forward(H.to(dev), W.to(dev), rpb.to(dev), cb.to(dev), vb.to(dev), 1, 4)
-    assert got.shape == (n, 24)  # sliced back from the padded row count
+    assert got.shape == (n, fout) and got.is_contiguous()  # sliced back from the padded row count
     np.testing.assert_allclose(got.cpu().numpy(), want, rtol=1e-4, atol=1e-4)
 
 
