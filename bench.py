@@ -536,7 +536,8 @@ def main():
         try:
             r = workloads.scaleout_brief(scale=args.c5_scale, nnz=args.c5_nnz, iters=args.scaleout_iters, rank=rank,
                                          world=world, device="cuda:%d" % local)
-            gf = lambda ms: round(2.0 * r["nnz"] * r["dim"] / ms / 1e6, 1)
+            flop = 2.0 * r["nnz"] * r["dim"]
+            gf = lambda ms: round(flop / ms / 1e6, 1)
             scaleout = {"workload": "c5_scaleout: R-MAT 2^%d nodes, %d entries, dim %d, rows of A in contiguous blocks "
                                     "balanced by nnz, one block per GPU" % (args.c5_scale, r["nnz"], r["dim"]),
                         "scaling": "strong", "n_gpus": world,
@@ -547,6 +548,22 @@ def main():
                         "exchange_form": "rows referenced by the shard only, fetched from the owners' peer-mapped blocks "
                                          "by the pull kernel: %s (transport %s)" % (r["exchange_form"], r["transport"]),
                         "detail": r}
+            if world > 1:
+                # the same matrix with its nodes relabelled by a seeded random permutation (P A P^T): equal rows,
+                # entries and exchange traffic per rank instead of the nnz-balanced blocks of the natural order
+                torch.cuda.empty_cache()
+                try:
+                    ri = workloads.scaleout_brief(scale=args.c5_scale, nnz=args.c5_nnz, iters=args.scaleout_iters,
+                                                  rank=rank, world=world, device="cuda:%d" % local,
+                                                  labels="scattered", legs=False)
+                    scaleout["scattered_labels"] = {
+                        "what": "same global matrix, nodes relabelled by a seeded random permutation before sharding "
+                                "(shard.scattered_labels); same product up to the order of rows",
+                        "replicated_ms": ri["replicated_ms"], "allgather_ms": ri["allgather_ms"],
+                        "exchange_ms": ri["exchange_ms"], "exchange_gflops": gf(ri["exchange_ms"]),
+                        "exchange_form": ri["exchange_form"], "detail": ri}
+                except Exception as e:
+                    scaleout["scattered_labels"] = {"unavailable": "%s: %s" % (type(e).__name__, e)}
         except Exception as e:  # the headline number must not depend on this leg
             scaleout = {"unavailable": "%s: %s" % (type(e).__name__, e)}
 

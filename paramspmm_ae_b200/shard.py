@@ -83,6 +83,45 @@ def partition_rows_even(n, world):
     return torch.tensor([(n * p) // world for p in range(world + 1)], dtype=torch.long)
 
 
+def scattered_labels(n, seed=0):
+    """new_of_old [n] (int64): a seeded random permutation of the node ids, the same on every rank.
+
+    On matrices whose degree depends on the node id (R-MAT: on its bits; degree-sorted graphs: on
+    its size) contiguous row blocks balanced by nnz give one rank the hubs and another most of the
+    rows; the latter then owns, and has to send, most of the dense rows the others reference, and
+    its outgoing link bounds the exchange.  With scattered labels every block is a uniform sample of
+    the nodes: about equal rows, equal entries and equal traffic in and out of every rank, for any
+    number of ranks.  It also scatters whatever index locality the matrix had, so it is meant for
+    skewed matrices without a band structure.  Apply once when the graph is loaded
+    (:func:`relabel_symmetric`); features, labels and outputs then live in the new order."""
+    g = torch.Generator()
+    g.manual_seed(int(seed))
+    return torch.randperm(n, generator=g, dtype=torch.int64)
+
+
+def relabel_symmetric(rowPtr, colIdx, val, new_of_old):
+    """P A P^T for the permutation ``new_of_old``: CSR arrays (int32, int32, fp32) of the matrix
+    whose row and column ids are the new labels, columns sorted inside every row.  Runs on the
+    device the arrays are on."""
+    dev = colIdx.device
+    n = rowPtr.shape[0] - 1
+    perm = torch.as_tensor(new_of_old).to(dev).long()
+    if perm.shape[0] != n or colIdx.numel() and int(colIdx.max()) >= n:
+        raise ValueError("a symmetric relabelling needs a square matrix and one label per node")
+    lens = (rowPtr[1:] - rowPtr[:-1]).long()
+    keys = torch.repeat_interleave(perm, lens) * n
+    keys += perm[colIdx.long()]
+    keys, order = torch.sort(keys)
+    new_val = val[order]
+    del order
+    rows = torch.div(keys, n, rounding_mode="floor")
+    new_col = (keys - rows * n).to(torch.int32)
+    del keys
+    rp = torch.zeros(n + 1, dtype=torch.int64, device=dev)
+    rp[1:] = torch.cumsum(torch.bincount(rows, minlength=n), 0)
+    return rp.to(torch.int32), new_col, new_val
+
+
 def extract_rows(rowPtr, colIdx, val, lo, hi):
     """Rows [lo, hi) of a CSR matrix with re-based row pointers and global column ids."""
     rp = torch.as_tensor(rowPtr)

@@ -450,7 +450,7 @@ def scaleout_spmm(scale=24, nnz=512_000_000, dim=128, seed=51, iters=5, warmup=2
 
 
 def scaleout_brief(scale=24, nnz=512_000_000, dim=128, seed=51, iters=5, warmup=2, rank=0, world=1,
-                   device="cuda:0", row_chunks=8):
+                   device="cuda:0", row_chunks=8, labels="natural", legs=True):
     """The three strong-scaling curves of the row-sharded SpMM that the benchmark line carries at
     every GPU count (same global R-MAT matrix and dense operand as :func:`scaleout_spmm`):
 
@@ -463,15 +463,27 @@ def scaleout_brief(scale=24, nnz=512_000_000, dim=128, seed=51, iters=5, warmup=
                       (``needed_rowgroups`` / ``pull``); the faster of the two is the figure, both and
                       the two legs of the first alone are reported.
 
+    ``labels="scattered"`` relabels the nodes by a seeded random permutation first
+    (``shard.scattered_labels``, a symmetric permutation P A P^T: the same product up to the order
+    of rows): every rank then holds the same mix of rows instead of rank 0 the hubs and the last rank
+    most of the rows, and no rank's outgoing link carries more than its share of the exchange.
+    ``legs=False`` leaves out the timings of the separate legs.
+
     Times are CUDA-event times on the launching stream, maximum over ranks.  The replicated product
     is checked on sampled rows against fp64 dense algebra, the other forms against it.
     """
     import torch.distributed as dist
+    from . import shard
     from .shard import ShardedSpMM
 
     dev = torch.device(device)
     m = synth.rmat(scale, nnz, seed=seed, device=dev)
     n = m.n_rows
+    if labels == "scattered":
+        m.rowPtr, m.colIdx, m.val = shard.relabel_symmetric(m.rowPtr, m.colIdx, m.val, shard.scattered_labels(n, seed))
+        torch.cuda.empty_cache()
+    elif labels != "natural":
+        raise ValueError("labels is 'natural' or 'scattered'")
     sh = ShardedSpMM(m.rowPtr, m.colIdx, m.val, n, rank, world, device=dev)
     a, b = int(m.rowPtr[sh.lo]), int(m.rowPtr[sh.hi])
     cols_global = m.colIdx[a:b].clone()
@@ -517,7 +529,8 @@ def scaleout_brief(scale=24, nnz=512_000_000, dim=128, seed=51, iters=5, warmup=
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    res = {"world": world, "n": n, "nnz": nnz_total, "dim": dim, "row_chunks": row_chunks, "transport": transport}
+    res = {"world": world, "n": n, "nnz": nnz_total, "dim": dim, "row_chunks": row_chunks, "transport": transport,
+           "labels": labels, "local_rows": int(sh.local_rows)}
     res["replicated_ms"] = timed(lambda: sh.forward_replicated(B_full, out_rep))
     rows = sample_rows(sh.rowPtr, 40, seed)
     res["fp64_worst_error_over_bound"] = round(check_rows_fp64(sh.rowPtr, cols_global, sh.val, B_full, out_rep, rows,
@@ -546,6 +559,18 @@ def scaleout_brief(scale=24, nnz=512_000_000, dim=128, seed=51, iters=5, warmup=
         res["first_fetch_share"] = round(sh_pipe.chunk_plan[0][1] / max(1, sh_pipe.n_needed), 4)
     res["needed_rows_fraction"] = round(sh_pull.n_needed / n, 4)
     if transport == "pull":
+        # rows every owner sends (summed over the ranks that fetch from it) against rows every rank
+        # receives: the busiest outgoing link bounds the exchange
+        first_all = sh_pull.pull_lists()[0][1]
+        mine = torch.tensor([first_all[p + 1] - first_all[p] if p != rank else 0 for p in range(world)],
+                            device=dev, dtype=torch.int64)
+        sent = mine.clone()
+        if world > 1:
+            dist.all_reduce(sent)
+        res["rows_received_by_this_rank"] = int(mine.sum())
+        res["rows_sent_per_owner"] = [int(x) for x in sent.tolist()]
+        res["busiest_sender_over_mean"] = round(float(sent.max()) / max(1.0, float(sent.double().mean())), 3)
+    if transport == "pull" and legs:
         # the two legs of the one-piece form alone: the fetch, and the product on the compact operand
         base, first, want_rows = sh_pull.pull_lists()[0]
         _, peers, _ = sh_pull._peer_blocks(dim, B_shard)

@@ -245,3 +245,49 @@ def test_pull_transport_rejects_other_exchanges():
     m = synth.uniform_rows(20, 3, seed=1)
     with pytest.raises(ValueError):
         shard.ShardedSpMM(m.rowPtr, m.colIdx, m.val, 20, 0, 1, device="cpu", exchange="allgather", transport="pull")
+
+
+@pytest.mark.parametrize("world", [2, 3, 8])
+def test_scattered_labels_balance_rows_entries_and_senders(world):
+    """Random relabelling: P A P^T gives the same product up to the order of rows, and the
+    nnz-balanced contiguous blocks of the relabelled matrix hold about equal rows, and every owner
+    is asked for about the same number of dense rows (the natural order is far from both)."""
+    m = synth.rmat(12, 60_000, seed=9)
+    n = m.n_rows
+    new_of_old = shard.scattered_labels(n, seed=5)
+    assert torch.equal(new_of_old, shard.scattered_labels(n, seed=5))
+    assert sorted(new_of_old.tolist()) == list(range(n))
+    rp, ci, v = shard.relabel_symmetric(m.rowPtr, m.colIdx, m.val, new_of_old)
+    assert rp.dtype == torch.int32 and ci.dtype == torch.int32 and int(rp[-1]) == m.nnz
+    for r in range(0, n, 97):  # columns sorted inside every row
+        seg = ci[int(rp[r]): int(rp[r + 1])]
+        assert bool((seg[1:] > seg[:-1]).all())
+    B = synth.dense_uniform(n, 8, 4)
+    dense = lambda a, b, c: torch.sparse_csr_tensor(a.long(), b.long(), c.double(), (n, n)).to_dense()
+    want = dense(m.rowPtr, m.colIdx, m.val) @ B.double()
+    old_of_new = torch.argsort(new_of_old)
+    got = dense(rp, ci, v) @ B.double()[old_of_new]
+    torch.testing.assert_close(got, want[old_of_new], rtol=1e-12, atol=1e-12)
+
+    def imbalance(rowPtr, colIdx):
+        b = shard.partition_rows_by_nnz(rowPtr, world)
+        owner = torch.bucketize(torch.arange(n), b[1:-1], right=True)
+        sent = torch.zeros(world, dtype=torch.long)
+        for r in range(world):
+            need = torch.unique(colIdx[int(rowPtr[b[r]]): int(rowPtr[b[r + 1]])].long())
+            c = torch.bincount(owner[need], minlength=world)
+            c[r] = 0
+            sent += c
+        rows = (b[1:] - b[:-1]).double()
+        return float(rows.max() / rows.mean()), float(sent.max()) / float(sent.double().mean())
+
+    rows_nat, sent_nat = imbalance(m.rowPtr, m.colIdx)
+    rows_int, sent_int = imbalance(rp, ci)
+    assert rows_int < 1.3 and sent_int < 1.3  # a 4096-node sample with hubs: a few per cent of noise per block
+    assert rows_nat > 1.5 and sent_nat > sent_int
+
+
+def test_relabel_rejects_rectangular_or_short_permutations():
+    m = synth.rmat(8, 1000, seed=2)
+    with pytest.raises(ValueError):
+        shard.relabel_symmetric(m.rowPtr, m.colIdx, m.val, torch.arange(m.n_rows - 1))
