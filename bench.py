@@ -16,7 +16,9 @@ replicated (no data-path collective); the step time is the maximum over ranks.
 Beside `value` the line carries `scaleout`: the strong-scaling times of the row-sharded SpMM of
 ONE global R-MAT matrix (2^24 nodes, 5.12e8 entries, dim 128) at this GPU count, with the dense
 operand replicated, all-gathered, and exchanged row by row through the pull kernel; the speed-up at
-N GPUs is the N = 1 run's figure divided by this one.
+N GPUs is the N = 1 run's figure divided by this one.  `scaleout.scattered_labels` holds the same three
+times for the same matrix after a seeded random relabelling of its nodes (P A P^T), which gives every
+rank the same share of rows, entries and exchange traffic.
 
 `--impl reference` times the reference's CPU path for the same products, torch.sparse.mm on CSR
 tensors on the host (verification.py:44-77 of the reference): one step is the same pass over all
@@ -548,9 +550,10 @@ def main():
                         "exchange_form": "rows referenced by the shard only, fetched from the owners' peer-mapped blocks "
                                          "by the pull kernel: %s (transport %s)" % (r["exchange_form"], r["transport"]),
                         "detail": r}
-            if world > 1:
+            for _once in (0,):
                 # the same matrix with its nodes relabelled by a seeded random permutation (P A P^T): equal rows,
                 # entries and exchange traffic per rank instead of the nnz-balanced blocks of the natural order
+                # (at one GPU it is the baseline of that curve)
                 torch.cuda.empty_cache()
                 try:
                     ri = workloads.scaleout_brief(scale=args.c5_scale, nnz=args.c5_nnz, iters=args.scaleout_iters,
