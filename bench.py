@@ -550,23 +550,22 @@ def main():
                         "exchange_form": "rows referenced by the shard only, fetched from the owners' peer-mapped blocks "
                                          "by the pull kernel: %s (transport %s)" % (r["exchange_form"], r["transport"]),
                         "detail": r}
-            for _once in (0,):
-                # the same matrix with its nodes relabelled by a seeded random permutation (P A P^T): equal rows,
-                # entries and exchange traffic per rank instead of the nnz-balanced blocks of the natural order
-                # (at one GPU it is the baseline of that curve)
-                torch.cuda.empty_cache()
-                try:
-                    ri = workloads.scaleout_brief(scale=args.c5_scale, nnz=args.c5_nnz, iters=args.scaleout_iters,
-                                                  rank=rank, world=world, device="cuda:%d" % local,
-                                                  labels="scattered", legs=False)
-                    scaleout["scattered_labels"] = {
-                        "what": "same global matrix, nodes relabelled by a seeded random permutation before sharding "
-                                "(shard.scattered_labels); same product up to the order of rows",
-                        "replicated_ms": ri["replicated_ms"], "allgather_ms": ri["allgather_ms"],
-                        "exchange_ms": ri["exchange_ms"], "exchange_gflops": gf(ri["exchange_ms"]),
-                        "exchange_form": ri["exchange_form"], "detail": ri}
-                except Exception as e:
-                    scaleout["scattered_labels"] = {"unavailable": "%s: %s" % (type(e).__name__, e)}
+            # the same matrix with its nodes relabelled by a seeded random permutation (P A P^T): equal rows,
+            # entries and exchange traffic per rank instead of the nnz-balanced blocks of the natural order
+            # (at one GPU it is the baseline of that curve)
+            torch.cuda.empty_cache()
+            try:
+                ri = workloads.scaleout_brief(scale=args.c5_scale, nnz=args.c5_nnz, iters=args.scaleout_iters,
+                                              rank=rank, world=world, device="cuda:%d" % local,
+                                              labels="scattered", legs=False)
+                scaleout["scattered_labels"] = {
+                    "what": "same global matrix, nodes relabelled by a seeded random permutation before sharding "
+                            "(shard.scattered_labels); same product up to the order of rows",
+                    "replicated_ms": ri["replicated_ms"], "allgather_ms": ri["allgather_ms"],
+                    "exchange_ms": ri["exchange_ms"], "exchange_gflops": gf(ri["exchange_ms"]),
+                    "exchange_form": ri["exchange_form"], "detail": ri}
+            except Exception as e:
+                scaleout["scattered_labels"] = {"unavailable": "%s: %s" % (type(e).__name__, e)}
         except Exception as e:  # the headline number must not depend on this leg
             scaleout = {"unavailable": "%s: %s" % (type(e).__name__, e)}
 
