@@ -450,7 +450,7 @@ def scaleout_spmm(scale=24, nnz=512_000_000, dim=128, seed=51, iters=5, warmup=2
 
 
 def scaleout_brief(scale=24, nnz=512_000_000, dim=128, seed=51, iters=5, warmup=2, rank=0, world=1,
-                   device="cuda:0", row_chunks=8, labels="natural", legs=True):
+                   device="cuda:0", row_chunks=(8, 16), labels="natural", legs=True):
     """The three strong-scaling curves of the row-sharded SpMM that the benchmark line carries at
     every GPU count (same global R-MAT matrix and dense operand as :func:`scaleout_spmm`):
 
@@ -460,8 +460,8 @@ def scaleout_brief(scale=24, nnz=512_000_000, dim=128, seed=51, iters=5, warmup=
                       peer-mapped blocks: in one piece followed by the product (``needed`` / ``pull``),
                       and in ``row_chunks`` fetches ordered by the row group that first needs a row,
                       the product of a row group running beside the next fetch
-                      (``needed_rowgroups`` / ``pull``); the faster of the two is the figure, both and
-                      the two legs of the first alone are reported.
+                      (``needed_rowgroups`` / ``pull``, once per group count given); the fastest is
+                      the figure, all of them and the two legs of the first alone are reported.
 
     ``labels="scattered"`` relabels the nodes by a seeded random permutation first
     (``shard.scattered_labels``, a symmetric permutation P A P^T: the same product up to the order
@@ -490,18 +490,20 @@ def scaleout_brief(scale=24, nnz=512_000_000, dim=128, seed=51, iters=5, warmup=
     sh.keep_global_columns(cols_global)
     common = dict(row_bounds=sh.row_bounds, device=dev, local_block=(sh.rowPtr, cols_global, sh.val))
     notes = {}
+    group_counts = [int(k) for k in (row_chunks if isinstance(row_chunks, (tuple, list)) else (row_chunks,))]
     try:
         sh_pull = ShardedSpMM(m.rowPtr, m.colIdx, m.val, n, rank, world, exchange="needed", transport="pull", **common)
-        sh_pipe = ShardedSpMM(m.rowPtr, m.colIdx, m.val, n, rank, world, exchange="needed_rowgroups",
-                              transport="pull", row_chunks=row_chunks, **common)
+        pipes = [ShardedSpMM(m.rowPtr, m.colIdx, m.val, n, rank, world, exchange="needed_rowgroups",
+                             transport="pull", row_chunks=k, **common) for k in group_counts]
         src = sh_pull.symmetric_input(dim)  # peer-mapped blocks, where a producer would leave its rows
-        src_pipe = sh_pipe.symmetric_input(dim)
+        src_pipes = [p.symmetric_input(dim) for p in pipes]
         transport = "pull"
     except Exception as ex:  # peer-mapped memory unavailable: the NCCL all-to-all forms stand in
         notes["pull_unavailable"] = "%s: %s" % (type(ex).__name__, ex)
         sh_pull = ShardedSpMM(m.rowPtr, m.colIdx, m.val, n, rank, world, exchange="needed", **common)
-        sh_pipe = ShardedSpMM(m.rowPtr, m.colIdx, m.val, n, rank, world, exchange="needed_pipelined",
-                              row_chunks=row_chunks, **common)
+        group_counts = group_counts[:1]
+        pipes = [ShardedSpMM(m.rowPtr, m.colIdx, m.val, n, rank, world, exchange="needed_pipelined",
+                             row_chunks=group_counts[0], **common)]
         transport = "nccl"
     nnz_total = m.nnz
     del m
@@ -529,7 +531,7 @@ def scaleout_brief(scale=24, nnz=512_000_000, dim=128, seed=51, iters=5, warmup=
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    res = {"world": world, "n": n, "nnz": nnz_total, "dim": dim, "row_chunks": row_chunks, "transport": transport,
+    res = {"world": world, "n": n, "nnz": nnz_total, "dim": dim, "row_chunks": group_counts, "transport": transport,
            "labels": labels, "local_rows": int(sh.local_rows)}
     res["replicated_ms"] = timed(lambda: sh.forward_replicated(B_full, out_rep))
     rows = sample_rows(sh.rowPtr, 40, seed)
@@ -543,20 +545,27 @@ def scaleout_brief(scale=24, nnz=512_000_000, dim=128, seed=51, iters=5, warmup=
     torch.testing.assert_close(out, out_rep, **tol)
     if transport == "pull":
         src.copy_(B_shard)
-        src_pipe.copy_(B_shard)
+        for sp in src_pipes:
+            sp.copy_(B_shard)
     else:
-        src = src_pipe = B_shard
+        src, src_pipes = B_shard, [B_shard]
     out.fill_(float("nan"))
     res["exchange_one_piece_ms"] = timed(lambda: sh_pull.forward(src, out))
     torch.testing.assert_close(out, out_rep, **tol)
-    out.fill_(float("nan"))
-    res["exchange_pipelined_ms"] = timed(lambda: sh_pipe.forward(src_pipe, out))
-    torch.testing.assert_close(out, out_rep, **tol)
+    by_groups = {}
+    for k, p, sp in zip(group_counts, pipes, src_pipes):
+        out.fill_(float("nan"))
+        by_groups[k] = timed(lambda: p.forward(sp, out))
+        torch.testing.assert_close(out, out_rep, **tol)
+    best_k = min(by_groups, key=by_groups.get)
+    res["exchange_pipelined_ms"] = by_groups[best_k]
+    res["exchange_pipelined_ms_by_groups"] = {str(k): round(v, 4) for k, v in by_groups.items()}
     res["exchange_ms"] = min(res["exchange_one_piece_ms"], res["exchange_pipelined_ms"])
     res["exchange_form"] = ("one fetch, then the product" if res["exchange_ms"] == res["exchange_one_piece_ms"]
-                            else "%d fetches ordered by first use, products of row groups overlapped" % row_chunks)
+                            else "%d fetches ordered by first use, products of row groups overlapped" % best_k)
     if transport == "pull":
-        res["first_fetch_share"] = round(sh_pipe.chunk_plan[0][1] / max(1, sh_pipe.n_needed), 4)
+        res["first_fetch_share"] = {str(k): round(p.chunk_plan[0][1] / max(1, p.n_needed), 4)
+                                    for k, p in zip(group_counts, pipes)}
     res["needed_rows_fraction"] = round(sh_pull.n_needed / n, 4)
     if transport == "pull":
         # rows every owner sends (summed over the ranks that fetch from it) against rows every rank
