@@ -59,6 +59,13 @@ product of row group k, a plain overwrite of its own rows of C at full row lengt
 fetches 0..k have arrived, beside fetch k+1.  Every entry of A is read once, no product adds into
 another's output, and the groups are views of the shard's arrays.
 
+Which rank's link is busy depends on the node order.  The dense operand is dealt in equal row
+blocks; where the degree of a node depends on its id (R-MAT, degree-sorted graphs) one block holds
+the hub columns that every rank references and its owner sends several times the mean, and the
+nnz-balanced row blocks of A are as uneven in row count.  ``scattered_labels`` +
+``relabel_symmetric`` relabel the nodes once by a seeded random permutation (P A P^T: the same
+product up to the order of rows), after which every block is a uniform sample of the nodes.
+
 ``dim_chunks > 1`` splits the dense columns into slices and gathers slice s+1 on a side
 stream while the SpMM of slice s runs (the kernels take explicit leading dimensions, so a
 slice of C is written in place).
