@@ -263,6 +263,19 @@ typedef struct pspmm_row_sources {
 PSPMM_API int pspmm_pull_rows(const pspmm_row_sources *sources, const int32_t *rows, int64_t n, float *dst,
                               int32_t dim, int64_t ld_src, int64_t ld_dst, int64_t rotate, int32_t ctas,
                               void *stream);
+/*
+ * The same copy through the bulk asynchronous copy unit (cp.async.bulk global -> shared -> global,
+ * completion on an mbarrier; plain untiled copies, no tensor map, no multicast): one warp and a
+ * ring of at most 96 KB of shared memory per thread block, no data in registers, so a fetch that
+ * runs beside a compute kernel takes far fewer warp slots and registers from it.  Same arguments;
+ * `ctas` thread blocks of one warp each.  Rows longer than 1536 bytes go through pspmm_pull_rows.
+ * Every wait inside the kernel is bounded (half a second); pspmm_pull_rows_status returns 1 once a
+ * wait has run out on this GPU since the library was loaded (it synchronises with the device).
+ */
+PSPMM_API int pspmm_pull_rows_bulk(const pspmm_row_sources *sources, const int32_t *rows, int64_t n, float *dst,
+                              int32_t dim, int64_t ld_src, int64_t ld_dst, int64_t rotate, int32_t ctas,
+                              void *stream);
+PSPMM_API int pspmm_pull_rows_status(int32_t *status);
 
 /*
  * Host-side CSR -> V x 1 block CSR, laid out exactly as scipy's tobsr((V,1)) (which the

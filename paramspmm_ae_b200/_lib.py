@@ -90,6 +90,8 @@ _SIGNATURES = {
     "pspmm_agnn_fused_csr": [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i32, _i64, _i64, _i64, ctypes.c_float, _i32,
                              _i32, _i32, _i32, _vp, _vp, _i64, _vp, ctypes.c_size_t, _vp],
     "pspmm_pull_rows": [ctypes.POINTER(RowSources), _vp, _i64, _vp, _i32, _i64, _i64, _i64, _i32, _vp],
+    "pspmm_pull_rows_bulk": [ctypes.POINTER(RowSources), _vp, _i64, _vp, _i32, _i64, _i64, _i64, _i32, _vp],
+    "pspmm_pull_rows_status": [ctypes.POINTER(ctypes.c_int32)],
     "pspmm_bcsr_count": [_vp, _vp, _i64, _i64, _i32, _vp, ctypes.POINTER(_i64)],
     "pspmm_bcsr_fill": [_vp, _vp, _vp, _i64, _i64, _i32, _vp, _vp, _vp],
     "pspmm_mtx_info_read": [ctypes.c_char_p, ctypes.POINTER(MtxInfo)],

@@ -621,12 +621,14 @@ def agnn_fused(A, B, rowPtr, colIdx, beta=1.0, softmax=True, target_row=None, n_
     return out
 
 
-def pull_rows(dst, sources, first, rows, rotate=0, ctas=0):
+def pull_rows(dst, sources, first, rows, rotate=0, ctas=0, bulk=False):
     """dst[j] = sources[s][rows[j]] for first[s] <= j < first[s+1]: gathers rows of a dense operand
     that lives in several blocks (this GPU's memory or peer-mapped memory of other GPUs) into one
     compact buffer with a copy kernel that reads the blocks directly (``pspmm_pull_rows``).
     ``sources``: 2-D float32 CUDA tensors with one row stride; ``first``: len(sources)+1
-    non-decreasing list positions; ``rows``: int32 CUDA tensor of row ids inside the owning block."""
+    non-decreasing list positions; ``rows``: int32 CUDA tensor of row ids inside the owning block.
+    ``bulk=True`` moves the rows with bulk asynchronous copies through shared memory
+    (``pspmm_pull_rows_bulk``: one warp per thread block), the form meant to run beside an SpMM."""
     if not sources or len(sources) > _lib.MAX_ROW_SOURCES or len(first) != len(sources) + 1:
         raise RuntimeError("between 1 and %d sources with len(sources)+1 list positions" % _lib.MAX_ROW_SOURCES)
     _check_cuda(rows, "rows", torch.int32, 1)
@@ -648,9 +650,17 @@ def pull_rows(dst, sources, first, rows, rotate=0, ctas=0):
     for s, f in enumerate(first):
         src.first[s] = int(f)
     src.n_src = len(sources)
-    check(lib().pspmm_pull_rows(ctypes.byref(src), _ptr(rows), n, _ptr(dst), dim, ld, dst.stride(0), int(rotate),
-                                int(ctas), _stream()))
+    fn = lib().pspmm_pull_rows_bulk if bulk else lib().pspmm_pull_rows
+    check(fn(ctypes.byref(src), _ptr(rows), n, _ptr(dst), dim, ld, dst.stride(0), int(rotate), int(ctas), _stream()))
     return dst
+
+
+def pull_rows_status():
+    """1 once a bounded wait inside the bulk fetch kernel has run out on this GPU, else 0
+    (synchronises with the device)."""
+    v = ctypes.c_int32(0)
+    check(lib().pspmm_pull_rows_status(ctypes.byref(v)))
+    return int(v.value)
 
 
 def genmask(rowPtr_bcsr, rowPtr, blkval, nnz):

@@ -170,6 +170,7 @@ class ShardedSpMM:
                              "'needed_pipelined' or 'needed_rowgroups'")
         if exchange == "needed_rowgroups" and transport != "pull":
             raise ValueError("exchange='needed_rowgroups' is built on the pull transport")
+        self.pull_bulk = 0  # 1: fetches that run beside a product use the bulk-copy kernel (one warp per block); 2: all fetches
         self.pull_ctas = 128  # thread blocks of one fetch: enough loads in flight to fill NVLink (measured), few enough to leave the SMs to the SpMM
         self.transport, self._peer = transport, None
         self.rank, self.world, self.group, self.dim_chunks = rank, world, group, dim_chunks
@@ -443,7 +444,8 @@ class ShardedSpMM:
                     rotate = first[(self.rank + 1) % self.world] % cnt
                     # no product of this call runs beside the first fetch: it may use every SM
                     ops.pull_rows(recv[base: base + cnt], peers, first, want_rows, rotate=rotate,
-                                  ctas=self.pull_ctas if kk else 8 * self.pull_ctas)
+                                  ctas=self.pull_ctas if kk else 8 * self.pull_ctas,
+                                  bulk=self.pull_bulk > (0 if kk else 1))
                 ev = torch.cuda.Event()
                 ev.record(side)
                 events.append(ev)

@@ -652,10 +652,12 @@ def test_pull_rows_copies_the_listed_rows(dev, dim):
     rows_d = torch.cat(rows).int().to(dev)
     want = torch.cat([b[r.to(dev)] for b, r in zip(blocks, rows)])
     n = first[-1]
-    for rotate, ctas in ((0, 0), (5, 1), (first[3], 3), (n - 1, 1000)):
-        dst = torch.full((n, dim + 8), float("nan"), device=dev)[:, :dim]
-        ops.pull_rows(dst, blocks, first, rows_d, rotate=rotate, ctas=ctas)
-        assert torch.equal(dst, want)
+    for bulk in (False, True):  # load/store kernel, and bulk asynchronous copies through shared memory
+        for rotate, ctas in ((0, 0), (5, 1), (first[3], 3), (n - 1, 1000)):
+            dst = torch.full((n, dim + 8), float("nan"), device=dev)[:, :dim]
+            ops.pull_rows(dst, blocks, first, rows_d, rotate=rotate, ctas=ctas, bulk=bulk)
+            assert torch.equal(dst, want)
+    assert ops.pull_rows_status() == 0  # no bounded wait ran out
     # nothing to copy, and the argument checks
     ops.pull_rows(torch.empty(0, dim, device=dev), blocks[:1], [0, 0], torch.empty(0, dtype=torch.int32, device=dev))
     with pytest.raises(RuntimeError):
@@ -666,9 +668,11 @@ def test_pull_rows_copies_the_listed_rows(dev, dim):
 
 @pytest.mark.parametrize("exchange,row_chunks", [("needed", 1), ("needed_pipelined", 3), ("needed_rowgroups", 3),
                                                  ("needed_rowgroups", 7)])
-def test_pull_transport_single_rank(dev, oracle, mats, exchange, row_chunks):
+@pytest.mark.parametrize("bulk", [0, 1, 2])
+def test_pull_transport_single_rank(dev, oracle, mats, exchange, row_chunks, bulk):
     """The pull transport with one rank (the owner's block is this GPU's own buffer): same product
-    as the plain kernel, twice in a row (buffers, streams and events are reused)."""
+    as the plain kernel, twice in a row (buffers, streams and events are reused); with the
+    load/store fetch kernel, and with the bulk-copy one for the later or for all fetches."""
     from paramspmm_ae_b200.shard import ShardedSpMM
     m = mats["rmat"]
     rp, ci, v = m.numpy()
@@ -677,6 +681,7 @@ def test_pull_transport_single_rank(dev, oracle, mats, exchange, row_chunks):
     want = oracle.spmm_csr(rp, ci, v, B.numpy())
     op = ShardedSpMM(d.rowPtr, d.colIdx, d.val, m.n_cols, 0, 1, device=dev, exchange=exchange, transport="pull",
                      row_chunks=row_chunks)
+    op.pull_bulk = bulk
     Bd = B.to(dev)
     for _ in range(2):
         out = op.forward(Bd, torch.full((m.n_rows, 64), float("nan"), device=dev))
@@ -685,6 +690,8 @@ def test_pull_transport_single_rank(dev, oracle, mats, exchange, row_chunks):
     src = op.symmetric_input(64)   # a producer writes the block in place: no staging copy
     src.copy_(Bd)
     close(op.forward(src), want)
+    from paramspmm_ae_b200 import ops
+    assert ops.pull_rows_status() == 0
 
 
 # ----------------------------------------------------------------------------- length-bucketed plan

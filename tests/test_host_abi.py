@@ -293,6 +293,13 @@ def test_new_entry_points_validate_before_touching_the_device(pspmm_lib):
     bad = _lib.RowSources()
     bad.n_src = _lib.MAX_ROW_SOURCES + 1
     assert call(8, 16, 16, 16, 0, bad) == _lib.PSPMM_E_ARG
+    # the bulk-copy form checks the same way; its status query wants somewhere to write
+    bulk = lambda n, dim, lds, ldd, rot: pspmm_lib.pspmm_pull_rows_bulk(ctypes.byref(src), one, n, one, dim, lds, ldd, rot, 0, null)
+    assert bulk(8, 0, 16, 16, 0) == _lib.PSPMM_E_ARG
+    assert bulk(8, 16, 16, 16, 8) == _lib.PSPMM_E_ARG
+    assert bulk(8, 18, 20, 20, 0) == _lib.PSPMM_E_UNSUPPORTED
+    assert bulk(0, 16, 16, 16, 0) == _lib.PSPMM_OK
+    assert pspmm_lib.pspmm_pull_rows_status(None) == _lib.PSPMM_E_ARG
     # bucketed is a 0/1 flag of the SpMM only
     assert pspmm_lib.pspmm_spmm_csr(one, one, one, one, one, 4, 4, 4, 16, 16, 16, ctypes.byref(_lib.make_cfg(bucketed=2)),
                                     null, null, 0, null) == _lib.PSPMM_E_CONFIG
