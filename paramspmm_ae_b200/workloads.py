@@ -552,17 +552,35 @@ def scaleout_brief(scale=24, nnz=512_000_000, dim=128, seed=51, iters=5, warmup=
     out.fill_(float("nan"))
     res["exchange_one_piece_ms"] = timed(lambda: sh_pull.forward(src, out))
     torch.testing.assert_close(out, out_rep, **tol)
+    # every group count with the load/store fetch kernel and, for the fetches that run beside a
+    # product, with the bulk-copy one (one warp per thread block: it takes fewer warp slots and
+    # registers from the product); a failure of the second form is recorded, not raised
     by_groups = {}
     for k, p, sp in zip(group_counts, pipes, src_pipes):
-        out.fill_(float("nan"))
-        by_groups[k] = timed(lambda: p.forward(sp, out))
-        torch.testing.assert_close(out, out_rep, **tol)
-    best_k = min(by_groups, key=by_groups.get)
-    res["exchange_pipelined_ms"] = by_groups[best_k]
-    res["exchange_pipelined_ms_by_groups"] = {str(k): round(v, 4) for k, v in by_groups.items()}
+        for bulk in ((0, 1) if transport == "pull" else (0,)):
+            label = "%d%s" % (k, "_bulk" if bulk else "")
+            try:
+                p.pull_bulk = bulk
+                out.fill_(float("nan"))
+                t = timed(lambda: p.forward(sp, out))
+                torch.testing.assert_close(out, out_rep, **tol)
+                by_groups[label] = t
+            except Exception as ex:
+                if not bulk:
+                    raise
+                notes["bulk_fetch_failed_%d_groups" % k] = "%s: %s" % (type(ex).__name__, str(ex)[:200])
+            finally:
+                p.pull_bulk = 0
+    if transport == "pull":
+        notes["bulk_fetch_status"] = ops.pull_rows_status()
+    best = min(by_groups, key=by_groups.get)
+    best_k = int(best.split("_")[0])
+    res["exchange_pipelined_ms"] = by_groups[best]
+    res["exchange_pipelined_ms_by_groups"] = {k: round(v, 4) for k, v in by_groups.items()}
     res["exchange_ms"] = min(res["exchange_one_piece_ms"], res["exchange_pipelined_ms"])
     res["exchange_form"] = ("one fetch, then the product" if res["exchange_ms"] == res["exchange_one_piece_ms"]
-                            else "%d fetches ordered by first use, products of row groups overlapped" % best_k)
+                            else "%d fetches ordered by first use, products of row groups overlapped%s"
+                            % (best_k, ", later fetches by bulk asynchronous copies" if best.endswith("_bulk") else ""))
     if transport == "pull":
         res["first_fetch_share"] = {str(k): round(p.chunk_plan[0][1] / max(1, p.n_needed), 4)
                                     for k, p in zip(group_counts, pipes)}
