@@ -11,7 +11,8 @@ pytestmark = pytest.mark.gpu
 
 MODES = [("allgather", "nccl", 1), ("allgather", "nccl", 4), ("needed", "nccl", 1), ("pipelined", "nccl", 1),
          ("needed_pipelined", "nccl", 1), ("pipelined", "copy_engine", 1), ("needed", "pull", 1),
-         ("needed_pipelined", "pull", 1), ("needed_rowgroups", "pull", 1)]
+         ("needed_pipelined", "pull", 1), ("needed_rowgroups", "pull", 1),
+         ("needed_rowgroups", "pull_bulk_later", 1), ("needed", "pull_bulk_all", 1)]
 
 
 def _worker(rank, world, port, q):
@@ -36,8 +37,11 @@ def _worker(rank, world, port, q):
         shard_of_B = B[c0:c1].contiguous()
         worst = {}
         for exchange, transport, dim_chunks in MODES:
+            bulk = {"pull_bulk_later": 1, "pull_bulk_all": 2}.get(transport, 0)  # fetches on the bulk-copy kernel
+            label, transport = transport, ("pull" if bulk else transport)
             op = ShardedSpMM(m.rowPtr, m.colIdx, m.val, n, rank, world, device=dev, exchange=exchange,
                              transport=transport, dim_chunks=dim_chunks, row_chunks=3)
+            op.pull_bulk = bulk
             src = shard_of_B
             if transport in ("copy_engine", "pull"):
                 src = op.symmetric_input(dim)
@@ -46,8 +50,10 @@ def _worker(rank, world, port, q):
                 got = op.forward(src, torch.full((op.local_rows, dim), float("nan"), device=dev))
             torch.cuda.synchronize()
             # hub rows add thousands of terms in an order that differs between launches
-            worst["%s/%s/%d" % (exchange, transport, dim_chunks)] = float(
+            worst["%s/%s/%d" % (exchange, label, dim_chunks)] = float(
                 ((got - want).abs() / (1e-3 + 1e-4 * want.abs())).max())
+        from paramspmm_ae_b200 import ops
+        assert ops.pull_rows_status() == 0  # no bounded wait of the bulk-copy kernel ran out
         q.put((rank, worst, base.local_rows))
     finally:
         dist.destroy_process_group()
