@@ -59,6 +59,11 @@ product of row group k, a plain overwrite of its own rows of C at full row lengt
 fetches 0..k have arrived, beside fetch k+1.  Every entry of A is read once, no product adds into
 another's output, and the groups are views of the shard's arrays.
 
+``pull_bulk`` (an attribute of the operator: 0, 1 or 2) moves the fetches after the first (1) or
+all fetches (2) with ``pspmm_pull_rows_bulk``, the same copy on bulk asynchronous copies through
+shared memory: one warp and no data registers per thread block, so a fetch that runs beside a
+product takes far fewer warp slots from it.
+
 Which rank's link is busy depends on the node order.  The dense operand is dealt in equal row
 blocks; where the degree of a node depends on its id (R-MAT, degree-sorted graphs) one block holds
 the hub columns that every rank references and its owner sends several times the mean, and the
