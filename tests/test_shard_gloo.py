@@ -43,7 +43,7 @@ def _free_port():
     return p
 
 
-def _worker(rank, world, port, dim_chunks, q, exchange="allgather"):
+def _worker(rank, world, port, dim_chunks, q, exchange="allgather", relabel=False):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -51,6 +51,13 @@ def _worker(rank, world, port, dim_chunks, q, exchange="allgather"):
         from oracle import oracle as orc
         m = synth.powerlaw_graph(1201, 9000, seed=7)          # same seed on every rank
         B = synth.dense_uniform(m.n_cols, 24, 5)
+        full = orc.spmm_csr(*m.numpy(), B.numpy())
+        full2 = orc.spmm_csr(*m.numpy(), full)
+        if relabel:  # nodes relabelled before sharding: the same products, rows in the new order
+            new_of_old = shard.scattered_labels(m.n_rows, seed=3)
+            old_of_new = torch.argsort(new_of_old).numpy()
+            m.rowPtr, m.colIdx, m.val = shard.relabel_symmetric(m.rowPtr, m.colIdx, m.val, new_of_old)
+            B, full, full2 = B[old_of_new], full[old_of_new], full2[old_of_new]
 
         def local_spmm(out, Bfull, rowPtr, colIdx, val, accumulate=False):
             prod = torch.from_numpy(orc.spmm_csr(rowPtr.numpy(), colIdx.numpy(), val.numpy(),
@@ -64,24 +71,23 @@ def _worker(rank, world, port, dim_chunks, q, exchange="allgather"):
                                exchange=exchange)
         lo, hi = op.my_cols
         C_local = op.forward(B[lo:hi].contiguous(), torch.full((op.local_rows, 24), float("nan")))
-        want = orc.spmm_csr(*m.numpy(), B.numpy())[op.lo: op.hi]
-        ok = np.allclose(C_local.numpy(), want, rtol=1e-5, atol=1e-5)
+        ok = np.allclose(C_local.numpy(), full[op.lo: op.hi], rtol=1e-5, atol=1e-5)
         # a second layer: the output shard is the next dense shard (row_bounds == col_bounds)
         C2 = op.forward(C_local)
-        want2 = orc.spmm_csr(*m.numpy(), orc.spmm_csr(*m.numpy(), B.numpy()))[op.lo: op.hi]
-        ok2 = np.allclose(C2.numpy(), want2, rtol=1e-4, atol=1e-4)
+        ok2 = np.allclose(C2.numpy(), full2[op.lo: op.hi], rtol=1e-4, atol=1e-4)
         q.put((rank, bool(ok), bool(ok2), op.local_rows))
     finally:
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("exchange", ["allgather", "needed", "pipelined", "needed_pipelined"])
+@pytest.mark.parametrize("exchange,relabel", [("allgather", False), ("needed", False), ("pipelined", False),
+                                              ("needed_pipelined", False), ("needed", True)])
 @pytest.mark.parametrize("world", [2, 3])
-def test_sharded_spmm_two_layers_gloo(world, exchange):
+def test_sharded_spmm_two_layers_gloo(world, exchange, relabel):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, 1, q, exchange)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, 1, q, exchange, relabel)) for r in range(world)]
     for p in procs:
         p.start()
     res = [q.get(timeout=120) for _ in range(world)]
