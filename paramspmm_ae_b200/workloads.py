@@ -17,7 +17,7 @@ import time
 
 import torch
 
-from . import _lib, baselines, decider, ops, synth
+from . import baselines, decider, ops, synth
 
 
 def _time_ms(fn, warmup=3, iters=10):
