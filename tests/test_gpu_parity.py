@@ -770,3 +770,22 @@ def test_planned_spmm_runs_every_layout(dev, oracle, mats):
         close(out, want)
         op(out, B.to(dev), accumulate=True)
         close(out, 2 * want)
+
+
+def test_relabel_symmetric_on_the_device_equals_the_host(dev, mats):
+    """shard.relabel_symmetric runs where its arrays are: the device result equals the host result
+    bit for bit (the sort keys are distinct), and the relabelled product is the original one with
+    its rows permuted."""
+    from paramspmm_ae_b200 import ops, shard
+    m = mats["rmat"]
+    new_of_old = shard.scattered_labels(m.n_rows, seed=11)
+    host = shard.relabel_symmetric(m.rowPtr, m.colIdx, m.val, new_of_old)
+    d = m.to(dev)
+    got = shard.relabel_symmetric(d.rowPtr, d.colIdx, d.val, new_of_old)
+    for a, b in zip(host, got):
+        assert b.is_cuda and torch.equal(a, b.cpu())
+    B = dense(m.n_cols, 32, 5).to(dev)
+    old_of_new = torch.argsort(new_of_old).to(dev)
+    want = ops.csr_spmm(B, d.rowPtr, d.colIdx, d.val, 1, 4)[old_of_new]
+    out = ops.csr_spmm(B[old_of_new].contiguous(), got[0], got[1], got[2], 1, 4)
+    torch.testing.assert_close(out, want, rtol=1e-5, atol=1e-4)
