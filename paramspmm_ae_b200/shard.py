@@ -175,6 +175,7 @@ class ShardedSpMM:
                              "'needed_pipelined' or 'needed_rowgroups'")
         if exchange == "needed_rowgroups" and transport != "pull":
             raise ValueError("exchange='needed_rowgroups' is built on the pull transport")
+        self.trace = False  # pull transport: bracket the fetches and products of a call with timing events (trace_result)
         self.pull_bulk = 0  # 1: fetches that run beside a product use the bulk-copy kernel (one warp per block); 2: all fetches
         self.pull_ctas = 128  # thread blocks of one fetch: enough loads in flight to fill NVLink (measured), few enough to leave the SMs to the SpMM
         self.transport, self._peer = transport, None
@@ -434,6 +435,16 @@ class ShardedSpMM:
         main = torch.cuda.current_stream()
         side = self._side
         events = []
+        # with `trace` set, timing events bracket every fetch and every product of this call
+        tr = {"start": None, "fetch": [], "product": [], "end": None} if self.trace else None
+
+        def mark(stream):
+            e = torch.cuda.Event(enable_timing=True)
+            e.record(stream)
+            return e
+
+        if tr is not None:
+            tr["start"] = mark(main)
         side.wait_stream(main)
         with torch.cuda.stream(side):
             if B_shard.data_ptr() != src.data_ptr():
@@ -444,6 +455,7 @@ class ShardedSpMM:
                 first = [0]
                 for c in recv_splits:
                     first.append(first[-1] + c)
+                t_a = mark(side) if tr is not None else None
                 if cnt:
                     # start at the next rank's rows so that the ranks read different owners at a time
                     rotate = first[(self.rank + 1) % self.world] % cnt
@@ -451,30 +463,54 @@ class ShardedSpMM:
                     ops.pull_rows(recv[base: base + cnt], peers, first, want_rows, rotate=rotate,
                                   ctas=self.pull_ctas if kk else 8 * self.pull_ctas,
                                   bulk=self.pull_bulk > (0 if kk else 1))
-                ev = torch.cuda.Event()
+                ev = torch.cuda.Event(enable_timing=tr is not None)
                 ev.record(side)
                 events.append(ev)
+                if tr is not None:
+                    tr["fetch"].append((t_a, ev))
             if fence is not None:
                 dist.all_reduce(fence, group=self.group)  # every peer has finished reading this block
         B_shard.record_stream(side)
+
+        def product(fn):
+            t_a = mark(main) if tr is not None else None
+            fn()
+            if tr is not None:
+                tr["product"].append((t_a, mark(main)))
+
         if self.exchange == "needed":
             main.wait_event(events[0])
-            self.local_spmm(out, recv, self.rowPtr, self.colIdx, self.val)
+            product(lambda: self.local_spmm(out, recv, self.rowPtr, self.colIdx, self.val))
         elif self.exchange == "needed_rowgroups":
             for kk in range(self.row_chunks):
                 main.wait_event(events[kk])  # fetches are in stream order: 0..kk have arrived
                 r0, r1 = self.group_bounds[kk], self.group_bounds[kk + 1]
                 if r1 > r0:
                     rp, ci, v = self.blocks[kk]
-                    self.block_spmm[kk](out[r0:r1], recv, rp, ci, v)
+                    product(lambda: self.block_spmm[kk](out[r0:r1], recv, rp, ci, v))
         else:
             for kk in range(self.row_chunks):
                 main.wait_event(events[kk])
                 rp, ci, v = self.blocks[kk]
-                self.block_spmm[kk](out, recv, rp, ci, v, accumulate=kk > 0)
+                product(lambda: self.block_spmm[kk](out, recv, rp, ci, v, accumulate=kk > 0))
         # a producer on the main stream may overwrite the block only after the closing fence
         main.wait_stream(side)
+        if tr is not None:
+            tr["end"] = mark(main)
+            self._trace_events = tr
         return out
+
+    def trace_result(self):
+        """Milliseconds from the start of the last traced pull-transport call (``trace = True``):
+        [begin, end] of every fetch and of every product, and the end of the call.  Synchronises."""
+        tr = getattr(self, "_trace_events", None)
+        if tr is None:
+            return None
+        torch.cuda.synchronize()
+        rel = lambda e: round(tr["start"].elapsed_time(e), 3)
+        return {"fetch_ms": [[rel(a), rel(b)] for a, b in tr["fetch"]],
+                "product_ms": [[rel(a), rel(b)] for a, b in tr["product"]],
+                "end_ms": rel(tr["end"]), "rows_per_fetch": [c[1] for c in self.chunk_plan]}
 
     def _forward_copy_engine(self, B_shard, out):
         import torch.distributed as dist

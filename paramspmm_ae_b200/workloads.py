@@ -577,6 +577,18 @@ def scaleout_brief(scale=24, nnz=512_000_000, dim=128, seed=51, iters=5, warmup=
     best_k = int(best.split("_")[0])
     res["exchange_pipelined_ms"] = by_groups[best]
     res["exchange_pipelined_ms_by_groups"] = {k: round(v, 4) for k, v in by_groups.items()}
+    if transport == "pull":
+        # where the time of one call of the best pipeline goes: every fetch and every row-group product
+        # bracketed by timing events (this rank's own clock, ms from the start of the call)
+        try:
+            p, sp = pipes[group_counts.index(best_k)], src_pipes[group_counts.index(best_k)]
+            p.pull_bulk, p.trace = int(best.endswith("_bulk")), True
+            p.forward(sp, out)
+            res["timeline_of_best_pipeline"] = p.trace_result()
+        except Exception as ex:
+            notes["timeline_failed"] = "%s: %s" % (type(ex).__name__, str(ex)[:200])
+        finally:
+            p.pull_bulk, p.trace = 0, False
     res["exchange_ms"] = min(res["exchange_one_piece_ms"], res["exchange_pipelined_ms"])
     res["exchange_form"] = ("one fetch, then the product" if res["exchange_ms"] == res["exchange_one_piece_ms"]
                             else "%d fetches ordered by first use, products of row groups overlapped%s"

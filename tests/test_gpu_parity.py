@@ -692,6 +692,13 @@ def test_pull_transport_single_rank(dev, oracle, mats, exchange, row_chunks, bul
     close(op.forward(src), want)
     from paramspmm_ae_b200 import ops
     assert ops.pull_rows_status() == 0
+    # a traced call: same result, and one [begin, end] pair per fetch and per product, in order
+    op.trace = True
+    close(op.forward(src), want)
+    op.trace = False
+    t = op.trace_result()
+    assert len(t["fetch_ms"]) == len(op.chunk_plan) and len(t["product_ms"]) >= 1
+    assert all(0.0 <= a <= b <= t["end_ms"] for a, b in t["fetch_ms"] + t["product_ms"])
 
 
 # ----------------------------------------------------------------------------- length-bucketed plan
